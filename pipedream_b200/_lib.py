@@ -1,0 +1,100 @@
+"""ctypes binding of libpipedream_b200.so (the C-ABI declared in include/pipedream_b200.h).
+
+There is no fallback: if the library is missing or the device is not sm_100 the
+first call raises.
+"""
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p, POINTER
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "lib", "libpipedream_b200.so")
+
+PD_F32 = 0
+PD_BF16 = 1
+PD_U8 = 2
+
+_lib = None
+
+P = c_void_p
+I = c_int
+L = c_int64
+F = c_float
+U64 = c_uint64
+
+# name -> (restype, argtypes)
+SIGNATURES = {
+    "pd_last_error": (c_char_p, []),
+    "pd_abi_version": (I, []),
+    "pd_device_ok": (I, []),
+    "pd_sm_count": (I, []),
+    "pd_opt_sgd_multi_tensor": (I, [P, L, I, I, I, P, P, P, L, F, F, F, F, I, I, F, P]),
+    "pd_opt_adam_multi_tensor": (I, [P, L, I, I, I, P, P, P, P, L, F, F, F, F, F, L, F, P]),
+    "pd_scale": (I, [P, L, I, F, P]),
+    "pd_convert": (I, [P, I, P, I, L, P]),
+    "pd_pack_pnhwc": (I, [P, I, L, L, L, L, I, I, I, I, P, I, P]),
+    "pd_unpack_pnhwc": (I, [P, I, I, I, I, I, P, I, P]),
+    "pd_im2col3x3": (I, [P, I, L, L, L, L, I, I, I, I, I, P, I, P]),
+    "pd_relu_fwd": (I, [P, P, L, I, P]),
+    "pd_relu_bwd": (I, [P, P, P, L, I, P]),
+    "pd_colsum_workspace_bytes": (L, [I]),
+    "pd_relu_bwd_colsum": (I, [P, P, P, L, I, I, P, I, P, L, P]),
+    "pd_maxpool2_fwd": (I, [P, I, I, I, I, P, I, I, P]),
+    "pd_maxpool2_bwd": (I, [P, P, I, I, I, I, P, I, I, I, P]),
+    "pd_dropout_fwd": (I, [P, P, P, L, F, U64, U64, I, P]),
+    "pd_dropout_bwd": (I, [P, P, P, L, F, I, P]),
+    "pd_add": (I, [P, P, P, L, I, P]),
+    "pd_softmax_ce_fwd": (I, [P, I, P, L, I, F, L, F, P, P, P, P]),
+    "pd_softmax_ce_bwd": (I, [P, I, P, P, L, I, F, L, P, F, P, P]),
+    "pd_revert_varlen": (I, [P, P, P, I, I, L, P]),
+    "pd_length_mask": (I, [P, I, I, P, I, P]),
+    "pd_embedding_fwd": (I, [P, P, L, I, L, P, I, P]),
+    "pd_embedding_bwd": (I, [P, P, L, I, L, L, P, I, P]),
+    "pd_gemm_nt": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, P]),
+    "pd_gemm_nn": (I, [I, P, L, P, L, P, I, L, I, I, I, P, L, P]),
+    "pd_gemm_tn": (I, [I, P, L, P, L, P, L, I, I, I, I, I, P]),
+    "pd_conv2d_fwd": (I, [I, P, I, I, I, I, P, L, I, P, I, I, P, P]),
+    "pd_conv2d_dgrad": (I, [I, P, I, I, I, I, P, L, I, P, P, P]),
+    "pd_conv2d_wgrad": (I, [I, P, P, I, I, I, I, I, P, L, I, I, P]),
+    "pd_gemm_poll_error": (I, [POINTER(c_int)]),
+}
+
+
+class PipedreamB200Error(RuntimeError):
+    pass
+
+
+def lib_path():
+    return _LIB_PATH
+
+
+def load():
+    """Load the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise PipedreamB200Error(
+            "%s not found: build it with `python -m pipedream_b200.build` "
+            "(there is no non-CUDA fallback)" % _LIB_PATH)
+    lib = ctypes.CDLL(_LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)   # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def last_error():
+    msg = load().pd_last_error()
+    return msg.decode() if msg else ""
+
+
+def call(name, *args):
+    """Call an int-status entry point and raise on a non-zero status."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise PipedreamB200Error("%s failed (status %d): %s" % (name, rc, last_error()))
+    return rc

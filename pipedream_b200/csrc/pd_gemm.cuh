@@ -1,0 +1,42 @@
+// Internal description of one contraction launch, shared by the tcgen05 (bf16)
+// and the SIMT (fp32) back ends.  The C-ABI entry points in pd_gemm_api.cu fill
+// it in for Linear / 3x3-convolution forward, data-gradient and weight-gradient.
+//
+//   D[z][m, n] (+)= sum_{t < num_taps} sum_{k < K} A(m, t, k) * B(n, t, k)
+//
+// Operand A is a 2-D row-major global matrix (a_rows x a_cols, leading dim lda).
+//   K-major  (a_major = 0): A(m,t,k) = a[a_row0 + m + a_tap_row[t] + z*0][a_col0 + a_tap_col[t] + k]
+//   MN-major (a_major = 1): A(m,t,k) = a[a_row0 + k + a_tap_row[t]][a_col0 + a_tap_col[t] + m]
+// and likewise for B with n.  Rows outside [0, rows) read as zero (this is what
+// gives the convolution its zero padding at the two ends of the buffer).
+// z enumerates independent outputs (the 9 taps of a weight gradient): for output
+// z the B rows are additionally shifted by z_b_row[z] and the output pointer by
+// z * z_out_col elements.  split_k > 1 slices the K range over extra CTAs that
+// accumulate with fp32 atomics.
+#pragma once
+#include "pd_common.cuh"
+
+#define PD_MAX_TAPS 9
+
+struct PdGemm {
+  int dtype;  // PD_BF16 -> tcgen05, PD_F32 -> SIMT
+  const void* a; int64_t a_rows, a_cols, lda; int a_major;
+  const void* b; int64_t b_rows, b_cols, ldb; int b_major;
+  int M, N, K;
+  int num_taps;
+  int a_row0, a_col0, b_row0, b_col0;
+  int a_tap_row[PD_MAX_TAPS], a_tap_col[PD_MAX_TAPS];
+  int b_tap_row[PD_MAX_TAPS], b_tap_col[PD_MAX_TAPS];
+  int num_z; int z_b_row[PD_MAX_TAPS]; int64_t z_out_col;
+  int split_k;
+  // epilogue
+  void* out; int out_dtype; int64_t ldo;
+  int atomic;                 // fp32 atomicAdd into out (out_dtype must be PD_F32)
+  const void* bias; int bias_dtype;   // per-column bias (may be null)
+  int relu;                   // max(x, 0) after the bias
+  int pad_hp, pad_wp;         // > 0: rows are padded-NHWC pixels, border rows are written as 0
+  const void* relu_aux; int64_t ld_aux;  // != null: out = aux[m,n] > 0 ? acc : 0 (aux in out dtype)
+};
+
+int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream);
+int pd_gemm_launch_simt(const PdGemm& g, cudaStream_t stream);

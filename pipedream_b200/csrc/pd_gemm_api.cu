@@ -1,0 +1,179 @@
+// C-ABI entry points of the contraction family: plain GEMMs in the three
+// transposition forms a Linear layer needs, and the 3x3 / stride 1 / pad 1
+// convolution passes on padded-NHWC activations.  bf16 problems run on the
+// tcgen05 back end, fp32 problems on the CUDA-core back end; there is no other
+// path.
+#include "pd_gemm.cuh"
+
+namespace {
+
+int dispatch(const PdGemm& g, cudaStream_t s) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  if (g.dtype == PD_BF16) return pd_gemm_launch_tcgen05(g, s);
+  if (g.dtype == PD_F32) return pd_gemm_launch_simt(g, s);
+  pd_set_error("gemm: unsupported dtype %d", g.dtype);
+  return PD_ERR_INVALID;
+}
+
+void init(PdGemm& g) {
+  memset(&g, 0, sizeof(g));
+  g.num_taps = 1;
+  g.num_z = 1;
+  g.split_k = 1;
+}
+
+// Output mode for fp32 gradient buffers: store when the whole contraction is in
+// one CTA and the caller does not accumulate, atomic add otherwise (after
+// clearing the destination when the caller does not accumulate).
+int prepare_grad_out(PdGemm& g, int accumulate, int64_t rows, int64_t row_elems, cudaStream_t s) {
+  if (!accumulate && g.split_k == 1) { g.atomic = 0; return PD_OK; }
+  g.atomic = 1;
+  if (!accumulate) {
+    if (row_elems == g.ldo) {
+      PD_CUDA(cudaMemsetAsync(g.out, 0, (size_t)rows * g.ldo * sizeof(float), s));
+    } else {
+      PD_CUDA(cudaMemset2DAsync(g.out, (size_t)g.ldo * sizeof(float), 0, (size_t)row_elems * sizeof(float), (size_t)rows, s));
+    }
+  }
+  return PD_OK;
+}
+
+int auto_split(int64_t tiles, int kblocks) {
+  // aim for about two waves of CTAs over the SMs
+  int sms = pd_num_sms();
+  int64_t want = (2ll * sms + tiles - 1) / tiles;
+  if (want < 1) want = 1;
+  if (want > kblocks) want = kblocks;
+  if (want > 512) want = 512;
+  return (int)want;
+}
+
+}  // namespace
+
+// out[M,N] = a[M,K] . b[N,K]^T (+ bias[N]) (ReLU)            -- Linear forward
+PD_EXPORT int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+                         int out_dtype, int64_t ldo, int M, int N, int K, const void* bias,
+                         int bias_dtype, int relu, void* stream) {
+  PD_REQUIRE(a && b && out, "pd_gemm_nt: null pointer");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = a; g.a_rows = M; g.a_cols = K; g.lda = lda; g.a_major = 0;
+  g.b = b; g.b_rows = N; g.b_cols = K; g.ldb = ldb; g.b_major = 0;
+  g.M = M; g.N = N; g.K = K;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  g.bias = bias; g.bias_dtype = bias_dtype; g.relu = relu;
+  return dispatch(g, (cudaStream_t)stream);
+}
+
+// out[M,N] = a[M,K] . b[K,N]; optional mask: out = aux > 0 ? out : 0   -- Linear data gradient
+PD_EXPORT int pd_gemm_nn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+                         int out_dtype, int64_t ldo, int M, int N, int K, const void* relu_aux,
+                         int64_t ld_aux, void* stream) {
+  PD_REQUIRE(a && b && out, "pd_gemm_nn: null pointer");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = a; g.a_rows = M; g.a_cols = K; g.lda = lda; g.a_major = 0;
+  g.b = b; g.b_rows = K; g.b_cols = N; g.ldb = ldb; g.b_major = 1;
+  g.M = M; g.N = N; g.K = K;
+  g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
+  g.relu_aux = relu_aux; g.ld_aux = ld_aux;
+  return dispatch(g, (cudaStream_t)stream);
+}
+
+// out[M,N] (fp32) (+)= a[K,M]^T . b[K,N]                       -- Linear weight gradient
+PD_EXPORT int pd_gemm_tn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, float* out,
+                         int64_t ldo, int M, int N, int K, int accumulate, int split_k, void* stream) {
+  PD_REQUIRE(a && b && out, "pd_gemm_tn: null pointer");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = a; g.a_rows = K; g.a_cols = M; g.lda = lda; g.a_major = 1;
+  g.b = b; g.b_rows = K; g.b_cols = N; g.ldb = ldb; g.b_major = 1;
+  g.M = M; g.N = N; g.K = K;
+  g.out = out; g.out_dtype = PD_F32; g.ldo = ldo;
+  const int bn = dtype == PD_BF16 ? (N > 128 ? 256 : (N > 64 ? 128 : 64)) : 64;
+  const int bm = dtype == PD_BF16 ? 128 : 64;
+  const int64_t tiles = (int64_t)((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+  g.split_k = split_k > 0 ? split_k : auto_split(tiles, (K + 63) / 64);
+  int rc = prepare_grad_out(g, accumulate, M, N, (cudaStream_t)stream);
+  if (rc != PD_OK) return rc;
+  return dispatch(g, (cudaStream_t)stream);
+}
+
+namespace {
+void conv_taps(int Wp, int* shift) {
+  for (int r = 0; r < 3; ++r)
+    for (int s = 0; s < 3; ++s) shift[r * 3 + s] = (r - 1) * Wp + (s - 1);
+}
+}  // namespace
+
+// y_pad[P,Cout] = conv3x3(x_pad[P,Cin], w[Cout, 9*Cin]) (+bias) (ReLU); P = N*(H+2)*(W+2).
+// w holds the filter as [Cout][r][s][Cin] (the channels-last order of a [Cout,Cin,3,3] tensor).
+PD_EXPORT int pd_conv2d_fwd(int dtype, const void* x_pad, int N, int H, int W, int Cin, const void* w,
+                            int64_t ldw, int Cout, const void* bias, int bias_dtype, int relu,
+                            void* y_pad, void* stream) {
+  PD_REQUIRE(x_pad && w && y_pad && N > 0 && H > 0 && W > 0 && Cin > 0 && Cout > 0, "pd_conv2d_fwd: bad arguments");
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t P = (int64_t)N * Hp * Wp;
+  PD_REQUIRE(P < (1ll << 31), "pd_conv2d_fwd: too many pixels");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = x_pad; g.a_rows = P; g.a_cols = Cin; g.lda = Cin; g.a_major = 0;
+  g.b = w; g.b_rows = Cout; g.b_cols = 9ll * Cin; g.ldb = ldw; g.b_major = 0;
+  g.M = (int)P; g.N = Cout; g.K = Cin;
+  g.num_taps = 9;
+  int shift[9]; conv_taps(Wp, shift);
+  for (int t = 0; t < 9; ++t) { g.a_tap_row[t] = shift[t]; g.b_tap_col[t] = t * Cin; }
+  g.out = y_pad; g.out_dtype = dtype; g.ldo = Cout;
+  g.bias = bias; g.bias_dtype = bias_dtype; g.relu = relu;
+  g.pad_hp = Hp; g.pad_wp = Wp;
+  return dispatch(g, (cudaStream_t)stream);
+}
+
+// dx_pad[P,Cin] = sum_t dy_pad[p - shift_t, :] . w[:, t, :]; optional ReLU mask by x_pad (> 0).
+PD_EXPORT int pd_conv2d_dgrad(int dtype, const void* dy_pad, int N, int H, int W, int Cout, const void* w,
+                              int64_t ldw, int Cin, const void* relu_aux, void* dx_pad, void* stream) {
+  PD_REQUIRE(dy_pad && w && dx_pad && N > 0 && H > 0 && W > 0 && Cin > 0 && Cout > 0, "pd_conv2d_dgrad: bad arguments");
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t P = (int64_t)N * Hp * Wp;
+  PD_REQUIRE(P < (1ll << 31), "pd_conv2d_dgrad: too many pixels");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = dy_pad; g.a_rows = P; g.a_cols = Cout; g.lda = Cout; g.a_major = 0;
+  g.b = w; g.b_rows = Cout; g.b_cols = 9ll * Cin; g.ldb = ldw; g.b_major = 1;
+  g.M = (int)P; g.N = Cin; g.K = Cout;
+  g.num_taps = 9;
+  int shift[9]; conv_taps(Wp, shift);
+  for (int t = 0; t < 9; ++t) { g.a_tap_row[t] = -shift[t]; g.b_tap_col[t] = t * Cin; }
+  g.out = dx_pad; g.out_dtype = dtype; g.ldo = Cin;
+  g.pad_hp = Hp; g.pad_wp = Wp;
+  g.relu_aux = relu_aux; g.ld_aux = Cin;
+  return dispatch(g, (cudaStream_t)stream);
+}
+
+// dw[Cout, 9*Cin] (fp32, leading dim lddw) (+)= sum_p dy_pad[p, co] * x_pad[p + shift_t, ci]
+PD_EXPORT int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int H, int W,
+                              int Cin, int Cout, float* dw, int64_t lddw, int accumulate, int split_k,
+                              void* stream) {
+  PD_REQUIRE(x_pad && dy_pad && dw && N > 0 && H > 0 && W > 0 && Cin > 0 && Cout > 0, "pd_conv2d_wgrad: bad arguments");
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t P = (int64_t)N * Hp * Wp;
+  PD_REQUIRE(P < (1ll << 31), "pd_conv2d_wgrad: too many pixels");
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = dy_pad; g.a_rows = P; g.a_cols = Cout; g.lda = Cout; g.a_major = 1;
+  g.b = x_pad; g.b_rows = P; g.b_cols = Cin; g.ldb = Cin; g.b_major = 1;
+  g.M = Cout; g.N = Cin; g.K = (int)P;
+  g.num_z = 9;
+  int shift[9]; conv_taps(Wp, shift);
+  for (int t = 0; t < 9; ++t) g.z_b_row[t] = shift[t];
+  g.z_out_col = Cin;
+  g.out = dw; g.out_dtype = PD_F32; g.ldo = lddw;
+  const int bn = dtype == PD_BF16 ? (Cin > 128 ? 256 : (Cin > 64 ? 128 : 64)) : 64;
+  const int bm = dtype == PD_BF16 ? 128 : 64;
+  const int64_t tiles = 9ll * ((Cout + bm - 1) / bm) * ((Cin + bn - 1) / bn);
+  g.split_k = split_k > 0 ? split_k : auto_split(tiles, (int)((P + 63) / 64));
+  int rc = prepare_grad_out(g, accumulate, Cout, 9ll * Cin, (cudaStream_t)stream);
+  if (rc != PD_OK) return rc;
+  return dispatch(g, (cudaStream_t)stream);
+}

@@ -1,0 +1,143 @@
+// Criterion kernels: softmax cross-entropy (torch.nn.CrossEntropyLoss, mean
+// reduction) and label-smoothed NLL (runtime/translation/seq2seq/train/smoothing.py:23-34).
+// Row statistics are accumulated in fp32 whatever the logits dtype.
+#include "pd_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float block_max(float v, float* sm) {
+  v = pd_warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < (blockDim.x >> 5)) ? sm[threadIdx.x] : -INFINITY;
+  if (w == 0) { r = pd_warp_max(r); if (l == 0) sm[0] = r; }
+  __syncthreads();
+  r = sm[0];
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum(float v, float* sm) {
+  v = pd_warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < (blockDim.x >> 5)) ? sm[threadIdx.x] : 0.f;
+  if (w == 0) { r = pd_warp_sum(r); if (l == 0) sm[0] = r; }
+  __syncthreads();
+  r = sm[0];
+  __syncthreads();
+  return r;
+}
+
+// One block per row.  row_loss[r] = per-row loss term (already weighted),
+// lse[r] = log-sum-exp of the row (kept for the backward pass).
+//   smoothing == 0, ignore < 0  : plain cross-entropy, row_loss = lse - x[target]
+//   label smoothing             : conf*(lse - x[t]) + smoothing*(lse - mean(x)), 0 for rows whose
+//                                 target equals padding_idx
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+softmax_ce_rows_kernel(const T* __restrict__ logits, const int64_t* __restrict__ target, int C,
+                       float smoothing, int64_t padding_idx, float* __restrict__ row_loss,
+                       float* __restrict__ lse_out) {
+  __shared__ float sm[32];
+  const int64_t r = blockIdx.x;
+  const T* x = logits + r * C;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) mx = fmaxf(mx, pd_to_float(x[c]));
+  mx = block_max(mx, sm);
+  float se = 0.f, sx = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = pd_to_float(x[c]);
+    se += __expf(v - mx);
+    sx += v;
+  }
+  se = block_sum(se, sm);
+  sx = block_sum(sx, sm);
+  if (threadIdx.x == 0) {
+    const float lse = mx + logf(se);
+    lse_out[r] = lse;
+    const int64_t t = target[r];
+    float loss = 0.f;
+    if (t >= 0 && t < C && !(padding_idx >= 0 && t == padding_idx)) {
+      const float nll = lse - pd_to_float(x[t]);
+      const float smooth = lse - sx / (float)C;
+      loss = (1.f - smoothing) * nll + smoothing * smooth;
+    }
+    row_loss[r] = loss;
+  }
+}
+
+// Deterministic single-block reduction: loss = scale * sum(row_loss).
+__global__ void __launch_bounds__(1024)
+loss_reduce_kernel(const float* __restrict__ row_loss, int64_t rows, float scale, float* __restrict__ loss) {
+  __shared__ float sm[32];
+  float acc = 0.f;
+  for (int64_t i = threadIdx.x; i < rows; i += blockDim.x) acc += row_loss[i];
+  acc = block_sum(acc, sm);
+  if (threadIdx.x == 0) *loss = acc * scale;
+}
+
+// dlogits[r,c] = gscale * upstream * (conf*(p - onehot) + smoothing*(p - 1/C)), zero for padded rows.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+softmax_ce_bwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ target,
+                      const float* __restrict__ lse, int C, float smoothing, int64_t padding_idx,
+                      const float* __restrict__ upstream, float gscale, T* __restrict__ dlogits) {
+  const int64_t r = blockIdx.x;
+  const T* x = logits + r * C;
+  T* dx = dlogits + r * C;
+  const int64_t t = target[r];
+  const bool dead = !(t >= 0 && t < C) || (padding_idx >= 0 && t == padding_idx);
+  const float g = gscale * (upstream ? *upstream : 1.f);
+  const float l = lse[r];
+  const float conf = 1.f - smoothing, sm_c = smoothing / (float)C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float v = 0.f;
+    if (!dead) {
+      const float p = __expf(pd_to_float(x[c]) - l);
+      v = g * (p - (c == t ? conf : 0.f) - sm_c);
+    }
+    dx[c] = pd_from_float<T>(v);
+  }
+}
+
+}  // namespace
+
+PD_EXPORT int pd_softmax_ce_fwd(const void* logits, int dtype, const int64_t* target, int64_t rows,
+                                int C, float smoothing, int64_t padding_idx, float scale,
+                                float* row_loss, float* lse, float* loss, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(logits && target && row_loss && lse && loss && rows > 0 && C > 0,
+             "pd_softmax_ce_fwd: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_F32)
+    softmax_ce_rows_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  else if (dtype == PD_BF16)
+    softmax_ce_rows_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  else PD_REQUIRE(false, "pd_softmax_ce_fwd: bad dtype");
+  PD_LAUNCH_CHECK("softmax_ce_rows_kernel");
+  loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, rows, scale, loss);
+  PD_LAUNCH_CHECK("loss_reduce_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_softmax_ce_bwd(const void* logits, int dtype, const int64_t* target,
+                                const float* lse, int64_t rows, int C, float smoothing,
+                                int64_t padding_idx, const float* upstream, float gscale,
+                                void* dlogits, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(logits && target && lse && dlogits && rows > 0 && C > 0, "pd_softmax_ce_bwd: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_F32)
+    softmax_ce_bwd_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, lse, C, smoothing, padding_idx, upstream, gscale, (float*)dlogits);
+  else if (dtype == PD_BF16)
+    softmax_ce_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, lse, C, smoothing, padding_idx, upstream, gscale, (__nv_bfloat16*)dlogits);
+  else PD_REQUIRE(false, "pd_softmax_ce_bwd: bad dtype");
+  PD_LAUNCH_CHECK("softmax_ce_bwd_kernel");
+  return PD_OK;
+}

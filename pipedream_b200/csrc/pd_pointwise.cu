@@ -1,0 +1,514 @@
+// Bandwidth-bound kernels between the contractions of a stage: layout packing,
+// ReLU, 2x2 max-pool, dropout, bias-gradient reduction, elementwise add.
+//
+// Activation layout ("padded NHWC"): a logical [N,C,H,W] tensor is stored as
+// [N, H+2, W+2, C] with a one-pixel zero border, channels innermost.  A 3x3
+// stride-1 pad-1 convolution then reads tap (r,s) of pixel row p at row
+// p + (r-1)*(W+2) + (s-1) of the flattened [N*(H+2)*(W+2), C] matrix, which is
+// what lets the implicit-GEMM kernels fetch every tap with a plain 2-D TMA box.
+// Every kernel that writes such a buffer keeps the border at zero.
+#include "pd_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_cap(int64_t blocks, int per_sm = 8) {
+  int64_t cap = (int64_t)pd_num_sms() * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+// ---- pack: arbitrary-stride [N,C,H,W] -> padded NHWC ------------------------
+template <typename S, typename D>
+__global__ void __launch_bounds__(kThreads)
+pack_pnhwc_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                  int N, int C, int H, int W, D* __restrict__ dst) {
+  // One block handles one padded row (n, hp); a shared tile transposes [C][W]
+  // reads (W fastest for NCHW sources) into [W][C] writes.
+  __shared__ float tile[32][33];
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t rows = (int64_t)N * Hp;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int n = (int)(row / Hp), hp = (int)(row % Hp);
+    D* drow = dst + row * (int64_t)Wp * C;
+    if (hp == 0 || hp == Hp - 1) {
+      for (int64_t i = threadIdx.x; i < (int64_t)Wp * C; i += blockDim.x) drow[i] = pd_from_float<D>(0.f);
+      continue;
+    }
+    const int h = hp - 1;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) {
+      drow[i] = pd_from_float<D>(0.f);
+      drow[(int64_t)(Wp - 1) * C + i] = pd_from_float<D>(0.f);
+    }
+    const S* sbase = src + n * sN + h * sH;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int c0 = 0; c0 < C; c0 += 32) {
+      for (int w0 = 0; w0 < W; w0 += 32) {
+        __syncthreads();
+        if (sC == 1) {  // channels-last source: read along C
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            int w = w0 + ty + j, c = c0 + tx;
+            tile[tx][ty + j] = (w < W && c < C) ? pd_to_float(sbase[c * sC + w * sW]) : 0.f;
+          }
+        } else {        // read along W
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            int c = c0 + ty + j, w = w0 + tx;
+            tile[ty + j][tx] = (w < W && c < C) ? pd_to_float(sbase[c * sC + w * sW]) : 0.f;
+          }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          int w = w0 + ty + j, c = c0 + tx;
+          if (w < W && c < C) drow[(int64_t)(w + 1) * C + c] = pd_from_float<D>(tile[tx][ty + j]);
+        }
+      }
+    }
+  }
+}
+
+// ---- unpack: padded NHWC -> contiguous NCHW ---------------------------------
+template <typename S, typename D>
+__global__ void __launch_bounds__(kThreads)
+unpack_pnhwc_kernel(const S* __restrict__ src, int N, int C, int H, int W, D* __restrict__ dst) {
+  __shared__ float tile[32][33];
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t rows = (int64_t)N * H;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int n = (int)(row / H), h = (int)(row % H);
+    const S* srow = src + ((int64_t)(n * Hp + h + 1) * Wp + 1) * C;
+    D* dbase = dst + (int64_t)n * C * H * W + (int64_t)h * W;
+    for (int c0 = 0; c0 < C; c0 += 32) {
+      for (int w0 = 0; w0 < W; w0 += 32) {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          int w = w0 + ty + j, c = c0 + tx;
+          tile[ty + j][tx] = (w < W && c < C) ? pd_to_float(srow[(int64_t)w * C + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          int c = c0 + ty + j, w = w0 + tx;
+          if (w < W && c < C) dbase[(int64_t)c * H * W + w] = pd_from_float<D>(tile[tx][ty + j]);
+        }
+      }
+    }
+  }
+}
+
+// ---- im2col for the 3-channel first convolution -----------------------------
+// A[p, k] over padded pixel rows p (border rows all zero), k = (r*3+s)*C + c for
+// k < 9*C, zero up to Kpad.  Source is any-stride [N,C,H,W].
+template <typename S, typename D>
+__global__ void __launch_bounds__(kThreads)
+im2col3x3_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                 int N, int C, int H, int W, int Kpad, D* __restrict__ dst) {
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t total = (int64_t)N * Hp * Wp * Kpad;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int k = (int)(i % Kpad);
+    const int64_t p = i / Kpad;
+    const int wp = (int)(p % Wp);
+    const int hp = (int)((p / Wp) % Hp);
+    const int n = (int)(p / ((int64_t)Wp * Hp));
+    float v = 0.f;
+    if (k < 9 * C && hp >= 1 && hp <= H && wp >= 1 && wp <= W) {
+      const int t = k / C, c = k % C;
+      const int h = hp - 1 + t / 3 - 1, w = wp - 1 + t % 3 - 1;
+      if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(src[n * sN + c * sC + h * sH + w * sW]);
+    }
+    dst[i] = pd_from_float<D>(v);
+  }
+}
+
+// ---- ReLU --------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+relu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = pd_from_float<T>(fmaxf(pd_to_float(x[i]), 0.f));
+}
+
+__global__ void __launch_bounds__(kThreads)
+relu_fwd_bf16x8_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t n8) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 v = x[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    const __nv_bfloat162 z = __float2bfloat162_rn(0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __hmax2(h[j], z);
+    y[i] = v;
+  }
+}
+
+// dx = dy * (y > 0); y is the ReLU output.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+relu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    dx[i] = pd_to_float(y[i]) > 0.f ? dy[i] : pd_from_float<T>(0.f);
+}
+
+// Fused: dx = dy * (y > 0) (when y != null) and per-column partial sums of dx
+// over a [rows, C] matrix.  partial[block][C] is reduced by colsum_final_kernel.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+relu_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx,
+                       int64_t rows, int C, float* __restrict__ partial) {
+  extern __shared__ float sm[];  // [lanes][C]
+  const int lanes = kThreads / C > 0 ? kThreads / C : 1;   // C <= kThreads handled per column
+  const int cols_per_thread = (C + kThreads - 1) / kThreads;
+  // thread -> (lane, col); for C > kThreads each thread walks several columns
+  const int lane = (C <= kThreads) ? threadIdx.x / C : 0;
+  const int col0 = (C <= kThreads) ? threadIdx.x % C : threadIdx.x;
+  const bool active = (C <= kThreads) ? (lane < lanes) : true;
+  for (int cc = 0; cc < cols_per_thread; ++cc) {
+    const int col = col0 + cc * kThreads;
+    float acc = 0.f;
+    if (active && col < C) {
+      for (int64_t r = (int64_t)blockIdx.x * lanes + lane; r < rows; r += (int64_t)gridDim.x * lanes) {
+        const int64_t i = r * C + col;
+        float g = pd_to_float(dy[i]);
+        if (y != nullptr && !(pd_to_float(y[i]) > 0.f)) g = 0.f;
+        if (dx != nullptr) dx[i] = pd_from_float<T>(g);
+        acc += g;
+      }
+    }
+    if (C <= kThreads) {
+      if (active) sm[lane * C + col] = acc;
+      __syncthreads();
+      if (threadIdx.x < C) {
+        float s = 0.f;
+        for (int l = 0; l < lanes; ++l) s += sm[l * C + threadIdx.x];
+        partial[(int64_t)blockIdx.x * C + threadIdx.x] = s;
+      }
+      __syncthreads();
+    } else if (col < C) {
+      partial[(int64_t)blockIdx.x * C + col] = acc;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+colsum_final_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ out,
+                    int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(int64_t)b * C + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ---- 2x2 stride-2 max-pool on padded NHWC -----------------------------------
+// out_mode 0: padded NHWC output; 1: contiguous NCHW output.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, T* __restrict__ y,
+                    int out_mode) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  if (out_mode == 0) {
+    const int64_t total = (int64_t)N * Hop * Wop * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+      const int c = (int)(i % C);
+      const int64_t p = i / C;
+      const int wo = (int)(p % Wop), ho = (int)((p / Wop) % Hop), n = (int)(p / ((int64_t)Wop * Hop));
+      float m = 0.f;
+      if (ho >= 1 && ho <= Ho && wo >= 1 && wo <= Wo) {
+        const T* b = x + (((int64_t)n * Hp + (2 * (ho - 1) + 1)) * Wp + (2 * (wo - 1) + 1)) * C + c;
+        m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])),
+                  fmaxf(pd_to_float(b[(int64_t)Wp * C]), pd_to_float(b[(int64_t)Wp * C + C])));
+      }
+      y[i] = pd_from_float<T>(m);
+    }
+  } else {
+    const int64_t total = (int64_t)N * C * Ho * Wo;
+    // iterate in NHWC order for coalesced reads; small tensors only use this mode
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+      const int c = (int)(i % C);
+      const int64_t p = i / C;
+      const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
+      const T* b = x + (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C + c;
+      float m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])),
+                      fmaxf(pd_to_float(b[(int64_t)Wp * C]), pd_to_float(b[(int64_t)Wp * C + C])));
+      y[(((int64_t)n * C + c) * Ho + ho) * Wo + wo] = pd_from_float<T>(m);
+    }
+  }
+}
+
+// dx (padded NHWC, incl. zero border) from dy.  The gradient goes to the first
+// maximum of the window in (h,w) scan order, as ATen's max_pool2d does.
+// dy_mode 0: dy is padded NHWC; 1: dy is contiguous NCHW.
+// relu_mask != 0: x is a ReLU output and dx is additionally multiplied by (x > 0).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+maxpool2_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, int N, int C, int H, int W,
+                    T* __restrict__ dx, int dy_mode, int relu_mask) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const int64_t total = (int64_t)N * Hp * Wp * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const int64_t p = i / C;
+    const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), n = (int)(p / ((int64_t)Wp * Hp));
+    float g = 0.f;
+    const int h = hp - 1, w = wp - 1;
+    if (h >= 0 && w >= 0 && h < 2 * Ho && w < 2 * Wo) {
+      const int ho = h >> 1, wo = w >> 1;
+      const T* b = x + (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C + c;
+      const float v00 = pd_to_float(b[0]), v01 = pd_to_float(b[C]);
+      const float v10 = pd_to_float(b[(int64_t)Wp * C]), v11 = pd_to_float(b[(int64_t)Wp * C + C]);
+      int arg = 0; float m = v00;
+      if (v01 > m) { m = v01; arg = 1; }
+      if (v10 > m) { m = v10; arg = 2; }
+      if (v11 > m) { m = v11; arg = 3; }
+      const int me = ((h & 1) << 1) | (w & 1);
+      if (me == arg && !(relu_mask && !(m > 0.f))) {
+        g = dy_mode == 0
+                ? pd_to_float(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C + c])
+                : pd_to_float(dy[(((int64_t)n * C + c) * Ho + ho) * Wo + wo]);
+      }
+    }
+    dx[i] = pd_from_float<T>(g);
+  }
+}
+
+// ---- dropout (counter-based RNG; mask kept as bytes) -------------------------
+__device__ __forceinline__ uint32_t mix32(uint64_t k) {
+  // splitmix64 finaliser; one draw per element index and (seed, offset) pair
+  k += 0x9E3779B97F4A7C15ull;
+  k = (k ^ (k >> 30)) * 0xBF58476D1CE4E5B9ull;
+  k = (k ^ (k >> 27)) * 0x94D049BB133111EBull;
+  k = k ^ (k >> 31);
+  return (uint32_t)(k >> 32);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+dropout_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ mask, int64_t n,
+                   float p, uint64_t seed, uint64_t offset) {
+  const float scale = 1.f / (1.f - p);
+  const uint32_t thresh = (uint32_t)((double)p * 4294967296.0 > 4294967295.0 ? 4294967295.0
+                                                                            : (double)p * 4294967296.0);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t r = mix32((seed * 0x100000001B3ull) ^ (offset + (uint64_t)i));
+    const uint8_t keep = r >= thresh;
+    mask[i] = keep;
+    y[i] = keep ? pd_from_float<T>(pd_to_float(x[i]) * scale) : pd_from_float<T>(0.f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+dropout_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ mask, T* __restrict__ dx,
+                   int64_t n, float p) {
+  const float scale = 1.f / (1.f - p);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    dx[i] = mask[i] ? pd_from_float<T>(pd_to_float(dy[i]) * scale) : pd_from_float<T>(0.f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = pd_from_float<T>(pd_to_float(a[i]) + pd_to_float(b[i]));
+}
+
+}  // namespace
+
+#define PD_DISPATCH_T(dtype, ...)                                   \
+  if (dtype == PD_F32) { using T = float; __VA_ARGS__ }             \
+  else if (dtype == PD_BF16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+  else { pd_set_error("bad dtype %d", dtype); return PD_ERR_INVALID; }
+
+PD_EXPORT int pd_pack_pnhwc(const void* src, int src_dtype, int64_t sN, int64_t sC, int64_t sH,
+                            int64_t sW, int N, int C, int H, int W, void* dst, int dst_dtype,
+                            void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(src && dst && N > 0 && C > 0 && H > 0 && W > 0, "pd_pack_pnhwc: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  int grid = grid_cap((int64_t)N * (H + 2), 16);
+  if (src_dtype == PD_F32 && dst_dtype == PD_F32)
+    pack_pnhwc_kernel<float, float><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, (float*)dst);
+  else if (src_dtype == PD_F32 && dst_dtype == PD_BF16)
+    pack_pnhwc_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, (__nv_bfloat16*)dst);
+  else if (src_dtype == PD_BF16 && dst_dtype == PD_BF16)
+    pack_pnhwc_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H, W, (__nv_bfloat16*)dst);
+  else if (src_dtype == PD_BF16 && dst_dtype == PD_F32)
+    pack_pnhwc_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H, W, (float*)dst);
+  else PD_REQUIRE(false, "pd_pack_pnhwc: bad dtype");
+  PD_LAUNCH_CHECK("pack_pnhwc_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_unpack_pnhwc(const void* src, int src_dtype, int N, int C, int H, int W, void* dst,
+                              int dst_dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(src && dst && N > 0 && C > 0 && H > 0 && W > 0, "pd_unpack_pnhwc: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  int grid = grid_cap((int64_t)N * H, 16);
+  if (src_dtype == PD_F32 && dst_dtype == PD_F32)
+    unpack_pnhwc_kernel<float, float><<<grid, kThreads, 0, s>>>((const float*)src, N, C, H, W, (float*)dst);
+  else if (src_dtype == PD_BF16 && dst_dtype == PD_BF16)
+    unpack_pnhwc_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)src, N, C, H, W, (__nv_bfloat16*)dst);
+  else if (src_dtype == PD_BF16 && dst_dtype == PD_F32)
+    unpack_pnhwc_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)src, N, C, H, W, (float*)dst);
+  else if (src_dtype == PD_F32 && dst_dtype == PD_BF16)
+    unpack_pnhwc_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const float*)src, N, C, H, W, (__nv_bfloat16*)dst);
+  else PD_REQUIRE(false, "pd_unpack_pnhwc: bad dtype");
+  PD_LAUNCH_CHECK("unpack_pnhwc_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t sC, int64_t sH,
+                           int64_t sW, int N, int C, int H, int W, int Kpad, void* dst,
+                           int dst_dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(src && dst && N > 0 && C > 0 && H > 0 && W > 0 && Kpad >= 9 * C, "pd_im2col3x3: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  int64_t total = (int64_t)N * (H + 2) * (W + 2) * Kpad;
+  int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  if (src_dtype == PD_F32 && dst_dtype == PD_F32)
+    im2col3x3_kernel<float, float><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (float*)dst);
+  else if (src_dtype == PD_F32 && dst_dtype == PD_BF16)
+    im2col3x3_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (__nv_bfloat16*)dst);
+  else if (src_dtype == PD_BF16 && dst_dtype == PD_BF16)
+    im2col3x3_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (__nv_bfloat16*)dst);
+  else PD_REQUIRE(false, "pd_im2col3x3: bad dtype combination");
+  PD_LAUNCH_CHECK("im2col3x3_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_relu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && y && n >= 0, "pd_relu_fwd: bad arguments");
+  if (n == 0) return PD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_BF16 && (n % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
+    int64_t n8 = n / 8;
+    relu_fwd_bf16x8_kernel<<<grid_cap((n8 + kThreads - 1) / kThreads), kThreads, 0, s>>>((const uint4*)x, (uint4*)y, n8);
+  } else {
+    PD_DISPATCH_T(dtype, relu_fwd_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)x, (T*)y, n);)
+  }
+  PD_LAUNCH_CHECK("relu_fwd_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_relu_bwd(const void* dy, const void* y, void* dx, int64_t n, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(dy && y && dx && n >= 0, "pd_relu_bwd: bad arguments");
+  if (n == 0) return PD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  PD_DISPATCH_T(dtype, relu_bwd_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)dy, (const T*)y, (T*)dx, n);)
+  PD_LAUNCH_CHECK("relu_bwd_kernel");
+  return PD_OK;
+}
+
+// workspace: at least pd_colsum_workspace_bytes(C) bytes of device memory.
+PD_EXPORT int64_t pd_colsum_workspace_bytes(int C) {
+  return (int64_t)pd_num_sms() * 4 * (int64_t)C * sizeof(float);
+}
+
+PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_t rows, int C,
+                                 int dtype, float* colsum, int accumulate, void* workspace,
+                                 int64_t workspace_bytes, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(dy && colsum && workspace && rows >= 0 && C > 0, "pd_relu_bwd_colsum: bad arguments");
+  PD_REQUIRE(C <= kThreads ? (kThreads / C) * C * (int)sizeof(float) <= 48 * 1024 : true, "pd_relu_bwd_colsum: C too large");
+  PD_REQUIRE(workspace_bytes >= pd_colsum_workspace_bytes(C), "pd_relu_bwd_colsum: workspace too small");
+  cudaStream_t s = (cudaStream_t)stream;
+  int lanes = C <= kThreads ? kThreads / C : 1;
+  int64_t want = (rows + lanes - 1) / lanes;
+  int grid = grid_cap(want, 4);
+  size_t smem = C <= kThreads ? (size_t)lanes * C * sizeof(float) : 0;
+  PD_DISPATCH_T(dtype, relu_bwd_colsum_kernel<T><<<grid, kThreads, smem, s>>>((const T*)dy, (const T*)y, (T*)dx, rows, C, (float*)workspace);)
+  PD_LAUNCH_CHECK("relu_bwd_colsum_kernel");
+  colsum_final_kernel<<<(C + kThreads - 1) / kThreads, kThreads, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
+  PD_LAUNCH_CHECK("colsum_final_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y, int out_mode,
+                              int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && y && N > 0 && C > 0 && H >= 2 && W >= 2, "pd_maxpool2_fwd: bad arguments");
+  PD_REQUIRE(out_mode == 0 || out_mode == 1, "pd_maxpool2_fwd: bad out_mode");
+  cudaStream_t s = (cudaStream_t)stream;
+  int64_t total = out_mode == 0 ? (int64_t)N * (H / 2 + 2) * (W / 2 + 2) * C : (int64_t)N * C * (H / 2) * (W / 2);
+  int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  PD_DISPATCH_T(dtype, maxpool2_fwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, N, C, H, W, (T*)y, out_mode);)
+  PD_LAUNCH_CHECK("maxpool2_fwd_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H, int W, void* dx,
+                              int dy_mode, int relu_mask, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && dy && dx && N > 0 && C > 0 && H >= 2 && W >= 2, "pd_maxpool2_bwd: bad arguments");
+  PD_REQUIRE(dy_mode == 0 || dy_mode == 1, "pd_maxpool2_bwd: bad dy_mode");
+  cudaStream_t s = (cudaStream_t)stream;
+  int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
+  int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  PD_DISPATCH_T(dtype, maxpool2_bwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)dy, N, C, H, W, (T*)dx, dy_mode, relu_mask);)
+  PD_LAUNCH_CHECK("maxpool2_bwd_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_dropout_fwd(const void* x, void* y, uint8_t* mask, int64_t n, float p,
+                             uint64_t seed, uint64_t offset, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && y && mask && n >= 0 && p >= 0.f && p < 1.f, "pd_dropout_fwd: bad arguments");
+  if (n == 0) return PD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  PD_DISPATCH_T(dtype, dropout_fwd_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)x, (T*)y, mask, n, p, seed, offset);)
+  PD_LAUNCH_CHECK("dropout_fwd_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, int64_t n, float p,
+                             int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(dy && dx && mask && n >= 0 && p >= 0.f && p < 1.f, "pd_dropout_bwd: bad arguments");
+  if (n == 0) return PD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  PD_DISPATCH_T(dtype, dropout_bwd_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)dy, mask, (T*)dx, n, p);)
+  PD_LAUNCH_CHECK("dropout_bwd_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int pd_add(const void* a, const void* b, void* y, int64_t n, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(a && b && y && n >= 0, "pd_add: bad arguments");
+  if (n == 0) return PD_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  PD_DISPATCH_T(dtype, add_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)y, n);)
+  PD_LAUNCH_CHECK("add_kernel");
+  return PD_OK;
+}

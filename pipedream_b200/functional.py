@@ -1,0 +1,327 @@
+"""Tensor-level wrappers over the C-ABI kernels (no autograd here).
+
+Every function takes CUDA tensors, passes raw device pointers and the current
+CUDA stream to libpipedream_b200.so, and returns / fills torch tensors that
+only serve as device-memory handles.  Nothing in this module computes with
+torch operators.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import PD_BF16, PD_F32, call
+
+_DT = {torch.float32: PD_F32, torch.bfloat16: PD_BF16}
+
+
+def dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise _lib.PipedreamB200Error("unsupported dtype %s (fp32 and bf16 only)" % t.dtype)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.PipedreamB200Error("pipedream_b200 kernels need CUDA tensors (no CPU path)")
+
+
+# --------------------------------------------------------------------------- #
+# padded-NHWC layout helpers
+# --------------------------------------------------------------------------- #
+def padded_shape(N, C, H, W):
+    return (N, H + 2, W + 2, C)
+
+
+def nchw_view(pad, N, C, H, W):
+    """Logical [N,C,H,W] view of the interior of a padded-NHWC buffer."""
+    Hp, Wp = H + 2, W + 2
+    return pad.as_strided((N, C, H, W), (Hp * Wp * C, 1, Wp * C, C), pad.storage_offset() + (Wp + 1) * C)
+
+
+def padded_of(view):
+    """If `view` is a logical-NCHW view of a padded-NHWC buffer, return that buffer, else None."""
+    if view.dim() != 4:
+        return None
+    N, C, H, W = view.shape
+    Hp, Wp = H + 2, W + 2
+    if view.stride() != (Hp * Wp * C, 1, Wp * C, C):
+        return None
+    off = view.storage_offset() - (Wp + 1) * C
+    if off < 0:
+        return None
+    nbytes = view.untyped_storage().nbytes() // view.element_size()
+    if off + N * Hp * Wp * C > nbytes:
+        return None
+    return view.as_strided((N, Hp, Wp, C), (Hp * Wp * C, Wp * C, C, 1), off)
+
+
+def pack_pnhwc(x, dtype=None):
+    """Any-stride [N,C,H,W] tensor -> new padded-NHWC buffer (zero border)."""
+    _cuda(x)
+    N, C, H, W = x.shape
+    dtype = dtype or x.dtype
+    out = torch.empty(padded_shape(N, C, H, W), dtype=dtype, device=x.device)
+    sN, sC, sH, sW = x.stride()
+    call("pd_pack_pnhwc", _p(x), dt(x), sN, sC, sH, sW, N, C, H, W, _p(out), _DT[dtype], _stream())
+    return out
+
+
+def as_padded(x, dtype=None):
+    """Padded-NHWC buffer for a logical NCHW tensor: zero-copy when it already is one."""
+    pad = padded_of(x)
+    if pad is not None and (dtype is None or dtype == x.dtype):
+        return pad
+    return pack_pnhwc(x, dtype)
+
+
+def unpack_pnhwc(pad, dtype=None):
+    """Padded-NHWC buffer -> contiguous NCHW tensor."""
+    _cuda(pad)
+    N, Hp, Wp, C = pad.shape
+    H, W = Hp - 2, Wp - 2
+    dtype = dtype or pad.dtype
+    out = torch.empty((N, C, H, W), dtype=dtype, device=pad.device)
+    call("pd_unpack_pnhwc", _p(pad), dt(pad), N, C, H, W, _p(out), _DT[dtype], _stream())
+    return out
+
+
+def im2col3x3(x, kpad, dtype):
+    """[N,C,H,W] any-stride -> [N*(H+2)*(W+2), kpad] patch matrix over padded pixel rows."""
+    _cuda(x)
+    N, C, H, W = x.shape
+    out = torch.empty((N * (H + 2) * (W + 2), kpad), dtype=dtype, device=x.device)
+    sN, sC, sH, sW = x.stride()
+    call("pd_im2col3x3", _p(x), dt(x), sN, sC, sH, sW, N, C, H, W, kpad, _p(out), _DT[dtype], _stream())
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# pointwise
+# --------------------------------------------------------------------------- #
+def relu_(x):
+    """In-place ReLU over a dense buffer (padded buffers stay valid: relu(0) = 0)."""
+    _cuda(x)
+    call("pd_relu_fwd", _p(x), _p(x), x.numel(), dt(x), _stream())
+    return x
+
+
+def relu(x):
+    y = torch.empty_like(x)
+    call("pd_relu_fwd", _p(x), _p(y), x.numel(), dt(x), _stream())
+    return y
+
+
+def relu_bwd(dy, y, out=None):
+    out = torch.empty_like(dy) if out is None else out
+    call("pd_relu_bwd", _p(dy), _p(y), _p(out), dy.numel(), dt(dy), _stream())
+    return out
+
+
+_WS = {}
+
+
+def _workspace(device, nbytes):
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WS[key] = ws
+    return ws
+
+
+def relu_bwd_colsum(dy, y, dx, colsum, accumulate):
+    """dx = dy * (y > 0) (y, dx may be None) and colsum[C] (+)= column sums of the masked dy.
+
+    dy is a dense [rows, C] matrix (any leading shape, C innermost)."""
+    _cuda(dy, colsum)
+    C = dy.shape[-1]
+    rows = dy.numel() // C
+    nbytes = _lib.load().pd_colsum_workspace_bytes(C)
+    ws = _workspace(dy.device, nbytes)
+    call("pd_relu_bwd_colsum", _p(dy), _p(y), _p(dx), rows, C, dt(dy), _p(colsum), int(accumulate), _p(ws),
+         ws.numel(), _stream())
+
+
+def maxpool2_fwd(x_pad, to_nchw):
+    N, Hp, Wp, C = x_pad.shape
+    H, W = Hp - 2, Wp - 2
+    if to_nchw:
+        y = torch.empty((N, C, H // 2, W // 2), dtype=x_pad.dtype, device=x_pad.device)
+    else:
+        y = torch.empty(padded_shape(N, C, H // 2, W // 2), dtype=x_pad.dtype, device=x_pad.device)
+    call("pd_maxpool2_fwd", _p(x_pad), N, C, H, W, _p(y), 1 if to_nchw else 0, dt(x_pad), _stream())
+    return y
+
+
+def maxpool2_bwd(x_pad, dy, dy_is_nchw, relu_mask):
+    N, Hp, Wp, C = x_pad.shape
+    dx = torch.empty_like(x_pad)
+    call("pd_maxpool2_bwd", _p(x_pad), _p(dy), N, C, Hp - 2, Wp - 2, _p(dx), 1 if dy_is_nchw else 0,
+         int(relu_mask), dt(x_pad), _stream())
+    return dx
+
+
+def dropout_fwd(x, p, seed, offset):
+    y = torch.empty_like(x)
+    mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    call("pd_dropout_fwd", _p(x), _p(y), _p(mask), x.numel(), float(p), int(seed), int(offset), dt(x), _stream())
+    return y, mask
+
+
+def dropout_bwd(dy, mask, p):
+    dx = torch.empty_like(dy)
+    call("pd_dropout_bwd", _p(dy), _p(mask), _p(dx), dy.numel(), float(p), dt(dy), _stream())
+    return dx
+
+
+def add(a, b):
+    y = torch.empty_like(a)
+    call("pd_add", _p(a), _p(b), _p(y), a.numel(), dt(a), _stream())
+    return y
+
+
+def convert(src, dtype, out=None):
+    out = torch.empty(src.shape, dtype=dtype, device=src.device) if out is None else out
+    call("pd_convert", _p(out), _DT[out.dtype], _p(src), dt(src), src.numel(), _stream())
+    return out
+
+
+def scale_(x, s):
+    call("pd_scale", _p(x), x.numel(), dt(x), float(s), _stream())
+    return x
+
+
+# --------------------------------------------------------------------------- #
+# contractions
+# --------------------------------------------------------------------------- #
+def gemm_nt(a, b, bias=None, relu=False, out_dtype=None):
+    """a[M,K] . b[N,K]^T (+bias) (ReLU)."""
+    _cuda(a, b)
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    call("pd_gemm_nt", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
+         _p(bias), dt(bias) if bias is not None else 0, int(relu), _stream())
+    return out
+
+
+def gemm_nn(a, b, relu_aux=None):
+    """a[M,K] . b[K,N], optionally masked by (relu_aux > 0)."""
+    _cuda(a, b)
+    M, K = a.shape
+    N = b.shape[1]
+    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    call("pd_gemm_nn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
+         _p(relu_aux), relu_aux.stride(0) if relu_aux is not None else 0, _stream())
+    return out
+
+
+def gemm_tn(a, b, out, accumulate=False, split_k=0):
+    """out[M,N] (fp32, any leading dim) (+)= a[K,M]^T . b[K,N]."""
+    _cuda(a, b, out)
+    K, M = a.shape
+    N = b.shape[1]
+    assert out.dtype == torch.float32
+    call("pd_gemm_tn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), M, N, K,
+         int(accumulate), int(split_k), _stream())
+    return out
+
+
+def conv2d_fwd(x_pad, w, ldw, cout, bias, relu):
+    """3x3/s1/p1 convolution on padded NHWC.  w: [Cout][r][s][Cin] storage with leading dim ldw."""
+    N, Hp, Wp, Cin = x_pad.shape
+    y = torch.empty((N, Hp, Wp, cout), dtype=x_pad.dtype, device=x_pad.device)
+    call("pd_conv2d_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, Cin, _p(w), ldw, cout, _p(bias),
+         dt(bias) if bias is not None else 0, int(relu), _p(y), _stream())
+    return y
+
+
+def conv2d_dgrad(dy_pad, w, ldw, cin, relu_aux=None):
+    N, Hp, Wp, Cout = dy_pad.shape
+    dx = torch.empty((N, Hp, Wp, cin), dtype=dy_pad.dtype, device=dy_pad.device)
+    call("pd_conv2d_dgrad", dt(dy_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cout, _p(w), ldw, cin, _p(relu_aux), _p(dx),
+         _stream())
+    return dx
+
+
+def conv2d_wgrad(x_pad, dy_pad, dw, lddw, accumulate=False, split_k=0):
+    N, Hp, Wp, Cin = x_pad.shape
+    Cout = dy_pad.shape[3]
+    assert dw.dtype == torch.float32
+    call("pd_conv2d_wgrad", dt(x_pad), _p(x_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cin, Cout, _p(dw), lddw,
+         int(accumulate), int(split_k), _stream())
+    return dw
+
+
+def gemm_poll_error():
+    code = ctypes.c_int(0)
+    call("pd_gemm_poll_error", ctypes.byref(code))
+    return code.value
+
+
+# --------------------------------------------------------------------------- #
+# criteria and sequence utilities
+# --------------------------------------------------------------------------- #
+def softmax_ce_fwd(logits, target, smoothing, padding_idx, scale):
+    """Returns (loss scalar fp32 tensor, lse[rows], row_loss[rows])."""
+    _cuda(logits, target)
+    rows, C = logits.shape
+    row_loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss = torch.empty((), dtype=torch.float32, device=logits.device)
+    call("pd_softmax_ce_fwd", _p(logits), dt(logits), _p(target), rows, C, float(smoothing), int(padding_idx),
+         float(scale), _p(row_loss), _p(lse), _p(loss), _stream())
+    return loss, lse, row_loss
+
+
+def softmax_ce_bwd(logits, target, lse, smoothing, padding_idx, upstream, gscale):
+    rows, C = logits.shape
+    dlogits = torch.empty_like(logits)
+    call("pd_softmax_ce_bwd", _p(logits), dt(logits), _p(target), _p(lse), rows, C, float(smoothing),
+         int(padding_idx), _p(upstream), float(gscale), _p(dlogits), _stream())
+    return dlogits
+
+
+def revert_varlen(x, lengths):
+    """x: [T,B,...] contiguous; lengths: int64 [B] on the same device."""
+    _cuda(x, lengths)
+    x = x if x.is_contiguous() else x.contiguous()
+    T, B = x.shape[0], x.shape[1]
+    out = torch.empty_like(x)
+    fbytes = (x.numel() // (T * B)) * x.element_size()
+    call("pd_revert_varlen", _p(x), _p(out), _p(lengths), T, B, fbytes, _stream())
+    return out
+
+
+def length_mask(lengths, T, dtype):
+    _cuda(lengths)
+    B = lengths.shape[0]
+    out = torch.empty((T, B), dtype=dtype, device=lengths.device)
+    code = 2 if dtype == torch.uint8 else _DT[dtype]
+    call("pd_length_mask", _p(lengths), T, B, _p(out), code, _stream())
+    return out
+
+
+def embedding_fwd(ids, table):
+    _cuda(ids, table)
+    vocab, D = table.shape
+    out = torch.empty(tuple(ids.shape) + (D,), dtype=table.dtype, device=table.device)
+    call("pd_embedding_fwd", _p(ids), _p(table), ids.numel(), D, vocab, _p(out), dt(table), _stream())
+    return out
+
+
+def embedding_bwd(ids, dy, dtable, padding_idx):
+    vocab, D = dtable.shape
+    call("pd_embedding_bwd", _p(ids), _p(dy), ids.numel(), D, vocab, int(padding_idx), _p(dtable), dt(dy), _stream())
+    return dtable
