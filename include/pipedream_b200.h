@@ -1,0 +1,161 @@
+/*
+ * pipedream_b200 - C ABI of libpipedream_b200.so (CUDA, sm_100a only).
+ *
+ * The reference (msr-fiddle/pipedream, `pipedream` branch) reaches its GPU work through
+ * PyTorch operators from Python; the only native code it ships is the pack_utils
+ * extension.  This header declares what a drop-in for the training-step hot path binds
+ * instead.  Each entry point names the reference call site it replaces (file:line inside
+ * the reference repository).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless stated
+ *   - the caller owns all memory; no entry point allocates or frees device memory
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); no hidden syncs
+ *     except where stated
+ *   - return value: 0 = ok, <0 = error (-1 invalid argument / unsupported shape,
+ *     -2 CUDA error, -3 device is not sm_100, -4 bounded device wait ran out,
+ *     -5 wrong state); pd_last_error() gives the thread-local message
+ *   - dtype codes: 0 = fp32, 1 = bf16 (2 = uint8 where stated)
+ *   - "padded NHWC": a logical [N,C,H,W] activation stored as [N, H+2, W+2, C] with a
+ *     zero one-pixel border, C innermost; P = N*(H+2)*(W+2) pixel rows
+ */
+#ifndef PIPEDREAM_B200_H_
+#define PIPEDREAM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- library ------------------------------------------------------------------------- */
+const char* pd_last_error(void);
+int pd_abi_version(void);
+int pd_device_ok(void);   /* 0 when the current device is sm_100 */
+int pd_sm_count(void);
+
+/* ---- optimizer over the weight-version ring -------------------------------------------
+ * Replaces runtime/optimizer.py:122-164 (`step`: base optimizer step + push of a cloned
+ * state_dict), runtime/optimizer.py:87-116 (`set_params` copies) and the per-tensor
+ * torch.optim.SGD / Adam loops behind runtime/sgd.py:12-24 and runtime/adam.py:12-22.
+ * arena: num_slots x slot_stride elements of w_dtype; the kernel reads slot read_slot
+ * (or `master`, fp32, required when w_dtype is bf16) and writes slot write_slot, `master`
+ * and the state in place.  grad is fp32 and is multiplied by grad_scale first.            */
+int pd_opt_sgd_multi_tensor(void* arena, int64_t slot_stride, int read_slot, int write_slot,
+                            int w_dtype, float* master, const float* grad, float* momentum_buf,
+                            int64_t n, float lr, float momentum, float dampening,
+                            float weight_decay, int nesterov, int first_step, float grad_scale,
+                            void* stream);
+int pd_opt_adam_multi_tensor(void* arena, int64_t slot_stride, int read_slot, int write_slot,
+                             int w_dtype, float* master, const float* grad, float* exp_avg,
+                             float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2,
+                             float eps, float weight_decay, int64_t step, float grad_scale,
+                             void* stream);
+/* x *= s; replaces `p.grad.div_(update_interval)` (runtime/optimizer.py:147-149) and the
+ * gradient averaging DistributedDataParallel does for a replicated stage
+ * (runtime/runtime.py:258-262).                                                            */
+int pd_scale(void* x, int64_t n, int dtype, float s, void* stream);
+/* dst = (dst_dtype) src; replaces apex master<->model copies (runtime/optimizer.py:137-155). */
+int pd_convert(void* dst, int dst_dtype, const void* src, int src_dtype, int64_t n, void* stream);
+
+/* ---- layout ----------------------------------------------------------------------------
+ * The stage modules keep logical NCHW tensors (runtime/image_classification/models/vgg16/
+ * gpus=8/stage0.py:47-71); these move data into and out of padded NHWC.                    */
+int pd_pack_pnhwc(const void* src, int src_dtype, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                  int N, int C, int H, int W, void* dst, int dst_dtype, void* stream);
+int pd_unpack_pnhwc(const void* src, int src_dtype, int N, int C, int H, int W, void* dst,
+                    int dst_dtype, void* stream);
+/* 3x3 patch matrix [P, Kpad] (k = (r*3+s)*C + c) of a small-C input: first VGG convolution. */
+int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                 int N, int C, int H, int W, int Kpad, void* dst, int dst_dtype, void* stream);
+
+/* ---- pointwise -------------------------------------------------------------------------
+ * torch.nn.ReLU / MaxPool2d(2,2) / Dropout of the stage files (vgg16/gpus=8/stage0.py:11-31,
+ * stage1.py:10-25), forward and backward.                                                  */
+int pd_relu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream);
+int pd_relu_bwd(const void* dy, const void* y, void* dx, int64_t n, int dtype, void* stream);
+int64_t pd_colsum_workspace_bytes(int C);
+/* dx = dy * (y > 0) (y, dx may be NULL) and colsum[C] (+)= column sums: ReLU backward fused
+ * with the bias gradient of the Conv2d / Linear in front of it.  workspace: scratch of at
+ * least pd_colsum_workspace_bytes(C) bytes.                                                */
+int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_t rows, int C, int dtype,
+                       float* colsum, int accumulate, void* workspace, int64_t workspace_bytes,
+                       void* stream);
+/* out_mode / dy_mode: 0 = padded NHWC, 1 = contiguous NCHW.                                */
+int pd_maxpool2_fwd(const void* x_pad, int N, int C, int H, int W, void* y, int out_mode,
+                    int dtype, void* stream);
+int pd_maxpool2_bwd(const void* x_pad, const void* dy, int N, int C, int H, int W, void* dx_pad,
+                    int dy_mode, int relu_mask, int dtype, void* stream);
+int pd_dropout_fwd(const void* x, void* y, uint8_t* mask, int64_t n, float p, uint64_t seed,
+                   uint64_t offset, int dtype, void* stream);
+int pd_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, int64_t n, float p, int dtype,
+                   void* stream);
+/* y = a + b: residual adds of the ResNet-50 / GNMT stage files.                             */
+int pd_add(const void* a, const void* b, void* y, int64_t n, int dtype, void* stream);
+
+/* ---- criteria --------------------------------------------------------------------------
+ * torch.nn.CrossEntropyLoss (runtime/image_classification/main_with_runtime.py:126) and
+ * LabelSmoothing (runtime/translation/seq2seq/train/smoothing.py:23-34).  smoothing = 0 and
+ * padding_idx < 0 give plain cross-entropy.  loss = scale * sum(row_loss).  row_loss[rows]
+ * and lse[rows] are caller-provided scratch / saved statistics.                             */
+int pd_softmax_ce_fwd(const void* logits, int dtype, const int64_t* target, int64_t rows, int C,
+                      float smoothing, int64_t padding_idx, float scale, float* row_loss,
+                      float* lse, float* loss, void* stream);
+int pd_softmax_ce_bwd(const void* logits, int dtype, const int64_t* target, const float* lse,
+                      int64_t rows, int C, float smoothing, int64_t padding_idx,
+                      const float* upstream, float gscale, void* dlogits, void* stream);
+
+/* ---- sequence utilities ----------------------------------------------------------------
+ * pd_revert_varlen replaces revert_varlen_tensor (runtime/translation/seq2seq/csrc/
+ * pack_utils_kernel.cu:24-63); pd_length_mask replaces set_mask_cpp (csrc/pack_utils.cpp:
+ * 13-31).  `lengths` is an int64 DEVICE vector here (the reference takes a CPU tensor and
+ * rebuilds and uploads an offset table on every call).  mask_dtype 2 = uint8.               */
+int pd_revert_varlen(const void* in, void* out, const int64_t* lengths, int T, int B,
+                     int64_t feature_bytes, void* stream);
+int pd_length_mask(const int64_t* lengths, int T, int B, void* mask, int mask_dtype, void* stream);
+/* torch.nn.Embedding(padding_idx=0) of runtime/translation/models/gnmt_large/gpus=4/stage0.py:10 */
+int pd_embedding_fwd(const int64_t* ids, const void* table, int64_t n, int D, int64_t vocab,
+                     void* out, int dtype, void* stream);
+int pd_embedding_bwd(const int64_t* ids, const void* dy, int64_t n, int D, int64_t vocab,
+                     int64_t padding_idx, float* dtable, int dtype, void* stream);
+
+/* ---- contractions ----------------------------------------------------------------------
+ * bf16 problems run on tcgen05 tensor cores (TMA-fed, fp32 accumulation in tensor memory),
+ * fp32 problems on CUDA cores.  Leading dimensions are in elements; for bf16 they must be
+ * multiples of 8 and base pointers 16-byte aligned.
+ *
+ * pd_gemm_nt : out[M,N] = a[M,K] . b[N,K]^T (+bias[N]) (ReLU)  - torch.nn.Linear forward
+ *              (vgg16/gpus=16/stage1.py:10-16).  pad_hp/pad_wp > 0: rows are padded-NHWC
+ *              pixels and border rows are written as zero.
+ * pd_gemm_nn : out[M,N] = a[M,K] . b[K,N], optionally masked by (relu_aux[M,N] > 0)
+ *              - Linear data gradient.
+ * pd_gemm_tn : out[M,N] (fp32) (+)= a[K,M]^T . b[K,N]           - Linear weight gradient.
+ *              split_k = 0 picks a split; partial sums are combined with fp32 atomics.      */
+int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+               int out_dtype, int64_t ldo, int M, int N, int K, const void* bias, int bias_dtype,
+               int relu, int pad_hp, int pad_wp, void* stream);
+int pd_gemm_nn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+               int out_dtype, int64_t ldo, int M, int N, int K, const void* relu_aux,
+               int64_t ld_aux, void* stream);
+int pd_gemm_tn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, float* out,
+               int64_t ldo, int M, int N, int K, int accumulate, int split_k, void* stream);
+/* torch.nn.Conv2d(kernel 3x3, stride 1, padding 1) forward / input gradient / weight gradient
+ * (vgg16/gpus=8/stage0.py:10-31, stage1.py:12-16) as implicit GEMMs over padded NHWC.
+ * w: [Cout][3][3][Cin] (channels-last order of the [Cout,Cin,3,3] parameter), leading dim ldw.
+ * dgrad: relu_aux != NULL additionally multiplies dx by (relu_aux > 0), relu_aux = the
+ * padded-NHWC input of the layer.  wgrad: dw fp32 [Cout][9*Cin], leading dim lddw.          */
+int pd_conv2d_fwd(int dtype, const void* x_pad, int N, int H, int W, int Cin, const void* w,
+                  int64_t ldw, int Cout, const void* bias, int bias_dtype, int relu, void* y_pad,
+                  void* stream);
+int pd_conv2d_dgrad(int dtype, const void* dy_pad, int N, int H, int W, int Cout, const void* w,
+                    int64_t ldw, int Cin, const void* relu_aux, void* dx_pad, void* stream);
+int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int H, int W, int Cin,
+                    int Cout, float* dw, int64_t lddw, int accumulate, int split_k, void* stream);
+/* Reads and clears the error word the tcgen05 kernels set when a bounded wait runs out
+ * (0 = none).  `code` is a HOST pointer; synchronises the device.                            */
+int pd_gemm_poll_error(int* code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIPEDREAM_B200_H_ */

