@@ -1,0 +1,321 @@
+"""Throughput benchmark of the pipeline-parallel training step (VGG-16, bf16, synthetic data).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1: the whole of VGG-16 in one stage on one GPU, batch 64 (the per-replica batch of the
+hybrid configuration the metric is quoted on).  N > 1 (under torch.distributed.run): the same
+network as a 2-stage pipeline cut after the flatten, stage 0 (all convolutions) replicated on
+N-1 GPUs and stage 1 (the three Linear layers) on one; every replica of stage 0 takes batch 64.
+
+One JSON line is printed by rank 0.  `value` is samples/s with the inputs already resident in
+HBM; `e2e` is the same loop fed from pinned host memory with the loss read back every step.
+`--impl reference` times the CPU oracle (the restatement of the reference's own Python/PyTorch
+path; the reference itself cannot travel to the benchmark machine) on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+BATCH = 64
+METRIC = "vgg16_train_samples_per_sec"
+UNIT = "samples/s"
+# algorithmic FLOPs of one VGG-16 training sample (2 per multiply-add; forward 30.94 G,
+# backward 61.71 G, counted on the reference modules with torch.utils.flop_counter)
+FLOPS_PER_SAMPLE = 92.65e9
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        # median of the samples under load (upper half: idle samples at the edges are dropped)
+        load = sm[len(sm) // 2:]
+        return {"sm_mhz": load[len(load) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class CyclingLoader:
+    """Endless (images, labels) stream from a small pool of pre-generated batches.
+    device="cuda": batches already resident in HBM; device="pinned": pinned host memory, so
+    the consumer's .to(device) is a real host-to-device copy every step."""
+
+    def __init__(self, batch, device, pool=4, seed=1234):
+        from pipedream_b200.stages import SyntheticImages
+        self.items = []
+        for x, y in SyntheticImages(batch, pool, seed=seed):
+            if device == "pinned":
+                self.items.append((x.pin_memory(), y.pin_memory()))
+            else:
+                self.items.append((x.to(device), y.to(device)))
+        self.bytes_per_step = self.items[0][0].numel() * 4 + self.items[0][1].numel() * 8
+
+    def __iter__(self):
+        i = 0
+        while True:
+            yield self.items[i % len(self.items)]
+            i += 1
+
+
+def build_single_stage(fp16=True):
+    """StageRuntime + optimizer for all of VGG-16 on cuda:0, built the way the driver script does
+    (runtime/image_classification/main_with_runtime.py:129-229)."""
+    from pipedream_b200 import runtime, sgd, stages
+    torch.manual_seed(0)
+    pkg = stages.vgg16("gpus=1")
+    model = pkg.model(torch.nn.CrossEntropyLoss())
+    shapes = {"input0": (BATCH, 3, 224, 224), "target": (BATCH,), "out0": (BATCH, 1000)}
+    dtypes = {"input0": torch.int64, "target": torch.int64, "out0": torch.bfloat16 if fp16 else torch.float32}
+    r = runtime.StageRuntime(
+        model=model, distributed_backend=None, fp16=fp16, loss_scale=1, training_tensor_shapes=shapes,
+        eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dtypes, inputs_module_destinations={"input": 0},
+        target_tensor_names={"target"},
+        configuration_maps={"module_to_stage_map": None, "stage_to_rank_map": None, "stage_to_depth_map": None},
+        master_addr=None, rank=None, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
+        model_type=runtime.IMAGE_CLASSIFICATION)
+    opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
+                                    num_versions=r.num_warmup_minibatches + 1, lr=0.01, momentum=0.9,
+                                    weight_decay=5e-4)
+    return r, opt
+
+
+def one_step(r, opt, read_loss):
+    """One minibatch of the 1F1B loop of a stage without warm-up (main_with_runtime.py:363-413)."""
+    r.run_forward()
+    loss = r.loss.item() if read_loss else None
+    opt.zero_grad()
+    opt.load_old_params()
+    r.run_backward()
+    opt.load_new_params()
+    opt.step()
+    return loss
+
+
+def timed_loop(r, opt, steps, warmup, read_loss):
+    """W untimed steps, then K steps between CUDA events; returns milliseconds for the K steps."""
+    for _ in range(warmup):
+        one_step(r, opt, read_loss)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step(r, opt, read_loss)
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end)
+
+
+def cpu_baseline(sample_steps=2, batch=8):
+    """The CPU oracle (port of the reference's PyTorch path) on the host cores, fp32, on a bounded
+    sample of the workload: `sample_steps` minibatches of `batch` images after one untimed one."""
+    from oracle import pipedream_oracle as oracle
+    from pipedream_b200.stages import SyntheticImages
+    torch.manual_seed(0)
+    st = oracle.vgg16_stages(None)
+    model = [(st[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    pipe = oracle.PipelineOracle(model, [0, 0], {0: [0]}, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=5e-4))
+    pipe.run({0: SyntheticImages(batch, 1)}, 1)
+    t0 = time.time()
+    pipe.run({0: SyntheticImages(batch, sample_steps, seed=99)}, sample_steps)
+    dt = time.time() - t0
+    return {"value": batch * sample_steps / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "%d minibatches of %d images, fp32, whole VGG-16 in one stage, after 1 untimed minibatch"
+                      % (sample_steps, batch)}
+
+
+def run_gpu_single(steps, warmup):
+    """N = 1: whole VGG-16, batch 64, bf16, one stage on cuda:0."""
+    from pipedream_b200 import _lib
+    from pipedream_b200 import functional as pf
+    torch.cuda.set_device(0)
+    r, opt = build_single_stage(fp16=True)
+    r.train(steps + warmup)
+
+    # (1) device-resident inputs: `value`
+    r.set_loader(CyclingLoader(BATCH, "cuda"))
+    sampler = ClockSampler(0)
+    sampler.start()
+    _lib.count_calls(True)
+    for _ in range(warmup):
+        one_step(r, opt, False)
+    torch.cuda.synchronize()
+    _lib.count_calls(True)                      # restart the count for the timed region
+    pf.timeline = pf.ContractionTimeline()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step(r, opt, False)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    launches = _lib.launches_counted()
+    calls = dict(_lib.COUNTERS)
+    _lib.count_calls(False)
+    tl = pf.timeline.summary()
+    pf.timeline = None
+    clocks = sampler.stop()
+
+    # (2) pinned host inputs + loss read back every step: `e2e`
+    host = CyclingLoader(BATCH, "pinned")
+    r.set_loader(host)
+    ms_e2e = timed_loop(r, opt, steps, max(1, warmup // 2), True)
+    err = pf.gemm_poll_error()
+    if err != 0:
+        raise RuntimeError("a tcgen05 kernel reported a bounded wait that ran out (code %d)" % err)
+
+    pk = peaks()
+    tot_flops = sum(v[1] for v in tl.values())
+    tot_ms = sum(v[2] for v in tl.values())
+    n_launch = sum(v[0] for v in tl.values())
+    achieved = tot_flops / (tot_ms * 1e-3) / 1e12 if tot_ms > 0 else 0.0
+    roof = {
+        "bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": round(achieved, 1),
+        "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(achieved / pk["bf16_tflops_sustained"], 4),
+        "peak_source": pk["source"] + " (sustained cuBLAS bf16)", "traffic": None,
+        "launches_per_step": n_launch // max(1, steps), "kernel_ms_per_step": round(tot_ms / steps, 3),
+        "algorithmic_tflop_per_step": round(tot_flops / steps / 1e12, 3),
+        "by_pass": {k: {"launches": v[0] // max(1, steps), "tflops": round(v[1] / (v[2] * 1e-3) / 1e12, 1),
+                        "ms_per_step": round(v[2] / steps, 3)} for k, v in sorted(tl.items()) if v[2] > 0},
+    }
+    return {
+        "metric": METRIC, "value": round(BATCH * steps / (ms * 1e-3), 2), "unit": UNIT, "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms / steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "VGG-16 (13 conv3x3 + 3 FC, 1000 classes) bf16 training step, batch 64 of 3x224x224 "
+                               "N(0,1) images, SGD momentum 0.9 lr 0.01 wd 5e-4, one stage on one GPU",
+                   "global_batch": BATCH, "parallelism": "1 stage x 1 replica",
+                   "l2": "no flush: per-step activations (>1 GB) exceed the 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": round(BATCH * steps / (ms_e2e * 1e-3), 2), "unit": UNIT,
+                "h2d_bytes_per_step": host.bytes_per_step, "d2h_bytes_per_step": 4,
+                "ms_per_step": round(ms_e2e / steps, 3)},
+        "gpu_launches": launches, "entry_point_calls": calls,
+        "roofline": roof,
+        "model_flops_utilisation": round(FLOPS_PER_SAMPLE * BATCH * steps / (ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], 4),
+    }
+
+
+def run_reference(steps, warmup, n_gpus):
+    """--impl reference: the reference's CPU path (oracle port) on the host cores, same metric and
+    network; each step is a bounded sample (batch 8 instead of 64 per replica, fp32)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import pipedream_oracle as oracle
+    from pipedream_b200.stages import SyntheticImages
+    batch = 8
+    torch.manual_seed(0)
+    st = oracle.vgg16_stages(None)
+    model = [(st[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    pipe = oracle.PipelineOracle(model, [0, 0], {0: [0]}, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=5e-4))
+    if warmup > 0:
+        pipe.run({0: SyntheticImages(batch, warmup)}, warmup)
+    t0 = time.time()
+    pipe.run({0: SyntheticImages(batch, steps, seed=99)}, steps)
+    dt = time.time() - t0
+    v = round(batch * steps / dt, 3)
+    sample = "each step = one minibatch of %d images (instead of 64), fp32, whole VGG-16 in one stage" % batch
+    return {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": n_gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(dt / steps * 1e3, 1), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "VGG-16 training step on host cores (CPU restatement of the reference's PyTorch path)",
+                   "global_batch": batch, "parallelism": "1 process"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        out = run_reference(a.steps, a.warmup, a.gpus)
+        if out is not None:
+            print(json.dumps(out))
+        return
+    if a.warmup < 3:
+        a.warmup = 3
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if a.gpus == 1 and world == 1:
+        out = run_gpu_single(a.steps, a.warmup)
+        if not a.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(out))
+        return
+    from bench_multi import run_gpu_multi     # pipeline / hybrid partitions over NVLink peer channels
+    out = run_gpu_multi(a.gpus, a.steps, a.warmup)
+    if out is not None:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

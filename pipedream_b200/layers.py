@@ -32,6 +32,8 @@ def grad_buffer(param):
     if g is None:
         data = param.data
         span = 1 + sum((s - 1) * st for s, st in zip(data.shape, data.stride())) if data.numel() else 0
+        if data.dim() >= 2:
+            span = max(span, data.shape[0] * data.stride(0))     # whole rows, incl. row padding
         store = torch.zeros(span, dtype=torch.float32, device=data.device)
         g = store.as_strided(data.shape, data.stride())
         param._pd_grad = g

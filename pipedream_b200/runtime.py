@@ -364,6 +364,9 @@ class StageRuntime:
                     [int(sum(torch.as_tensor(tgt_length, dtype=torch.int64) - 1))], dtype=torch.int))
             elif self.model_type == IMAGE_CLASSIFICATION:
                 (input, target) = input
+                if self.fp16 and not self.native:
+                    input = input.to(self.compute_dtype)     # runtime/runtime.py:397-398 (native
+                    # stages convert inside their first kernel instead)
                 self.tensors[-1]["input0"] = self._to_device(input)
                 self.tensors[-1]["target"] = self._to_device(target)
             else:

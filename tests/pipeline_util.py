@@ -28,7 +28,7 @@ def disable_dropout(model):
 
 
 def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, momentum=0.9, weight_decay=5e-4,
-                dropout=False, optimizer="sgd", macrobatch=False, shapes=None):
+                dropout=False, optimizer="sgd", macrobatch=False, shapes=None, native=True):
     torch.manual_seed(seed)
     model = package.model(torch.nn.CrossEntropyLoss())
     if not dropout:
@@ -45,7 +45,7 @@ def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, mome
         configuration_maps=conf if conf is not None else {"module_to_stage_map": None, "stage_to_rank_map": None,
                                                           "stage_to_depth_map": None},
         master_addr="127.0.0.1", rank=rank, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
-        model_type=runtime.IMAGE_CLASSIFICATION)
+        model_type=runtime.IMAGE_CLASSIFICATION, native=native)
     nv = r.num_warmup_minibatches + 1
     if optimizer == "sgd":
         opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=nv,
@@ -80,3 +80,32 @@ def param_checksums(r):
             out["module%d.%s" % (mi, k)] = {"sum": t.sum().item(), "abs_sum": t.abs().sum().item(),
                                             "sq_sum": (t * t).sum().item(), "samples": t[idx].tolist()}
     return out
+
+
+def run_cfg1(gold, fp16, native):
+    """The golden run's configuration through LocalPipeline; returns (losses, workers).
+    native=False keeps the torch.nn modules (cuDNN / cuBLAS) as a same-GPU control."""
+    cfg = gold["config"]
+    pkg = stages.vgg16("gpus=8")
+    pipe = local_pipeline(pkg, pkg.conf, cfg["batch"], fp16, lr=cfg["lr"], momentum=cfg["momentum"],
+                          weight_decay=cfg["weight_decay"], seed=cfg["seed"], native=native)
+    (r0, o0), (r1, o1) = pipe.workers
+    n = cfg["steps"]
+    r0.set_loader(stages.SyntheticImages(cfg["batch"], n, seed=cfg["data_seed"]))
+    r1.set_loader(None)
+    losses = []
+    pipe.run([n, n], on_loss=lambda k, i, rr: losses.append(float(rr.loss)))
+    return losses, pipe.workers
+
+
+def checksum_errors(workers, gold):
+    """Relative error of the parameter checksums per tensor, split into weights and biases."""
+    werr, berr = {}, {}
+    for (r, _), key in zip(workers, ("stage0", "stage1")):
+        got = param_checksums(r)
+        for name, ref in gold["params"][key].items():
+            g = got[name]
+            scale = max(abs(ref["abs_sum"]), 1e-6)
+            e = max(abs(g["sum"] - ref["sum"]), abs(g["abs_sum"] - ref["abs_sum"])) / scale
+            (berr if name.endswith("bias") else werr)[key + "." + name] = e
+    return werr, berr
