@@ -215,6 +215,11 @@ def run_gpu_single(steps, warmup):
     calls = dict(_lib.COUNTERS)
     _lib.count_calls(False)
     tl = pf.timeline.summary()
+    if os.environ.get("PD_BENCH_DETAIL"):
+        with open(os.environ["PD_BENCH_DETAIL"], "w") as f:
+            for k, v in sorted(pf.timeline.per_shape().items()):
+                f.write("%-40s launches/step %3d  ms/step %7.3f  TFLOP/s %7.1f\n" % (
+                    k, v[0] // steps, v[2] / steps, v[1] / max(v[2], 1e-9) / 1e9))
     pf.timeline = None
     clocks = sampler.stop()
 
@@ -292,7 +297,7 @@ def run_reference(steps, warmup, n_gpus):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

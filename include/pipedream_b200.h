@@ -155,6 +155,30 @@ int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int
  * (0 = none).  `code` is a HOST pointer; synchronises the device.                            */
 int pd_gemm_poll_error(int* code);
 
+/* ---- peer channels --------------------------------------------------------------------
+ * One-directional FIFO between two pipeline-adjacent GPUs; replaces the helper threads and the
+ * GPU -> CPU -> TCP -> CPU -> GPU path of runtime/communication.py:610-712 (`recv_helper_thread`,
+ * `send_helper_thread`, `_recv`, `_send`) and the shape message of :664-669.  The ring of
+ * `num_slots` slots lives in the consumer's HBM and is mapped into the producer process with
+ * CUDA IPC; a push is wait-for-free-slot, NVLink copy, publish, all enqueued on `stream`.
+ * create/open/close are set-up calls (they allocate and synchronise); push and wait are not.
+ * timeout_ms bounds every device-side wait; when it runs out the channel's status becomes -4
+ * (read with pd_chan_status) and the kernels return, so a dead peer cannot hang the GPU.
+ * blob128: 128 bytes of HOST memory carried to the producer by any host transport.
+ * pd_chan_open_local makes a producer end over the same memory inside one process (tests).
+ * pd_chan_peek_header blocks the host until the next message is there; out8 (HOST) receives
+ * {seq, nbytes, ndim, d0..d4} - for tensors whose shape changes per minibatch.               */
+int pd_chan_create(int64_t slot_bytes, int num_slots, int timeout_ms, void** chan);
+int pd_chan_export_handle(void* chan, void* blob128);
+int pd_chan_open(const void* blob128, int timeout_ms, void** chan);
+int pd_chan_open_local(void* consumer_chan, int timeout_ms, void** chan);
+int pd_chan_push(void* chan, const void* src, int64_t bytes, int ndim, const int64_t* dims,
+                 void* stream);
+int pd_chan_wait(void* chan, void* dst, int64_t bytes, void* stream);
+int pd_chan_peek_header(void* chan, int64_t* out8, void* stream);
+int pd_chan_status(void* chan, void* stream);
+int pd_chan_close(void* chan);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,6 +57,15 @@ SIGNATURES = {
     "pd_conv2d_dgrad": (I, [I, P, I, I, I, I, P, L, I, P, P, P]),
     "pd_conv2d_wgrad": (I, [I, P, P, I, I, I, I, I, P, L, I, I, P]),
     "pd_gemm_poll_error": (I, [POINTER(c_int)]),
+    "pd_chan_create": (I, [L, I, I, POINTER(c_void_p)]),
+    "pd_chan_export_handle": (I, [P, P]),
+    "pd_chan_open": (I, [P, I, POINTER(c_void_p)]),
+    "pd_chan_open_local": (I, [P, I, POINTER(c_void_p)]),
+    "pd_chan_push": (I, [P, P, L, I, POINTER(c_int64), P]),
+    "pd_chan_wait": (I, [P, P, L, P]),
+    "pd_chan_peek_header": (I, [P, POINTER(c_int64), P]),
+    "pd_chan_status": (I, [P, P]),
+    "pd_chan_close": (I, [P]),
 }
 
 

@@ -38,29 +38,38 @@ class ContractionTimeline:
         e.record()
         return e
 
-    def end(self, name, flops, start):
+    def end(self, name, flops, start, detail=None):
         e = torch.cuda.Event(enable_timing=True)
         e.record()
-        self.records.append((name, flops, start, e))
+        self.records.append((name, flops, start, e, detail))
 
     def summary(self):
         """{name: (launches, total_flops, total_ms)} - call after a synchronize."""
         out = {}
-        for name, flops, s, e in self.records:
+        for name, flops, s, e, _ in self.records:
             n, f, t = out.get(name, (0, 0.0, 0.0))
             out[name] = (n + 1, f + flops, t + s.elapsed_time(e))
+        return out
+
+    def per_shape(self):
+        """{(name, detail): (launches, total_flops, total_ms)} - call after a synchronize."""
+        out = {}
+        for name, flops, s, e, detail in self.records:
+            k = "%s %s" % (name, detail)
+            n, f, t = out.get(k, (0, 0.0, 0.0))
+            out[k] = (n + 1, f + flops, t + s.elapsed_time(e))
         return out
 
 
 timeline = None
 
 
-def _timed(name, flops, fn):
+def _timed(name, flops, fn, detail=None):
     if timeline is None:
         return fn()
     s = timeline.begin()
     r = fn()
-    timeline.end(name, flops, s)
+    timeline.end(name, flops, s, detail)
     return r
 
 
@@ -252,7 +261,7 @@ def gemm_nt(a, b, bias=None, relu=False, out_dtype=None, pad_hw=None):
     hp, wp = pad_hw if pad_hw is not None else (0, 0)
     _timed("gemm_nt", 2.0 * M * N * K, lambda: call(
         "pd_gemm_nt", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
-        _p(bias), dt(bias) if bias is not None else 0, int(relu), hp, wp, _stream()))
+        _p(bias), dt(bias) if bias is not None else 0, int(relu), hp, wp, _stream()), (M, N, K))
     return out
 
 
@@ -264,7 +273,7 @@ def gemm_nn(a, b, relu_aux=None):
     out = torch.empty((M, N), dtype=a.dtype, device=a.device)
     _timed("gemm_nn", 2.0 * M * N * K, lambda: call(
         "pd_gemm_nn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
-        _p(relu_aux), relu_aux.stride(0) if relu_aux is not None else 0, _stream()))
+        _p(relu_aux), relu_aux.stride(0) if relu_aux is not None else 0, _stream()), (M, N, K))
     return out
 
 
@@ -276,7 +285,7 @@ def gemm_tn(a, b, out, accumulate=False, split_k=0):
     assert out.dtype == torch.float32
     _timed("gemm_tn", 2.0 * M * N * K, lambda: call(
         "pd_gemm_tn", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), out.stride(0), M, N, K,
-        int(accumulate), int(split_k), _stream()))
+        int(accumulate), int(split_k), _stream()), (M, N, K))
     return out
 
 
@@ -287,7 +296,7 @@ def conv2d_fwd(x_pad, w, ldw, cout, bias, relu):
     # algorithmic FLOPs: 2 * 9 * Cin * Cout per real output pixel (the padded border is overhead)
     _timed("conv_fwd", 18.0 * N * (Hp - 2) * (Wp - 2) * Cin * cout, lambda: call(
         "pd_conv2d_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, Cin, _p(w), ldw, cout, _p(bias),
-        dt(bias) if bias is not None else 0, int(relu), _p(y), _stream()))
+        dt(bias) if bias is not None else 0, int(relu), _p(y), _stream()), (N, Hp - 2, Cin, cout))
     return y
 
 
@@ -296,7 +305,7 @@ def conv2d_dgrad(dy_pad, w, ldw, cin, relu_aux=None):
     dx = torch.empty((N, Hp, Wp, cin), dtype=dy_pad.dtype, device=dy_pad.device)
     _timed("conv_dgrad", 18.0 * N * (Hp - 2) * (Wp - 2) * cin * Cout, lambda: call(
         "pd_conv2d_dgrad", dt(dy_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cout, _p(w), ldw, cin, _p(relu_aux), _p(dx),
-        _stream()))
+        _stream()), (N, Hp - 2, cin, Cout))
     return dx
 
 
@@ -306,7 +315,7 @@ def conv2d_wgrad(x_pad, dy_pad, dw, lddw, accumulate=False, split_k=0):
     assert dw.dtype == torch.float32
     _timed("conv_wgrad", 18.0 * N * (Hp - 2) * (Wp - 2) * Cin * Cout, lambda: call(
         "pd_conv2d_wgrad", dt(x_pad), _p(x_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cin, Cout, _p(dw), lddw,
-        int(accumulate), int(split_k), _stream()))
+        int(accumulate), int(split_k), _stream()), (N, Hp - 2, Cin, Cout))
     return dw
 
 
