@@ -221,8 +221,6 @@ class CommunicationHandler(object):
         self.setup_messaging_schedule()
         self.tensor_shapes = None
         self.forward_only = False
-        if hasattr(self.transport, "open_channels"):
-            self.transport.open_channels(self)
 
     def setup_messaging_schedule(self):
         self.schedule = MessagingSchedule(self.rank_in_stage, self.num_ranks_in_stage,
@@ -264,6 +262,8 @@ class CommunicationHandler(object):
             self.receive_ranks.pop("ack", None)
             self.send_ranks.pop("ack", None)
         self.num_iterations_for_helper_threads(num_iterations)
+        if hasattr(self.transport, "setup"):
+            self.transport.setup(self, self.tensor_shapes)    # collective: opens missing peer channels
 
     def wait(self):
         self.transport.wait()

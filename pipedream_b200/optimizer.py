@@ -269,9 +269,9 @@ class OptimizerWithWeightStashing:
         if log_timing:
             start_time = time.time()
         self._collect_foreign_grads()
-        if self._grad_sync is not None:
-            self._grad_sync(self.grad_arena)
         grad_scale = 1.0 / self.update_interval
+        if self._grad_sync is not None:
+            grad_scale *= self._grad_sync(self.grad_arena)
         if self.dtype != torch.float32 and self.loss_scale != 1.0:
             grad_scale /= self.loss_scale
         group = self.base_optimizer.param_groups[0]

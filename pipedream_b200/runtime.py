@@ -15,6 +15,7 @@ optimizer step instead of DistributedDataParallel.
 """
 import collections
 import itertools
+import os
 
 import torch
 import torch.distributed as dist
@@ -200,7 +201,8 @@ class StageRuntime:
             self.is_criterion = a["is_criterion"]
             self.num_warmup_minibatches = a["num_warmup_minibatches"]
 
-            master_port = 12345
+            # fixed port of the reference (runtime/runtime.py:181); overridable for concurrent jobs
+            master_port = int(os.environ.get("PIPEDREAM_MASTER_PORT", "12345"))
             self.comm_handler = communication.CommunicationHandler(
                 master_addr=master_addr, master_port=master_port, rank=self.rank,
                 local_rank=self.local_rank, num_ranks_in_server=num_ranks_in_server,
@@ -273,14 +275,12 @@ class StageRuntime:
         group, world = self.stage_group, self.num_ranks_in_stage
 
         def sync(grad_arena):
+            """Sums the arena over the replicas; returns the factor that turns the sum into the mean
+            (the optimizer folds it into the gradient scale of its fused kernel)."""
             if group is None:
-                return
+                return 1.0
             dist.all_reduce(grad_arena, op=dist.ReduceOp.SUM, group=group)
-            if grad_arena.is_cuda:
-                from . import functional as pf
-                pf.scale_(grad_arena, 1.0 / world)
-            else:
-                grad_arena.mul_(1.0 / world)
+            return 1.0 / world
         return sync
 
     # ------------------------------------------------------------------ accessors

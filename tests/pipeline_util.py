@@ -28,7 +28,7 @@ def disable_dropout(model):
 
 
 def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, momentum=0.9, weight_decay=5e-4,
-                dropout=False, optimizer="sgd", macrobatch=False, shapes=None, native=True):
+                dropout=False, optimizer="sgd", macrobatch=False, shapes=None, native=True, local_rank=0):
     torch.manual_seed(seed)
     model = package.model(torch.nn.CrossEntropyLoss())
     if not dropout:
@@ -44,7 +44,7 @@ def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, mome
         inputs_module_destinations={"input": 0}, target_tensor_names={"target"},
         configuration_maps=conf if conf is not None else {"module_to_stage_map": None, "stage_to_rank_map": None,
                                                           "stage_to_depth_map": None},
-        master_addr="127.0.0.1", rank=rank, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
+        master_addr="127.0.0.1", rank=rank, local_rank=local_rank, num_ranks_in_server=1, verbose_freq=0,
         model_type=runtime.IMAGE_CLASSIFICATION, native=native)
     nv = r.num_warmup_minibatches + 1
     if optimizer == "sgd":
