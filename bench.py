@@ -319,7 +319,10 @@ def main():
     from bench_multi import run_gpu_multi     # pipeline / hybrid partitions over NVLink peer channels
     out = run_gpu_multi(a.gpus, a.steps, a.warmup)
     if out is not None:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -161,6 +161,15 @@ class _GlooTransport:
         self.pending = []
 
 
+def _rendezvous_env(master_addr, master_port):
+    """MASTER_ADDR / MASTER_PORT as the reference sets them (runtime/communication.py:38-40),
+    unless a launcher (torch.distributed.run) already hosts the rendezvous store."""
+    if os.environ.get("TORCHELASTIC_RUN_ID") or os.environ.get("TORCHELASTIC_USE_AGENT_STORE"):
+        return
+    os.environ['MASTER_ADDR'] = master_addr
+    os.environ['MASTER_PORT'] = str(master_port)
+
+
 # --------------------------------------------------------------------------- #
 # handler
 # --------------------------------------------------------------------------- #
@@ -180,16 +189,14 @@ class CommunicationHandler(object):
             self.transport = _LocalTransport(rank)
         elif backend == GLOO:
             if not dist.is_initialized():
-                os.environ['MASTER_ADDR'] = master_addr
-                os.environ['MASTER_PORT'] = str(master_port)
+                _rendezvous_env(master_addr, master_port)
                 dist.init_process_group(backend, rank=rank, world_size=world_size)
             assert dist.get_world_size() == self.world_size
             self.transport = _GlooTransport(rank)
         elif backend in (NCCL, P2P):
             from . import peer_channel
             if not dist.is_initialized():
-                os.environ['MASTER_ADDR'] = master_addr
-                os.environ['MASTER_PORT'] = str(master_port)
+                _rendezvous_env(master_addr, master_port)
                 dist.init_process_group(NCCL, rank=rank, world_size=world_size,
                                         device_id=torch.device("cuda", local_rank))
             assert dist.get_world_size() == self.world_size
