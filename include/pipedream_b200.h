@@ -105,6 +105,18 @@ int pd_softmax_ce_bwd(const void* logits, int dtype, const int64_t* target, cons
                       int64_t rows, int C, float smoothing, int64_t padding_idx,
                       const float* upstream, float gscale, void* dlogits, void* stream);
 
+/* No counterpart in the reference: the forward criterion for callers that must not allocate.
+ * Identical result to pd_softmax_ce_fwd, but the per-row scratch is a fixed 65536-row array
+ * inside the library (256 KiB held by every GPU that loads it) and the call performs no device
+ * allocation.  Meant for hosts with a fixed device-memory plan (all HBM handed out up front) or
+ * a no-allocation rule after start-up.  rows > pd_softmax_ce_static_max_rows() is an error (-1).
+ * The first call on a device looks up the array's address: make it before any stream capture.
+ * Calls share the array; calls that overlap on the GPU race.                                  */
+int pd_softmax_ce_fwd_static(const void* logits, int dtype, const int64_t* target, int64_t rows,
+                             int C, float smoothing, int64_t padding_idx, float scale, float* lse,
+                             float* loss, void* stream);
+int64_t pd_softmax_ce_static_max_rows(void);
+
 /* ---- sequence utilities ----------------------------------------------------------------
  * pd_revert_varlen replaces revert_varlen_tensor (runtime/translation/seq2seq/csrc/
  * pack_utils_kernel.cu:24-63); pd_length_mask replaces set_mask_cpp (csrc/pack_utils.cpp:

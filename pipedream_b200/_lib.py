@@ -46,6 +46,8 @@ SIGNATURES = {
     "pd_add": (I, [P, P, P, L, I, P]),
     "pd_softmax_ce_fwd": (I, [P, I, P, L, I, F, L, F, P, P, P, P]),
     "pd_softmax_ce_bwd": (I, [P, I, P, P, L, I, F, L, P, F, P, P]),
+    "pd_softmax_ce_fwd_static": (I, [P, I, P, L, I, F, L, F, P, P, P]),
+    "pd_softmax_ce_static_max_rows": (L, []),
     "pd_revert_varlen": (I, [P, P, P, I, I, L, P]),
     "pd_length_mask": (I, [P, I, I, P, I, P]),
     "pd_embedding_fwd": (I, [P, P, L, I, L, P, I, P]),

@@ -2,10 +2,16 @@
 // reduction) and label-smoothed NLL (runtime/translation/seq2seq/train/smoothing.py:23-34).
 // Row statistics are accumulated in fp32 whatever the logits dtype.
 #include "pd_common.cuh"
+#include <mutex>
 
 namespace {
 
 constexpr int kThreads = 256;
+
+// Scratch of pd_softmax_ce_fwd_static: one per-row loss term per logits row.  It is part of the
+// library image, so every GPU that loads the library holds these 256 KiB until the process exits.
+constexpr int kStaticRowsMax = 65536;
+static __device__ __align__(256) float g_static_row_loss[kStaticRowsMax];
 
 __device__ __forceinline__ float block_max(float v, float* sm) {
   v = pd_warp_max(v);
@@ -141,3 +147,63 @@ PD_EXPORT int pd_softmax_ce_bwd(const void* logits, int dtype, const int64_t* ta
   PD_LAUNCH_CHECK("softmax_ce_bwd_kernel");
   return PD_OK;
 }
+
+
+namespace {
+std::mutex g_static_mu;
+float* g_static_row_loss_addr[64];     // device address of g_static_row_loss, per device ordinal
+
+// In host code `g_static_row_loss` is only a handle for the symbol, not an address a kernel can
+// use; the device address is looked up once per device, with that device current.
+int static_row_loss_ptr(float** out) {
+  int dev = 0;
+  PD_CUDA(cudaGetDevice(&dev));
+  PD_REQUIRE(dev >= 0 && dev < 64, "pd_softmax_ce_fwd_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_row_loss_addr[dev] == nullptr) {
+    float* p = nullptr;
+    PD_CUDA(cudaGetSymbolAddress((void**)&p, g_static_row_loss));
+    PD_REQUIRE(p != nullptr, "pd_softmax_ce_fwd_static: the scratch symbol has no device address");
+    g_static_row_loss_addr[dev] = p;
+  }
+  *out = g_static_row_loss_addr[dev];
+  return PD_OK;
+}
+}  // namespace
+
+// Same result as pd_softmax_ce_fwd (loss and lse), but the per-row scratch is a fixed array inside
+// the library instead of a caller buffer, and the call makes no device allocation of any kind.
+// For hosts that must not allocate once training runs: a stage whose HBM was planned and handed
+// out up front (weight-version ring, activation stash), or an embedding runtime that forbids
+// cudaMalloc after start-up because it synchronises the device and can fail late.
+//   - rows above pd_softmax_ce_static_max_rows() (65536) are rejected with PD_ERR_INVALID;
+//   - the first call on each device looks up the array's device address (a host-side runtime
+//     query, no allocation); make that first call before starting any stream capture;
+//   - all calls on a device share the one array: every call overwrites the rows it uses and reads
+//     nothing older, so nothing needs clearing, but two calls that overlap on the GPU (different
+//     streams without an ordering between them) race on it.
+PD_EXPORT int pd_softmax_ce_fwd_static(const void* logits, int dtype, const int64_t* target, int64_t rows,
+                                       int C, float smoothing, int64_t padding_idx, float scale, float* lse,
+                                       float* loss, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(logits && target && lse && loss && rows > 0 && C > 0, "pd_softmax_ce_fwd_static: bad arguments");
+  PD_REQUIRE(rows <= kStaticRowsMax,
+             "pd_softmax_ce_fwd_static: %lld rows exceed the built-in scratch of %d rows; use pd_softmax_ce_fwd "
+             "with a caller buffer", (long long)rows, kStaticRowsMax);
+  float* row_loss = nullptr;
+  rc = static_row_loss_ptr(&row_loss);
+  if (rc != PD_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_F32)
+    softmax_ce_rows_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  else if (dtype == PD_BF16)
+    softmax_ce_rows_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  else PD_REQUIRE(false, "pd_softmax_ce_fwd_static: bad dtype");
+  PD_LAUNCH_CHECK("softmax_ce_rows_kernel");
+  loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, rows, scale, loss);
+  PD_LAUNCH_CHECK("loss_reduce_kernel");
+  return PD_OK;
+}
+
+PD_EXPORT int64_t pd_softmax_ce_static_max_rows() { return kStaticRowsMax; }
