@@ -28,6 +28,7 @@ struct PdGemm {
   int a_tap_row[PD_MAX_TAPS], a_tap_col[PD_MAX_TAPS];
   int b_tap_row[PD_MAX_TAPS], b_tap_col[PD_MAX_TAPS];
   int num_z; int z_b_row[PD_MAX_TAPS]; int64_t z_out_col;
+  int z_group;                // tcgen05: up to this many z outputs share one CTA (and its A tiles)
   int split_k;
   // epilogue
   void* out; int out_dtype; int64_t ldo;

@@ -171,10 +171,13 @@ PD_EXPORT int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, 
   int shift[9]; conv_taps(Wp, shift);
   for (int t = 0; t < 9; ++t) g.z_b_row[t] = shift[t];
   g.z_out_col = Cin;
+  g.z_group = 4;
   g.out = dw; g.out_dtype = PD_F32; g.ldo = lddw;
   const int bn = dtype == PD_BF16 ? (Cin > 128 ? 256 : (Cin > 64 ? 128 : 64)) : 64;
   const int bm = dtype == PD_BF16 ? 128 : 64;
-  const int64_t tiles = 9ll * ((Cout + bm - 1) / bm) * ((Cin + bn - 1) / bn);
+  // bf16: up to 256 accumulator columns per CTA, i.e. several taps share one CTA (z groups)
+  const int per_cta = dtype == PD_BF16 ? (256 / bn < 4 ? (256 / bn < 1 ? 1 : 256 / bn) : 4) : 1;
+  const int64_t tiles = (int64_t)((9 + per_cta - 1) / per_cta) * ((Cout + bm - 1) / bm) * ((Cin + bn - 1) / bn);
   g.split_k = split_k > 0 ? split_k : auto_split(tiles, (int)((P + 63) / 64));
   int rc = prepare_grad_out(g, accumulate, Cout, 9ll * Cin, (cudaStream_t)stream);
   if (rc != PD_OK) return rc;

@@ -32,8 +32,9 @@ constexpr uint32_t kAtomBytes = 64 * kBlockK * 2;     // one 64-wide MN-major at
 constexpr long long kWaitCycles = 400000000ll;        // ~0.2 s at 2 GHz
 
 struct KParams {
-  int M, N, block_n;
-  int num_taps, kb_per_tap, kb_per_split, split_k, num_z;
+  int M, N, block_n, m_tiles, n_tiles;
+  int num_taps, kb_per_tap, kb_per_split, split_k, num_z;   // num_z = number of z groups
+  int acc_count, num_z_total;                                // accumulators per tile, outputs in all
   int a_major, b_major;
   int a_row0, a_col0, b_row0, b_col0;
   int a_cols, b_cols;
@@ -126,42 +127,46 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, int mn_major) 
   return d;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent: each CTA walks the tile list with stride gridDim.x.  The accumulator is double
+// buffered in tensor memory (2 x block_n columns), so the epilogue of one tile runs under the
+// MMAs of the next one; the shared-memory stage ring runs on across tile boundaries.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-  __shared__ __align__(8) uint64_t tmem_full_bar;
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_holder;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t b_bytes = (uint32_t)p.block_n * kBlockK * 2;
-  const uint32_t stage_bytes = kABytes + b_bytes;
+  const uint32_t stage_bytes = kABytes + (uint32_t)p.acc_count * b_bytes;
   const int S = p.num_stages;
+  const uint32_t acc_cols = (uint32_t)(p.acc_count * p.block_n);   // TMEM columns of one buffer
+  const int tiles_mn = p.m_tiles * p.n_tiles;
+  const int total_tiles = tiles_mn * p.num_z * p.split_k;
 
-  const int m0 = blockIdx.x * kBlockM;
-  const int n0 = blockIdx.y * p.block_n;
-  const int z = blockIdx.z / p.split_k;
-  const int split = blockIdx.z % p.split_k;
-  const int kb_begin = split * p.kb_per_split;
-  int kb_end = kb_begin + p.kb_per_split;
-  if (kb_end > p.kb_per_tap) kb_end = p.kb_per_tap;
-  const int kbn = kb_end - kb_begin;
-  const int iters = kbn > 0 ? kbn * p.num_taps : 0;
-
-  // TMEM columns: power of two >= 32 covering block_n
+  // TMEM columns: power of two >= 32 covering two accumulators
   uint32_t tmem_cols = 32;
-  while (tmem_cols < (uint32_t)p.block_n) tmem_cols <<= 1;
+  while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    mbar_init(smem_u32(&tmem_full_bar), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 4);     // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -175,80 +180,137 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_holder;
 
+  // tile -> (m0, n0, z, kb_begin, kbn); n varies fastest so that CTAs running together share A rows
+#define PD_DECODE_TILE(tile)                                                   \
+  const int zs_ = (tile) / tiles_mn;                                           \
+  const int rem_ = (tile) - zs_ * tiles_mn;                                    \
+  const int m0 = (rem_ / p.n_tiles) * kBlockM;                                 \
+  const int n0 = (rem_ % p.n_tiles) * p.block_n;                               \
+  const int z = zs_ / p.split_k;                                               \
+  const int kb_begin = (zs_ % p.split_k) * p.kb_per_split;                     \
+  const int kb_end_ = min(kb_begin + p.kb_per_split, p.kb_per_tap);            \
+  const int kbn = kb_end_ - kb_begin;                                          \
+  const int iters = kbn > 0 ? kbn * p.num_taps : 0;                             \
+  const int acc0 = z * p.acc_count;                                             \
+  const int accn = min(p.acc_count, p.num_z_total - acc0);
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0 && iters > 0) {
+    // The whole warp walks the loop; lane 0 arms the barrier, lanes 0..boxes-1 each issue one box,
+    // so the (up to six) box loads of a stage go out in one instruction slot.
+    {
       const int a_boxes = p.a_major ? 2 : 1;
       const int b_boxes = p.b_major ? p.block_n / 64 : 1;
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % S;
-        const uint32_t ph = (uint32_t)(it / S) & 1u;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) break;
-        const int t = it / kbn;
-        const int kb = kb_begin + it % kbn;
-        const uint32_t fb = smem_u32(&full_bar[s]);
-        const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
-        const uint32_t sb = sa + kABytes;
-        // count the bytes of the boxes that are actually issued
-        uint32_t tx = 0;
-        int a_issue = 0, b_issue = 0;
-        if (p.a_major) {
-          for (int j = 0; j < a_boxes; ++j)
-            if (p.a_col0 + p.a_tap_col[t] + m0 + j * 64 < p.a_cols) { ++a_issue; tx += kAtomBytes; }
-        } else { a_issue = 1; tx += kABytes; }
-        if (p.b_major) {
-          for (int j = 0; j < b_boxes; ++j)
-            if (p.b_col0 + p.b_tap_col[t] + n0 + j * 64 < p.b_cols) { ++b_issue; tx += kAtomBytes; }
-        } else { b_issue = 1; tx += b_bytes; }
-        mbar_expect_tx(fb, tx);
-        if (p.a_major) {
-          const int y = p.a_row0 + kb * kBlockK + p.a_tap_row[t];
-          for (int j = 0; j < a_issue; ++j)
-            tma_load_2d(sa + (uint32_t)j * kAtomBytes, &tma_a, fb, p.a_col0 + p.a_tap_col[t] + m0 + j * 64, y);
-        } else {
-          tma_load_2d(sa, &tma_a, fb, p.a_col0 + p.a_tap_col[t] + kb * kBlockK, p.a_row0 + m0 + p.a_tap_row[t]);
-        }
-        if (p.b_major) {
-          const int y = p.b_row0 + kb * kBlockK + p.b_tap_row[t] + p.z_b_row[z];
-          for (int j = 0; j < b_issue; ++j)
-            tma_load_2d(sb + (uint32_t)j * kAtomBytes, &tma_b, fb, p.b_col0 + p.b_tap_col[t] + n0 + j * 64, y);
-        } else {
-          tma_load_2d(sb, &tma_b, fb, p.b_col0 + p.b_tap_col[t] + kb * kBlockK,
-                      p.b_row0 + n0 + p.b_tap_row[t] + p.z_b_row[z]);
+      const bool is_a = lane < a_boxes;
+      const int bl = lane - a_boxes;                         // B lanes: accumulator-major
+      const int acc = is_a ? 0 : bl / b_boxes;               // which accumulator's B tile
+      const int j = is_a ? lane : bl % b_boxes;              // box index within its operand tile
+      uint32_t g = 0;                       // stage uses so far (ring position across tiles)
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        PD_DECODE_TILE(tile)
+        (void)iters;
+        const bool has_box = is_a || acc < accn;
+        const int zrow = p.z_b_row[min(acc0 + acc, PD_MAX_TAPS - 1)];
+        for (int t = 0; t < p.num_taps && ok; ++t) {
+          // per-tap constants of this lane's box
+          int x0, y0, xk, yk;              // coordinate = (x0 + kb * xk, y0 + kb * yk)
+          uint32_t dst_off, bytes;
+          bool issue = has_box;
+          if (is_a) {
+            if (p.a_major) {
+              x0 = p.a_col0 + p.a_tap_col[t] + m0 + j * 64; y0 = p.a_row0 + p.a_tap_row[t]; xk = 0; yk = kBlockK;
+              dst_off = (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              issue = issue && x0 < p.a_cols;
+            } else {
+              x0 = p.a_col0 + p.a_tap_col[t]; y0 = p.a_row0 + m0 + p.a_tap_row[t]; xk = kBlockK; yk = 0;
+              dst_off = 0; bytes = kABytes;
+            }
+          } else {
+            if (p.b_major) {
+              x0 = p.b_col0 + p.b_tap_col[t] + n0 + j * 64; y0 = p.b_row0 + p.b_tap_row[t] + zrow; xk = 0; yk = kBlockK;
+              dst_off = kABytes + (uint32_t)acc * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              issue = issue && x0 < p.b_cols;
+            } else {
+              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0 + p.b_tap_row[t] + zrow; xk = kBlockK; yk = 0;
+              dst_off = kABytes + (uint32_t)acc * b_bytes; bytes = b_bytes;
+            }
+          }
+          // bytes that will land in a stage = sum over the issuing lanes
+          uint32_t tx = issue ? bytes : 0u;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+          const CUtensorMap* map = is_a ? &tma_a : &tma_b;
+          for (int kb = kb_begin; kb < kb_begin + kbn; ++kb, ++g) {
+            const int s = (int)(g % (uint32_t)S);
+            const uint32_t ph = (g / (uint32_t)S) & 1u;
+            ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t fb = smem_u32(&full_bar[s]);
+            if (lane == 0) mbar_expect_tx(fb, tx);
+            __syncwarp();
+            if (issue)
+              tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0 && iters > 0) {
+    if (lane == 0) {
       const uint32_t adv_a = p.a_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
       const uint32_t adv_b = p.b_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
+      uint32_t g = 0;
+      uint32_t local = 0;                   // tiles done by this CTA
       bool ok = true;
-      for (int it = 0; it < iters && ok; ++it) {
-        const int s = it % S;
-        const uint32_t ph = (uint32_t)(it / S) & 1u;
-        ok = mbar_wait(smem_u32(&full_bar[s]), ph, p.err, 2);
-        if (!ok) break;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        PD_DECODE_TILE(tile)
+        (void)m0; (void)n0; (void)kb_begin; (void)acc0;
+        if (iters == 0) continue;             // (cannot happen: the host never creates empty splits)
+        const uint32_t buf = local & 1u;
+        const uint32_t use = local >> 1;
+        // the epilogue must have drained this accumulator (passes at once on its first use)
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), (use & 1u) ^ 1u, p.err, 4)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
-        const uint64_t da = make_desc(sa, p.a_major);
-        const uint64_t db = make_desc(sa + kABytes, p.b_major);
+        const uint32_t tmem_d = tmem_base + buf * acc_cols;
+        for (int it = 0; it < iters; ++it, ++g) {
+          const int s = (int)(g % (uint32_t)S);
+          const uint32_t ph = (g / (uint32_t)S) & 1u;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, p.err, 2)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
+          const uint64_t da = make_desc(sa, p.a_major);
+          for (int a = 0; a < accn; ++a) {
+            const uint64_t db = make_desc(sa + kABytes + (uint32_t)a * b_bytes, p.b_major);
 #pragma unroll
-        for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-          umma_bf16(tmem_base, da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b), p.idesc,
-                    (uint32_t)((it | kk) != 0));
-        umma_commit(smem_u32(&empty_bar[s]));
+            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
+              umma_bf16(tmem_d + (uint32_t)(a * p.block_n), da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b),
+                        p.idesc, (uint32_t)((it | kk) != 0));
+          }
+          umma_commit(smem_u32(&empty_bar[s]));
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[buf]));
+        ++local;
       }
-      if (ok) umma_commit(smem_u32(&tmem_full_bar));
     }
   } else {
     // -------------------------------- epilogue --------------------------------
     const int lg = warp & 3;                 // TMEM lane group this warp may read
-    const int m = m0 + lg * 32 + lane;
-    bool ready = iters > 0;
-    if (ready) ready = mbar_wait(smem_u32(&tmem_full_bar), 0, p.err, 3);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ready) {
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      PD_DECODE_TILE(tile)
+      (void)kb_begin;
+      if (iters == 0) continue;
+      const uint32_t buf = local & 1u;
+      const uint32_t use = local >> 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[buf]), use & 1u, p.err, 3);
+      // the wait result can differ between lanes only when the bound ran out; make it uniform
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m = m0 + lg * 32 + lane;
       bool border = false;
       if (p.pad_wp > 0) {
         const int wp = m % p.pad_wp;
@@ -256,14 +318,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         border = (wp == 0) | (wp == p.pad_wp - 1) | (hp == 0) | (hp == p.pad_hp - 1);
       }
       const bool row_ok = m < p.M;
-      const long long out_col0 = (long long)z * p.z_out_col;
-      for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+      const uint32_t tmem_acc = tmem_base + buf * acc_cols + ((uint32_t)(lg * 32) << 16);
+      for (int cc = 0; cc < accn * p.block_n; cc += 32) {
+        const int a = cc / p.block_n;
+        const int c0 = cc - a * p.block_n;
+        const long long out_col0 = (long long)(acc0 + a) * p.z_out_col;
+        const int nb = n0 + c0;
+        if (nb >= p.N) continue;              // warp-uniform
         uint32_t r[32];
         __syncwarp();
-        tmem_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld32(tmem_acc + (uint32_t)cc, r);
         if (!row_ok) continue;
-        const int nb = n0 + c0;
-        if (nb >= p.N) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -299,9 +364,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const bool full = nb + 32 <= p.N;
         if (p.atomic) {
           float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
+          if (full && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full || nb + j < p.N) atomicAdd(o + j, v[j]);
+            for (int q = 0; q < 8; ++q)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                           ::"l"(o + q * 4), "f"(v[q * 4]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                           : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || nb + j < p.N) atomicAdd(o + j, v[j]);
+          }
         } else if (p.out_dtype == PD_BF16) {
           __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)m * p.ldo + out_col0 + nb;
           if (full && (((uintptr_t)o) & 15) == 0) {
@@ -336,8 +409,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
         }
       }
+      // this warp has read everything it needs from the accumulator: hand it back to the MMA warp
+      __syncwarp();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+      ++local;
     }
   }
+#undef PD_DECODE_TILE
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -393,12 +472,15 @@ bool g_attr_set[64];
 
 }  // namespace
 
-int pd_gemm_pick_block_n(int N, int b_major) {
-  int bn;
-  if (N > 128) bn = 256;
-  else if (N > 64) bn = 128;
-  else bn = 64;
-  (void)b_major;
+// Widest N tile that still leaves about one tile per SM; K-major B allows 32-wide tiles, which is what
+// keeps a skinny Linear layer (M = batch <= 128) from running on a handful of SMs.
+int pd_gemm_pick_block_n(int M, int N, int b_major, int zs) {
+  const int sms = pd_num_sms();
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int min_bn = b_major ? 64 : 32;
+  int bn = N > 128 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
+  if (bn < min_bn) bn = min_bn;
+  while (bn > min_bn && (long long)m_tiles * ((N + bn - 1) / bn) * zs < sms) bn >>= 1;
   return bn;
 }
 
@@ -415,7 +497,7 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   for (int t = 0; t < g.num_taps; ++t)
     PD_REQUIRE((g.a_tap_col[t] % 8) == 0 && (g.b_tap_col[t] % 8) == 0, "tcgen05 gemm: tap column offsets must be multiples of 8");
 
-  const int block_n = pd_gemm_pick_block_n(g.N, g.b_major);
+  const int block_n = pd_gemm_pick_block_n(g.M, g.N, g.b_major, g.num_z * g.split_k);
   KParams p;
   memset(&p, 0, sizeof(p));
   p.M = g.M; p.N = g.N; p.block_n = block_n;
@@ -425,7 +507,14 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   if (p.split_k > p.kb_per_tap) p.split_k = p.kb_per_tap;
   p.kb_per_split = (p.kb_per_tap + p.split_k - 1) / p.split_k;
   p.split_k = (p.kb_per_tap + p.kb_per_split - 1) / p.kb_per_split;   // no empty splits
-  p.num_z = g.num_z;
+  // z groups: several independent outputs (weight-gradient taps) share one CTA's A tiles
+  int acc = g.z_group > 1 ? g.z_group : 1;
+  if (acc > 256 / block_n) acc = 256 / block_n;
+  if (acc < 1) acc = 1;
+  if (acc > g.num_z) acc = g.num_z;
+  p.acc_count = acc;
+  p.num_z_total = g.num_z;
+  p.num_z = (g.num_z + acc - 1) / acc;
   p.a_major = g.a_major; p.b_major = g.b_major;
   p.a_row0 = g.a_row0; p.a_col0 = g.a_col0; p.b_row0 = g.b_row0; p.b_col0 = g.b_col0;
   p.a_cols = (int)g.a_cols; p.b_cols = (int)g.b_cols;
@@ -442,7 +531,7 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.a_major ? 1 : 0) << 15) |
             ((uint32_t)(g.b_major ? 1 : 0) << 16) | ((uint32_t)(block_n >> 3) << 17) |
             ((uint32_t)(kBlockM >> 4) << 24);
-  const uint32_t stage_bytes = kABytes + (uint32_t)block_n * kBlockK * 2;
+  const uint32_t stage_bytes = kABytes + (uint32_t)p.acc_count * (uint32_t)block_n * kBlockK * 2;
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
@@ -466,7 +555,12 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
       g_attr_set[dev] = true;
     }
   }
-  dim3 grid((g.M + kBlockM - 1) / kBlockM, (g.N + block_n - 1) / block_n, g.num_z * p.split_k);
+  p.m_tiles = (g.M + kBlockM - 1) / kBlockM;
+  p.n_tiles = (g.N + block_n - 1) / block_n;
+  const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.num_z * p.split_k;
+  PD_REQUIRE(total_tiles < (1ll << 31), "tcgen05 gemm: too many tiles");
+  const int sms = pd_num_sms();
+  dim3 grid((unsigned)(total_tiles < sms ? total_tiles : sms), 1, 1);
   gemm_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(ma, mb, p);
   PD_LAUNCH_CHECK("gemm_tcgen05_kernel");
   return PD_OK;

@@ -330,6 +330,193 @@ add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, 
     y[i] = pd_from_float<T>(pd_to_float(a[i]) + pd_to_float(b[i]));
 }
 
+
+// ---- bf16 x 8 (16-byte) variants of the hot layout kernels --------------------
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x; f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return v;
+}
+__device__ __forceinline__ uint4 max8(const uint4& a, const uint4& b) {
+  uint4 r;
+  const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&b);
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = __hmax2(x[j], y[j]);
+  return r;
+}
+
+// padded NHWC -> padded NHWC, 8 channels per thread
+__global__ void __launch_bounds__(kThreads)
+maxpool2_fwd_bf16x8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int W, uint4* __restrict__ y) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const int64_t total = (int64_t)N * Hop * Wop * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int wo = (int)(p % Wop), ho = (int)((p / Wop) % Hop), n = (int)(p / ((int64_t)Wop * Hop));
+    uint4 m = make_uint4(0, 0, 0, 0);
+    if (ho >= 1 && ho <= Ho && wo >= 1 && wo <= Wo) {
+      const uint4* b = x + (((int64_t)n * Hp + (2 * (ho - 1) + 1)) * Wp + (2 * (wo - 1) + 1)) * C8 + c;
+      m = max8(max8(b[0], b[C8]), max8(b[(int64_t)Wp * C8], b[(int64_t)Wp * C8 + C8]));
+    }
+    y[i] = m;
+  }
+}
+
+// One thread per (output window, 8 channels): reads the 2x2 window and dy once, writes the four
+// dx vectors.  The padded border of dx is written by the threads of the border windows.
+__global__ void __launch_bounds__(kThreads)
+maxpool2_bwd_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, int N, int C8, int H, int W,
+                           uint4* __restrict__ dx, int relu_mask) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  // windows cover padded rows/cols pairwise: window (i, j), i in [0, Ho], j in [0, Wo], owns padded pixels
+  // (2i, 2j) .. (2i+1, 2j+1); interior pooling windows are the pixels (2ho+1.., 2wo+1..), i.e. shifted by one,
+  // so here a thread is assigned to a pooling window (ho, wo) in [-1.., ..]: simpler to loop over pooling
+  // windows for the interior and let a second pass zero the border.
+  const int64_t total = (int64_t)N * Ho * Wo * C8;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
+    const int64_t base = (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C8 + c;
+    float v[4][8], g[8];
+    unpack8(x[base], v[0]);
+    unpack8(x[base + C8], v[1]);
+    unpack8(x[base + (int64_t)Wp * C8], v[2]);
+    unpack8(x[base + (int64_t)Wp * C8 + C8], v[3]);
+    unpack8(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C8 + c], g);
+    float o[4][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      int arg = 0; float m = v[0][k];
+      if (v[1][k] > m) { m = v[1][k]; arg = 1; }
+      if (v[2][k] > m) { m = v[2][k]; arg = 2; }
+      if (v[3][k] > m) { m = v[3][k]; arg = 3; }
+      const float gg = (relu_mask && !(m > 0.f)) ? 0.f : g[k];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o[q][k] = (q == arg) ? gg : 0.f;
+    }
+    dx[base] = pack8(o[0]);
+    dx[base + C8] = pack8(o[1]);
+    dx[base + (int64_t)Wp * C8] = pack8(o[2]);
+    dx[base + (int64_t)Wp * C8 + C8] = pack8(o[3]);
+  }
+  // border pixels (and odd trailing rows/cols, which no window covers) are zero
+  const int64_t border = (int64_t)N * Hp * Wp * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < border;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t p = i / C8;
+    const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp);
+    if (hp == 0 || wp == 0 || hp > 2 * Ho || wp > 2 * Wo) dx[i] = zero;
+  }
+}
+
+// dx = dy * (y > 0), 8 columns per thread, plus per-block column partial sums (C % 8 == 0, C8 <= kThreads).
+__global__ void __launch_bounds__(kThreads)
+relu_bwd_colsum_bf16x8_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ y, uint4* __restrict__ dx,
+                              int64_t rows, int C8, float* __restrict__ partial) {
+  extern __shared__ float sm[];   // [lanes][C8 * 8]
+  const int lanes = kThreads / C8;
+  const int lane = threadIdx.x / C8, c = threadIdx.x % C8;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (lane < lanes) {
+    for (int64_t r = (int64_t)blockIdx.x * lanes + lane; r < rows; r += (int64_t)gridDim.x * lanes) {
+      const int64_t i = r * C8 + c;
+      float g[8];
+      unpack8(dy[i], g);
+      if (y != nullptr) {
+        float yv[8];
+        unpack8(y[i], yv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) if (!(yv[k] > 0.f)) g[k] = 0.f;
+      }
+      if (dx != nullptr) dx[i] = pack8(g);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += g[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sm[(lane * C8 + c) * 8 + k] = acc[k];
+  }
+  __syncthreads();
+  const int C = C8 * 8;
+  for (int col = threadIdx.x; col < C; col += blockDim.x) {
+    float s = 0.f;
+    for (int l = 0; l < lanes; ++l) s += sm[l * C + col];
+    partial[(int64_t)blockIdx.x * C + col] = s;
+  }
+}
+
+// out[c] (+)= sum_b partial[b][c]; 32 columns per block, 8 row lanes per column.
+__global__ void __launch_bounds__(256)
+colsum_final_fast_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ out,
+                         int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (c < C)
+    for (int b = ty; b < nblocks; b += 8) s += partial[(int64_t)b * C + c];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    out[c] = accumulate ? out[c] + t : t;
+  }
+}
+
+// im2col for small C: one thread per padded pixel row, Kpad bf16 written as 16-byte vectors.
+template <typename S>
+__global__ void __launch_bounds__(kThreads)
+im2col3x3_rows_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                      int N, int C, int H, int W, int Kpad, __nv_bfloat16* __restrict__ dst) {
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t rows = (int64_t)N * Hp * Wp;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < rows;
+       p += (int64_t)gridDim.x * blockDim.x) {
+    const int wp = (int)(p % Wp);
+    const int hp = (int)((p / Wp) % Hp);
+    const int n = (int)(p / ((int64_t)Wp * Hp));
+    const bool inside = hp >= 1 && hp <= H && wp >= 1 && wp <= W;
+    uint4* out = reinterpret_cast<uint4*>(dst + p * Kpad);
+    for (int k0 = 0; k0 < Kpad; k0 += 8) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = k0 + j;
+        float v = 0.f;
+        if (inside && k < 9 * C) {
+          const int t = k / C, c = k - t * C;
+          const int h = hp - 1 + t / 3 - 1, w = wp - 1 + t % 3 - 1;
+          if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(src[n * sN + c * sC + h * sH + w * sW]);
+        }
+        f[j] = v;
+      }
+      out[k0 >> 3] = pack8(f);
+    }
+  }
+}
+
 }  // namespace
 
 #define PD_DISPATCH_T(dtype, ...)                                   \
@@ -387,6 +574,16 @@ PD_EXPORT int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t s
   cudaStream_t s = (cudaStream_t)stream;
   int64_t total = (int64_t)N * (H + 2) * (W + 2) * Kpad;
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && ((uintptr_t)dst % 16) == 0) {
+    const int64_t rows = (int64_t)N * (H + 2) * (W + 2);
+    const int g2 = grid_cap((rows + kThreads - 1) / kThreads, 16);
+    if (src_dtype == PD_F32)
+      im2col3x3_rows_kernel<float><<<g2, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (__nv_bfloat16*)dst);
+    else
+      im2col3x3_rows_kernel<__nv_bfloat16><<<g2, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (__nv_bfloat16*)dst);
+    PD_LAUNCH_CHECK("im2col3x3_rows_kernel");
+    return PD_OK;
+  }
   if (src_dtype == PD_F32 && dst_dtype == PD_F32)
     im2col3x3_kernel<float, float><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (float*)dst);
   else if (src_dtype == PD_F32 && dst_dtype == PD_BF16)
@@ -427,7 +624,7 @@ PD_EXPORT int pd_relu_bwd(const void* dy, const void* y, void* dx, int64_t n, in
 
 // workspace: at least pd_colsum_workspace_bytes(C) bytes of device memory.
 PD_EXPORT int64_t pd_colsum_workspace_bytes(int C) {
-  return (int64_t)pd_num_sms() * 4 * (int64_t)C * sizeof(float);
+  return (int64_t)pd_num_sms() * 4 * (int64_t)C * sizeof(float);   // >= blocks launched x C floats
 }
 
 PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_t rows, int C,
@@ -439,14 +636,25 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
   PD_REQUIRE(C <= kThreads ? (kThreads / C) * C * (int)sizeof(float) <= 48 * 1024 : true, "pd_relu_bwd_colsum: C too large");
   PD_REQUIRE(workspace_bytes >= pd_colsum_workspace_bytes(C), "pd_relu_bwd_colsum: workspace too small");
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_BF16 && (C % 8) == 0 && C / 8 <= kThreads && ((uintptr_t)dy % 16) == 0 &&
+      (y == nullptr || ((uintptr_t)y % 16) == 0) && (dx == nullptr || ((uintptr_t)dx % 16) == 0)) {
+    const int C8 = C / 8, lanes8 = kThreads / C8;
+    int g8 = grid_cap((rows + lanes8 - 1) / lanes8, 2);
+    relu_bwd_colsum_bf16x8_kernel<<<g8, kThreads, (size_t)lanes8 * C * sizeof(float), s>>>(
+        (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
+    PD_LAUNCH_CHECK("relu_bwd_colsum_bf16x8_kernel");
+    colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
+    PD_LAUNCH_CHECK("colsum_final_fast_kernel");
+    return PD_OK;
+  }
   int lanes = C <= kThreads ? kThreads / C : 1;
   int64_t want = (rows + lanes - 1) / lanes;
   int grid = grid_cap(want, 4);
   size_t smem = C <= kThreads ? (size_t)lanes * C * sizeof(float) : 0;
   PD_DISPATCH_T(dtype, relu_bwd_colsum_kernel<T><<<grid, kThreads, smem, s>>>((const T*)dy, (const T*)y, (T*)dx, rows, C, (float*)workspace);)
   PD_LAUNCH_CHECK("relu_bwd_colsum_kernel");
-  colsum_final_kernel<<<(C + kThreads - 1) / kThreads, kThreads, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
-  PD_LAUNCH_CHECK("colsum_final_kernel");
+  colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
+  PD_LAUNCH_CHECK("colsum_final_fast_kernel");
   return PD_OK;
 }
 
@@ -459,6 +667,12 @@ PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y
   cudaStream_t s = (cudaStream_t)stream;
   int64_t total = out_mode == 0 ? (int64_t)N * (H / 2 + 2) * (W / 2 + 2) * C : (int64_t)N * C * (H / 2) * (W / 2);
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  if (dtype == PD_BF16 && out_mode == 0 && (C % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
+    maxpool2_fwd_bf16x8_kernel<<<grid_cap((total / 8 + kThreads - 1) / kThreads, 16), kThreads, 0, s>>>(
+        (const uint4*)x, N, C / 8, H, W, (uint4*)y);
+    PD_LAUNCH_CHECK("maxpool2_fwd_bf16x8_kernel");
+    return PD_OK;
+  }
   PD_DISPATCH_T(dtype, maxpool2_fwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, N, C, H, W, (T*)y, out_mode);)
   PD_LAUNCH_CHECK("maxpool2_fwd_kernel");
   return PD_OK;
@@ -473,6 +687,14 @@ PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H
   cudaStream_t s = (cudaStream_t)stream;
   int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  if (dtype == PD_BF16 && dy_mode == 0 && (C % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)dy % 16) == 0 &&
+      ((uintptr_t)dx % 16) == 0) {
+    const int64_t win = (int64_t)N * (H / 2) * (W / 2) * (C / 8);
+    maxpool2_bwd_bf16x8_kernel<<<grid_cap((win + kThreads - 1) / kThreads, 16), kThreads, 0, s>>>(
+        (const uint4*)x, (const uint4*)dy, N, C / 8, H, W, (uint4*)dx, relu_mask);
+    PD_LAUNCH_CHECK("maxpool2_bwd_bf16x8_kernel");
+    return PD_OK;
+  }
   PD_DISPATCH_T(dtype, maxpool2_bwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)dy, N, C, H, W, (T*)dx, dy_mode, relu_mask);)
   PD_LAUNCH_CHECK("maxpool2_bwd_kernel");
   return PD_OK;
