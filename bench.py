@@ -294,6 +294,33 @@ def run_reference(steps, warmup, n_gpus):
     }
 
 
+def run_profile_case(name):
+    """A few launches of one convolution pass at one layer shape, for `ncu` captures of the
+    tensor-core kernel on a case that is larger than L2 but only a few hundred MB:
+    name = fwd|dgrad|wgrad : batch 64, 56x56, 256 -> 256 channels, bf16."""
+    from pipedream_b200 import functional as pf
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    N, H, W, Cin, Cout = 64, 56, 56, 256, 256
+    x = pf.pack_pnhwc(torch.randn(N, Cin, H, W, generator=g).cuda().to(torch.bfloat16))
+    dy = pf.pack_pnhwc(torch.randn(N, Cout, H, W, generator=g).cuda().to(torch.bfloat16))
+    w = (torch.randn(Cout, 9 * Cin, generator=g) * 0.02).cuda().to(torch.bfloat16)
+    bias = torch.zeros(Cout, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(Cout, 9 * Cin, device="cuda")
+    for _ in range(4):
+        if name == "fwd":
+            pf.conv2d_fwd(x, w, 9 * Cin, Cout, bias, True)
+        elif name == "dgrad":
+            pf.conv2d_dgrad(dy, w, 9 * Cin, Cin, relu_aux=x)
+        else:
+            pf.conv2d_wgrad(x, dy, dw, 9 * Cin, accumulate=False)
+    torch.cuda.synchronize()
+    assert pf.gemm_poll_error() == 0
+    flops = 18.0 * N * H * W * Cin * Cout
+    print(json.dumps({"case": name, "shape": [N, H, W, Cin, Cout], "algorithmic_flop_per_launch": flops,
+                      "algorithmic_bytes_per_launch": int(x.numel() * 2 + dy.numel() * 2 + w.numel() * 2)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -301,7 +328,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad"],
+                    help="run a few launches of one convolution pass (for ncu) and exit")
     a = ap.parse_args()
+    if a.profile_case:
+        run_profile_case(a.profile_case)
+        return
     if a.impl == "reference":
         out = run_reference(a.steps, a.warmup, a.gpus)
         if out is not None:

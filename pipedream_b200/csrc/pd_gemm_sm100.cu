@@ -109,6 +109,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
@@ -125,6 +127,119 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, int mn_major) 
   d |= (uint64_t)1 << 46;   // descriptor version for sm_100
   d |= (uint64_t)2 << 61;   // SWIZZLE_128B
   return d;
+}
+
+// Epilogue of one 32-column chunk of one accumulator row: bias, ReLU, masks, store / atomic add.
+__device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t* r, int m, int nb, long long out_col0,
+                                               bool border) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (p.bias != nullptr) {
+    const __nv_bfloat16* bb = (const __nv_bfloat16*)p.bias + nb;
+    if (p.bias_dtype == PD_BF16 && nb + 32 <= p.N && (((uintptr_t)bb) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 pk = __ldg(reinterpret_cast<const uint4*>(bb) + q);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[q * 8 + 2 * e] += f.x;
+          v[q * 8 + 2 * e + 1] += f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (nb + j < p.N)
+          v[j] += p.bias_dtype == PD_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.bias)[nb + j])
+                                          : ((const float*)p.bias)[nb + j];
+      }
+    }
+  }
+  if (p.relu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+  }
+  if (p.relu_aux != nullptr) {
+    if (p.out_dtype == PD_BF16) {
+      const __nv_bfloat16* ax = (const __nv_bfloat16*)p.relu_aux + (long long)m * p.ld_aux + nb;
+      if (nb + 32 <= p.N && (((uintptr_t)ax) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 pk = reinterpret_cast<const uint4*>(ax)[q];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            if (!(f.x > 0.f)) v[q * 8 + 2 * e] = 0.f;
+            if (!(f.y > 0.f)) v[q * 8 + 2 * e + 1] = 0.f;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < p.N && !(__bfloat162float(ax[j]) > 0.f)) v[j] = 0.f;
+      }
+    } else {
+      const float* ax = (const float*)p.relu_aux + (long long)m * p.ld_aux + nb;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N && !(ax[j] > 0.f)) v[j] = 0.f;
+    }
+  }
+  if (border) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+  }
+  const bool full = nb + 32 <= p.N;
+  if (p.atomic) {
+    float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
+    if (full && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(o + q * 4), "f"(v[q * 4]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                     : "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || nb + j < p.N) atomicAdd(o + j, v[j]);
+    }
+  } else if (p.out_dtype == PD_BF16) {
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)m * p.ldo + out_col0 + nb;
+    if (full && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2);
+        pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        reinterpret_cast<uint4*>(o)[q] = pk;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
+    if (full && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        reinterpret_cast<float4*>(o)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) o[j] = v[j];
+    }
+  }
 }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -198,6 +313,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ------------------------------ TMA producer ------------------------------
     // The whole warp walks the loop; lane 0 arms the barrier, lanes 0..boxes-1 each issue one box,
     // so the (up to six) box loads of a stage go out in one instruction slot.
+    // Two boxes per stage (both operands K-major): one lane issues both, nothing to coordinate.
+    if (!p.a_major && !p.b_major && p.acc_count == 1) {
+      if (lane == 0) {
+        uint32_t g = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+          PD_DECODE_TILE(tile)
+          (void)iters; (void)accn;
+          const int zrow = p.z_b_row[min(acc0, PD_MAX_TAPS - 1)];
+          for (int t = 0; t < p.num_taps && ok; ++t) {
+            const int ax = p.a_col0 + p.a_tap_col[t], ay = p.a_row0 + m0 + p.a_tap_row[t];
+            const int bx = p.b_col0 + p.b_tap_col[t], by = p.b_row0 + n0 + p.b_tap_row[t] + zrow;
+            for (int kb = kb_begin; kb < kb_begin + kbn; ++kb, ++g) {
+              const int s = (int)(g % (uint32_t)S);
+              const uint32_t ph = (g / (uint32_t)S) & 1u;
+              if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) { ok = false; break; }
+              const uint32_t fb = smem_u32(&full_bar[s]);
+              const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
+              mbar_expect_tx(fb, kABytes + b_bytes);
+              tma_load_2d(sa, &tma_a, fb, ax + kb * kBlockK, ay);
+              tma_load_2d(sa + kABytes, &tma_b, fb, bx + kb * kBlockK, by);
+            }
+          }
+        }
+      }
+    } else
     {
       const int a_boxes = p.a_major ? 2 : 1;
       const int b_boxes = p.b_major ? p.block_n / 64 : 1;
@@ -244,8 +385,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int kb = kb_begin; kb < kb_begin + kbn; ++kb, ++g) {
             const int s = (int)(g % (uint32_t)S);
             const uint32_t ph = (g / (uint32_t)S) & 1u;
-            ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1);
-            ok = __all_sync(0xffffffffu, ok);
+            if (lane == 0) ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) break;
             const uint32_t fb = smem_u32(&full_bar[s]);
             if (lane == 0) mbar_expect_tx(fb, tx);
@@ -319,93 +460,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
       const bool row_ok = m < p.M;
       const uint32_t tmem_acc = tmem_base + buf * acc_cols + ((uint32_t)(lg * 32) << 16);
-      for (int cc = 0; cc < accn * p.block_n; cc += 32) {
-        const int a = cc / p.block_n;
-        const int c0 = cc - a * p.block_n;
-        const long long out_col0 = (long long)(acc0 + a) * p.z_out_col;
-        const int nb = n0 + c0;
-        if (nb >= p.N) continue;              // warp-uniform
-        uint32_t r[32];
+      const int total_cols = accn * p.block_n;
+      for (int cc = 0; cc < total_cols; cc += 64) {
+        // two chunks in flight per wait
+        const bool two = cc + 32 < total_cols;
+        uint32_t r0[32], r1[32];
         __syncwarp();
-        tmem_ld32(tmem_acc + (uint32_t)cc, r);
-        if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (nb + j < p.N)
-              v[j] += p.bias_dtype == PD_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.bias)[nb + j])
-                                              : ((const float*)p.bias)[nb + j];
+        tmem_ld32(tmem_acc + (uint32_t)cc, r0);
+        if (two) tmem_ld32(tmem_acc + (uint32_t)(cc + 32), r1);
+        tmem_ld_wait();
+        if (row_ok) {
+          {
+            const int a = cc / p.block_n, c0 = cc - a * p.block_n;
+            if (n0 + c0 < p.N) epilogue_chunk(p, r0, m, n0 + c0, (long long)(acc0 + a) * p.z_out_col, border);
           }
-        }
-        if (p.relu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-        }
-        if (p.relu_aux != nullptr) {
-          if (p.out_dtype == PD_BF16) {
-            const __nv_bfloat16* ax = (const __nv_bfloat16*)p.relu_aux + (long long)m * p.ld_aux + nb;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N && !(__bfloat162float(ax[j]) > 0.f)) v[j] = 0.f;
-          } else {
-            const float* ax = (const float*)p.relu_aux + (long long)m * p.ld_aux + nb;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N && !(ax[j] > 0.f)) v[j] = 0.f;
-          }
-        }
-        if (border) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        }
-        const bool full = nb + 32 <= p.N;
-        if (p.atomic) {
-          float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
-          if (full && (((uintptr_t)o) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
-                           ::"l"(o + q * 4), "f"(v[q * 4]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
-                           : "memory");
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || nb + j < p.N) atomicAdd(o + j, v[j]);
-          }
-        } else if (p.out_dtype == PD_BF16) {
-          __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)m * p.ldo + out_col0 + nb;
-          if (full && (((uintptr_t)o) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 pk;
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]);
-              __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
-              __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
-              pk.x = *reinterpret_cast<uint32_t*>(&h0);
-              pk.y = *reinterpret_cast<uint32_t*>(&h1);
-              pk.z = *reinterpret_cast<uint32_t*>(&h2);
-              pk.w = *reinterpret_cast<uint32_t*>(&h3);
-              reinterpret_cast<uint4*>(o)[q] = pk;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
-          }
-        } else {
-          float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
-          if (full && (((uintptr_t)o) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              reinterpret_cast<float4*>(o)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) o[j] = v[j];
+          if (two) {
+            const int a = (cc + 32) / p.block_n, c0 = cc + 32 - a * p.block_n;
+            if (n0 + c0 < p.N) epilogue_chunk(p, r1, m, n0 + c0, (long long)(acc0 + a) * p.z_out_col, border);
           }
         }
       }

@@ -77,6 +77,9 @@ class _Conv3x3Fn(torch.autograd.Function):
         ctx.weight_param = weight
         ctx.bias_param = bias
         ctx.geom = (N, Cin, H, W, Cout)
+        # x is the output of a fused conv+ReLU: this layer's data gradient can apply that ReLU's
+        # mask in its epilogue and save the producer a pass over the gradient
+        ctx.premask = bool(getattr(x, "_pd_relu_out", False)) and ctx.direct
         if ctx.direct:
             x_pad = pf.as_padded(x, w.dtype)
             y_pad = pf.conv2d_fwd(x_pad, w, w.stride(0), Cout, b, fuse_relu)
@@ -86,7 +89,7 @@ class _Conv3x3Fn(torch.autograd.Function):
             col = pf.im2col3x3(x, kpad, w.dtype)
             y2d = pf.gemm_nt(col, _dense2d(w, Cout, kpad), bias=b, relu=fuse_relu, pad_hw=(H + 2, W + 2))
             y_pad = y2d.view(N, H + 2, W + 2, Cout)
-            ctx.x_saved = x      # the patch matrix is rebuilt in backward
+            ctx.x_saved = col    # the patch matrix (a few hundred MB at most) is kept for the weight gradient
         ctx.y_pad = y_pad if fuse_relu else None
         if out_nchw:
             return pf.unpack_pnhwc(y_pad)
@@ -101,8 +104,13 @@ class _Conv3x3Fn(torch.autograd.Function):
         # saved tensor aliases the parameter storage.
         w = wp.detach()
         dy_pad = pf.as_padded(dy, w.dtype)
-        # ReLU mask and bias gradient in one pass over dy
-        if ctx.fuse_relu:
+        # ReLU mask and bias gradient in one pass over dy; if the consumer's backward already applied
+        # this layer's mask (see ctx.premask), only the bias gradient is left to do
+        if ctx.fuse_relu and getattr(dy, "_pd_premasked", False) and pf.padded_of(dy) is not None:
+            dym = dy_pad
+            if bp is not None:
+                pf.relu_bwd_colsum(dy_pad, None, None, grad_buffer(bp), take_accumulate_flag(bp))
+        elif ctx.fuse_relu:
             dym = torch.empty_like(dy_pad)
             if bp is not None:
                 pf.relu_bwd_colsum(dy_pad, ctx.y_pad, dym, grad_buffer(bp), take_accumulate_flag(bp))
@@ -118,12 +126,13 @@ class _Conv3x3Fn(torch.autograd.Function):
             x_pad = ctx.x_saved
             pf.conv2d_wgrad(x_pad, dym, gw, gw.stride(0), accumulate=take_accumulate_flag(wp))
             if ctx.needs_input_grad[0]:
-                dx_pad = pf.conv2d_dgrad(dym, w, w.stride(0), Cin)
+                dx_pad = pf.conv2d_dgrad(dym, w, w.stride(0), Cin, relu_aux=x_pad if ctx.premask else None)
                 dx = pf.nchw_view(dx_pad, N, Cin, H, W)
+                if ctx.premask:
+                    dx._pd_premasked = True
         else:
             kpad = w.stride(0)
-            col = pf.im2col3x3(ctx.x_saved, kpad, w.dtype)
-            pf.gemm_tn(dym.view(-1, Cout), col, _dense2d(gw, Cout, kpad), accumulate=take_accumulate_flag(wp))
+            pf.gemm_tn(dym.view(-1, Cout), ctx.x_saved, _dense2d(gw, Cout, kpad), accumulate=take_accumulate_flag(wp))
             if ctx.needs_input_grad[0]:
                 raise NotImplementedError("input gradient of a convolution with Cin %% 64 != 0 is not implemented")
         return dx, None, None, None, None
@@ -162,7 +171,10 @@ class NativeConv2d(nn.Module):
                 and (conv.in_channels % 64 == 0 or conv.in_channels < 8))
 
     def forward(self, x):
-        return _Conv3x3Fn.apply(x, self.weight, self.bias, self.fuse_relu, self.out_nchw)
+        y = _Conv3x3Fn.apply(x, self.weight, self.bias, self.fuse_relu, self.out_nchw)
+        if self.fuse_relu and not self.out_nchw:
+            y._pd_relu_out = True      # consumers may fold this ReLU's mask into their data gradient
+        return y
 
     def extra_repr(self):
         return "%d, %d, kernel_size=(3, 3), stride=(1, 1), padding=(1, 1), fuse_relu=%s" % (
@@ -220,6 +232,7 @@ class _MaxPool2Fn(torch.autograd.Function):
         x_pad = pf.as_padded(x)
         ctx.x_pad = x_pad
         ctx.geom = (N, C, H, W)
+        ctx.premask = bool(getattr(x, "_pd_relu_out", False))
         y = pf.maxpool2_fwd(x_pad, out_nchw)
         return y if out_nchw else pf.nchw_view(y, N, C, H // 2, W // 2)
 
@@ -228,11 +241,14 @@ class _MaxPool2Fn(torch.autograd.Function):
         N, C, H, W = ctx.geom
         dy_pad = pf.padded_of(dy)
         if dy_pad is not None:
-            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dy_pad, False, False)
+            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dy_pad, False, ctx.premask)
         else:
             dyc = dy if dy.is_contiguous() else dy.contiguous()
-            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dyc, True, False)
-        return pf.nchw_view(dx_pad, N, C, H, W), None
+            dx_pad = pf.maxpool2_bwd(ctx.x_pad, dyc, True, ctx.premask)
+        dx = pf.nchw_view(dx_pad, N, C, H, W)
+        if ctx.premask:
+            dx._pd_premasked = True
+        return dx, None
 
 
 class NativeMaxPool2d(nn.Module):
