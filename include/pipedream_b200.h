@@ -125,6 +125,9 @@ int64_t pd_softmax_ce_static_max_rows(void);
 int pd_revert_varlen(const void* in, void* out, const int64_t* lengths, int T, int B,
                      int64_t feature_bytes, void* stream);
 int pd_length_mask(const int64_t* lengths, int T, int B, void* mask, int mask_dtype, void* stream);
+/* y[r,:] = x[r,:] * mask[r] (mask in the tensor's dtype): `model0(input)[0] * mask` of
+ * runtime/translation/seq2seq/models/encoder.py:51,55.                                          */
+int pd_mul_rows(const void* x, const void* mask, void* y, int64_t rows, int F, int dtype, void* stream);
 /* torch.nn.Embedding(padding_idx=0) of runtime/translation/models/gnmt_large/gpus=4/stage0.py:10 */
 int pd_embedding_fwd(const int64_t* ids, const void* table, int64_t n, int D, int64_t vocab,
                      void* out, int dtype, void* stream);
@@ -163,6 +166,20 @@ int pd_conv2d_dgrad(int dtype, const void* dy_pad, int N, int H, int W, int Cout
                     int64_t ldw, int Cin, const void* relu_aux, void* dx_pad, void* stream);
 int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int H, int W, int Cin,
                     int Cout, float* dw, int64_t lddw, int accumulate, int split_k, void* stream);
+/* torch.nn.LSTM(I, H), one layer, one direction, [T,B,*] sequences (runtime/translation/models/
+ * gnmt_large/gpus=4/stage0.py:11-19; the reference reaches cuDNN's RNN through it): the time loop.
+ * The caller computes the input projections gx = x . W_ih^T + b_ih for all steps with pd_gemm_nt;
+ * pd_lstm_fwd then runs, per step, h_{t-1} . W_hh^T on the tensor cores and a fused cell kernel
+ * (gate order i,f,g,o; cell state kept in fp32; zero initial state), saving gate activations `act`
+ * [T,B,4H] and cell states `c_all` [T,B,H] (fp32).  pd_lstm_bwd walks back through time and
+ * produces the gate pre-activation gradients `dgates` [T,B,4H]; dx, dW_ih, dW_hh and the bias
+ * gradients are then pd_gemm_nn / pd_gemm_tn / pd_relu_bwd_colsum calls over dgates.
+ * gh_ws [B,4H], dh_ws and dc_ws [B,H]: fp32 scratch provided by the caller.                      */
+int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const void* b_hh, int T, int B, int H,
+                void* y, void* act, float* c_all, float* gh_ws, void* stream);
+int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all,
+                int T, int B, int H, void* dgates, float* dh_ws, float* dc_ws, void* stream);
+
 /* Reads and clears the error word the tcgen05 kernels set when a bounded wait runs out
  * (0 = none).  `code` is a HOST pointer; synchronises the device.                            */
 int pd_gemm_poll_error(int* code);

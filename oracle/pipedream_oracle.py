@@ -535,3 +535,33 @@ def cross_entropy_loss(logits, target):
     mx = x.max(axis=1, keepdims=True)
     logp = x - mx - np.log(np.exp(x - mx).sum(axis=1, keepdims=True))
     return float(-np.mean([logp[r, t] for r, t in enumerate(target)]))
+
+
+# --------------------------------------------------------------------------- #
+# LSTM layer and additive attention as explicit tensor arithmetic
+# --------------------------------------------------------------------------- #
+def lstm_layer(x, w_ih, w_hh, b_ih, b_hh):
+    """torch.nn.LSTM(I, H) forward (one layer, one direction, zero initial state, gate order i,f,g,o)
+    written out step by step; x: [T,B,I].  What the translation stages run through cuDNN in the
+    reference (runtime/translation/models/gnmt_large/gpus=4/stage0.py:11-19)."""
+    T, B, _ = x.shape
+    H = w_hh.shape[1]
+    h = x.new_zeros(B, H)
+    c = x.new_zeros(B, H)
+    ys = []
+    for t in range(T):
+        gates = x[t] @ w_ih.t() + b_ih + h @ w_hh.t() + b_hh
+        i, f, g, o = gates.split(H, dim=1)
+        i, f, g, o = torch.sigmoid(i), torch.sigmoid(f), torch.tanh(g), torch.sigmoid(o)
+        c = f * c + i * g
+        h = o * torch.tanh(c)
+        ys.append(h)
+    return torch.stack(ys, 0)
+
+
+def bahdanau_scores(pq, pk, linear_att, normalize_scalar, normalize_bias):
+    """Normalised additive attention scores (runtime/translation/seq2seq/models/attention.py:84-114):
+    pq [b,tq,n], pk [b,tk,n] -> [b,tq,tk]."""
+    v = linear_att / linear_att.norm() * normalize_scalar
+    s = torch.tanh(pq.unsqueeze(2) + pk.unsqueeze(1) + normalize_bias)
+    return (s * v).sum(-1)

@@ -50,6 +50,7 @@ SIGNATURES = {
     "pd_softmax_ce_static_max_rows": (L, []),
     "pd_revert_varlen": (I, [P, P, P, I, I, L, P]),
     "pd_length_mask": (I, [P, I, I, P, I, P]),
+    "pd_mul_rows": (I, [P, P, P, L, I, I, P]),
     "pd_embedding_fwd": (I, [P, P, L, I, L, P, I, P]),
     "pd_embedding_bwd": (I, [P, P, L, I, L, L, P, I, P]),
     "pd_gemm_nt": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, I, I, P]),
@@ -58,6 +59,8 @@ SIGNATURES = {
     "pd_conv2d_fwd": (I, [I, P, I, I, I, I, P, L, I, P, I, I, P, P]),
     "pd_conv2d_dgrad": (I, [I, P, I, I, I, I, P, L, I, P, P, P]),
     "pd_conv2d_wgrad": (I, [I, P, P, I, I, I, I, I, P, L, I, I, P]),
+    "pd_lstm_fwd": (I, [I, P, P, P, I, I, I, P, P, P, P, P]),
+    "pd_lstm_bwd": (I, [I, P, P, P, P, I, I, I, P, P, P, P]),
     "pd_gemm_poll_error": (I, [POINTER(c_int)]),
     "pd_chan_create": (I, [L, I, I, POINTER(c_void_p)]),
     "pd_chan_export_handle": (I, [P, P]),

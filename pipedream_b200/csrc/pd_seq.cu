@@ -41,6 +41,15 @@ length_mask_kernel(const int64_t* __restrict__ lengths, int Tn, int B, T* __rest
   }
 }
 
+// y[r, :] = x[r, :] * mask[r]
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+mul_rows_kernel(const T* __restrict__ x, const T* __restrict__ mask, T* __restrict__ y, int64_t rows, int F) {
+  const int64_t total = rows * F;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = pd_from_float<T>(pd_to_float(x[i]) * pd_to_float(mask[i / F]));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 embedding_fwd_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table, int64_t n, int D,
@@ -131,5 +140,22 @@ PD_EXPORT int pd_embedding_bwd(const int64_t* ids, const void* dy, int64_t n, in
   else if (dtype == PD_BF16) embedding_bwd_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(ids, (const __nv_bfloat16*)dy, n, D, vocab, padding_idx, dtable);
   else PD_REQUIRE(false, "pd_embedding_bwd: bad dtype");
   PD_LAUNCH_CHECK("embedding_bwd_kernel");
+  return PD_OK;
+}
+
+
+// y[r,:] = x[r,:] * mask[r]: the length mask applied to the forward half of the bidirectional encoder
+// layer (runtime/translation/seq2seq/models/encoder.py:51,55).
+PD_EXPORT int pd_mul_rows(const void* x, const void* mask, void* y, int64_t rows, int F, int dtype, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && mask && y && rows > 0 && F > 0, "pd_mul_rows: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  int64_t blocks = (rows * F + kThreads - 1) / kThreads;
+  int grid = (int)(blocks < (int64_t)pd_num_sms() * 16 ? blocks : (int64_t)pd_num_sms() * 16);
+  if (dtype == PD_F32) mul_rows_kernel<float><<<grid, kThreads, 0, s>>>((const float*)x, (const float*)mask, (float*)y, rows, F);
+  else if (dtype == PD_BF16) mul_rows_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)mask, (__nv_bfloat16*)y, rows, F);
+  else PD_REQUIRE(false, "pd_mul_rows: bad dtype");
+  PD_LAUNCH_CHECK("mul_rows_kernel");
   return PD_OK;
 }

@@ -368,6 +368,15 @@ def length_mask(lengths, T, dtype):
     return out
 
 
+def mul_rows(x, mask):
+    """y[r,:] = x[r,:] * mask[r]; x: [..., F] contiguous, mask: x.shape[:-1] in x's dtype."""
+    _cuda(x, mask)
+    F = x.shape[-1]
+    y = torch.empty_like(x)
+    call("pd_mul_rows", _p(x), _p(mask), _p(y), x.numel() // F, F, dt(x), _stream())
+    return y
+
+
 def embedding_fwd(ids, table):
     _cuda(ids, table)
     vocab, D = table.shape
@@ -380,3 +389,29 @@ def embedding_bwd(ids, dy, dtable, padding_idx):
     vocab, D = dtable.shape
     call("pd_embedding_bwd", _p(ids), _p(dy), ids.numel(), D, vocab, int(padding_idx), _p(dtable), dt(dy), _stream())
     return dtable
+
+
+# --------------------------------------------------------------------------- #
+# LSTM time loops
+# --------------------------------------------------------------------------- #
+def lstm_fwd(gx, w_hh, b_hh, T, B, H):
+    """gx: [T*B, 4H] input projections (+ b_ih).  Returns (y [T,B,H], act [T,B,4H], c_all [T,B,H] fp32)."""
+    _cuda(gx, w_hh)
+    dev, dtype = gx.device, gx.dtype
+    y = torch.empty((T, B, H), dtype=dtype, device=dev)
+    act = torch.empty((T, B, 4 * H), dtype=dtype, device=dev)
+    c_all = torch.empty((T, B, H), dtype=torch.float32, device=dev)
+    gh_ws = torch.empty((B, 4 * H), dtype=torch.float32, device=dev)
+    call("pd_lstm_fwd", dt(gx), _p(gx), _p(w_hh), _p(b_hh), T, B, H, _p(y), _p(act), _p(c_all), _p(gh_ws), _stream())
+    return y, act, c_all
+
+
+def lstm_bwd(dy, w_hh, act, c_all):
+    """dy: [T,B,H] contiguous.  Returns dgates [T,B,4H] (gate pre-activation gradients)."""
+    T, B, H = dy.shape
+    dgates = torch.empty((T, B, 4 * H), dtype=dy.dtype, device=dy.device)
+    dh_ws = torch.empty((B, H), dtype=torch.float32, device=dy.device)
+    dc_ws = torch.empty((B, H), dtype=torch.float32, device=dy.device)
+    call("pd_lstm_bwd", dt(dy), _p(dy), _p(w_hh), _p(act), _p(c_all), T, B, H, _p(dgates), _p(dh_ws), _p(dc_ws),
+         _stream())
+    return dgates

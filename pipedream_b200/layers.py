@@ -370,6 +370,178 @@ class NativeLinear(nn.Module):
         return "in_features=%d, out_features=%d, fuse_relu=%s" % (self.in_features, self.out_features, self.fuse_relu)
 
 
+
+# --------------------------------------------------------------------------- #
+# LSTM (one layer, one direction, sequence first)
+# --------------------------------------------------------------------------- #
+class _LSTMFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_ih, w_hh, b_ih, b_hh):
+        wi, wh = w_ih.detach(), w_hh.detach()
+        T, B, I = x.shape
+        H = wh.shape[1]
+        x2 = x.reshape(T * B, I)
+        if x2.dtype != wi.dtype:
+            x2 = pf.convert(x2.contiguous(), wi.dtype)
+        elif not x2.is_contiguous():
+            x2 = x2.contiguous()
+        gx = pf.gemm_nt(x2, wi, bias=b_ih.detach() if b_ih is not None else None)
+        y, act, c_all = pf.lstm_fwd(gx, wh, b_hh.detach() if b_hh is not None else None, T, B, H)
+        ctx.saved = (x2, y, act, c_all)
+        ctx.params = (w_ih, w_hh, b_ih, b_hh)
+        ctx.geom = (T, B, I, H)
+        ctx.x_dtype = x.dtype
+        ctx.c_last = c_all[T - 1]
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, y, act, c_all = ctx.saved
+        w_ih, w_hh, b_ih, b_hh = ctx.params
+        T, B, I, H = ctx.geom
+        wi, wh = w_ih.detach(), w_hh.detach()      # weights loaded at backward time
+        dyc = dy
+        if dyc.dtype != wi.dtype:
+            dyc = pf.convert(dyc.contiguous(), wi.dtype)
+        elif not dyc.is_contiguous():
+            dyc = dyc.contiguous()
+        dgates = pf.lstm_bwd(dyc, wh, act, c_all)
+        dg2 = dgates.view(T * B, 4 * H)
+        pf.gemm_tn(dg2, x2, grad_buffer(w_ih), accumulate=take_accumulate_flag(w_ih))
+        ghh = grad_buffer(w_hh)
+        acc_hh = take_accumulate_flag(w_hh)
+        if T > 1:
+            pf.gemm_tn(dg2[B:], y.view(T * B, H)[:(T - 1) * B], ghh, accumulate=acc_hh)
+        elif not acc_hh:
+            ghh.zero_()
+        for bp in (b_ih, b_hh):
+            if bp is not None:
+                pf.relu_bwd_colsum(dg2, None, None, grad_buffer(bp), take_accumulate_flag(bp))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = pf.gemm_nn(dg2, wi).view(T, B, I)
+            if dx.dtype != ctx.x_dtype:
+                dx = pf.convert(dx, ctx.x_dtype)
+        return dx, None, None, None, None
+
+
+class NativeLSTM(nn.Module):
+    """torch.nn.LSTM(input_size, hidden_size): one layer, one direction, [T,B,*] input, zero initial state."""
+
+    def __init__(self, lstm):
+        super().__init__()
+        self.input_size, self.hidden_size = lstm.input_size, lstm.hidden_size
+        self.weight_ih_l0 = lstm.weight_ih_l0
+        self.weight_hh_l0 = lstm.weight_hh_l0
+        self.bias_ih_l0 = lstm.bias_ih_l0 if lstm.bias else None
+        self.bias_hh_l0 = lstm.bias_hh_l0 if lstm.bias else None
+        _mark_native(self.weight_ih_l0, self.weight_hh_l0, self.bias_ih_l0, self.bias_hh_l0)
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.LSTM) and m.num_layers == 1 and not m.bidirectional and not m.batch_first
+                and getattr(m, "proj_size", 0) == 0 and m.input_size % 8 == 0 and m.hidden_size % 8 == 0)
+
+    def forward(self, x, hx=None):
+        if hx is not None:
+            raise NotImplementedError("NativeLSTM starts from a zero state (the stage modules pass None)")
+        y = _LSTMFn.apply(x, self.weight_ih_l0, self.weight_hh_l0, self.bias_ih_l0, self.bias_hh_l0)
+        with torch.no_grad():
+            h_n = y.detach()[-1:]
+        return y, (h_n, None)
+
+    def extra_repr(self):
+        return "%d, %d" % (self.input_size, self.hidden_size)
+
+
+class _RevertVarlenFn(torch.autograd.Function):
+    """Per-sequence time reversal (its own inverse, so also its own gradient):
+    runtime/translation/seq2seq/models/encoder.py:13-21."""
+
+    @staticmethod
+    def forward(ctx, x, lengths):
+        ctx.lengths = lengths
+        return pf.revert_varlen(x, lengths)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return pf.revert_varlen(dy, ctx.lengths), None
+
+
+class _MaskRowsFn(torch.autograd.Function):
+    """y[t,b,:] = x[t,b,:] * (t < len[b])."""
+
+    @staticmethod
+    def forward(ctx, x, lengths):
+        T, B = x.shape[0], x.shape[1]
+        mask = pf.length_mask(lengths, T, x.dtype)
+        ctx.mask = mask
+        return pf.mul_rows(x if x.is_contiguous() else x.contiguous(), mask)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return pf.mul_rows(dy if dy.is_contiguous() else dy.contiguous(), ctx.mask), None
+
+
+class NativeEmuBidirLSTM(nn.Module):
+    """Bidirectional first encoder layer built from two one-direction LSTMs, the second one run on the
+    per-sequence time-reversed input (runtime/translation/seq2seq/models/encoder.py:25-64, the path taken
+    for batches of at most 128).  Keeps the attribute layout `bidir`, `layer1`, `layer2` of the module it
+    replaces, so parameter names do not change."""
+
+    def __init__(self, emu):
+        super().__init__()
+        self.bidir = emu.bidir                 # owns the parameters under their bidirectional names
+        self.layer1 = NativeLSTM(emu.layer1)
+        self.layer2 = NativeLSTM(emu.layer2)
+
+    @staticmethod
+    def supports(m):
+        return (type(m).__name__ == "EmuBidirLSTM" and all(hasattr(m, a) for a in ("bidir", "layer1", "layer2"))
+                and NativeLSTM.supports(m.layer1) and NativeLSTM.supports(m.layer2))
+
+    def forward(self, input, lengths):
+        lengths = lengths.to(device=input.device, dtype=torch.int64)
+        rev_in = _RevertVarlenFn.apply(input, lengths)
+        out_rev = _RevertVarlenFn.apply(self.layer2(rev_in)[0], lengths)
+        out_fwd = _MaskRowsFn.apply(self.layer1(input)[0], lengths)
+        return torch.cat([out_fwd, out_rev], dim=2)
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, padding_idx):
+        w = weight.detach()
+        idc = ids if ids.is_contiguous() else ids.contiguous()
+        ctx.ids, ctx.weight_param, ctx.padding_idx = idc, weight, padding_idx
+        return pf.embedding_fwd(idc, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        wp = ctx.weight_param
+        g = grad_buffer(wp)
+        if not take_accumulate_flag(wp):
+            g.zero_()
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        pf.embedding_bwd(ctx.ids, dyc, g, ctx.padding_idx if ctx.padding_idx is not None else -1)
+        return None, None, None
+
+
+class NativeEmbedding(nn.Module):
+    def __init__(self, emb):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim, self.padding_idx = emb.num_embeddings, emb.embedding_dim, emb.padding_idx
+        self.weight = emb.weight
+        _mark_native(self.weight)
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.Embedding) and m.max_norm is None and not m.scale_grad_by_freq and not m.sparse
+                and m.embedding_dim % 8 == 0)
+
+    def forward(self, ids):
+        return _EmbeddingFn.apply(ids, self.weight, self.padding_idx)
+
 # --------------------------------------------------------------------------- #
 # criteria
 # --------------------------------------------------------------------------- #
@@ -421,10 +593,13 @@ class NativeLabelSmoothing(nn.Module):
 # stage rewriting
 # --------------------------------------------------------------------------- #
 _LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway)
+_NATIVE_TYPES = _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
+                                 NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding)
 
 
 def _swap_leaf(m):
-    if isinstance(m, _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing)):
+    if isinstance(m, _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
+                                      NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding)):
         return m
     if NativeConv2d.supports(m):
         return NativeConv2d(m)
@@ -434,6 +609,12 @@ def _swap_leaf(m):
         return NativeMaxPool2d()
     if NativeLinear.supports(m):
         return NativeLinear(m)
+    if NativeLSTM.supports(m):
+        return NativeLSTM(m)
+    if NativeEmuBidirLSTM.supports(m):
+        return NativeEmuBidirLSTM(m)
+    if NativeEmbedding.supports(m):
+        return NativeEmbedding(m)
     if isinstance(m, nn.Dropout):
         return NativeDropout(m.p)
     if NativeCrossEntropyLoss.supports(m):
@@ -455,9 +636,14 @@ def nativize(module):
     single = _swap_leaf(module)
     if single is not module:
         return single
-    names = [n for n, _ in module.named_children()]
-    for n in names:
-        setattr(module, n, _swap_leaf(getattr(module, n)))
+    def swap_children(parent):
+        for n, child in list(parent.named_children()):
+            new = _swap_leaf(child)
+            if new is not child:
+                setattr(parent, n, new)
+            elif not isinstance(child, _NATIVE_TYPES) and any(True for _ in child.children()):
+                swap_children(child)        # a container (e.g. an attention block): look inside
+    swap_children(module)
     try:
         import torch.fx as fx
 

@@ -173,3 +173,79 @@ class SyntheticImages:
             if self.pin:
                 x, y = x.pin_memory(), y.pin_memory()
             yield x, y
+
+
+# --------------------------------------------------------------------------- #
+# translation: the 8+8-layer GNMT ("gnmt_large"), 4-stage partitioning
+# --------------------------------------------------------------------------- #
+class GnmtPackage:
+    """Stage package of runtime/translation/models/gnmt_large/gpus=4/__init__.py: four stages whose
+    boundary tensors are named as there (out0, out1, out12, out13, out14, out15, out12again, out18)."""
+
+    def __init__(self, hidden=1024, vocab=32320, dropout=0.2, stage_to_rank_map=None):
+        self.hidden, self.vocab, self.dropout = hidden, vocab, dropout
+        ranks = stage_to_rank_map or {s: [s] for s in range(4)}
+        self.conf = {"module_to_stage_map": [0, 1, 2, 3, 3], "stage_to_rank_map": ranks}
+
+    def arch(self):
+        return "gnmt_large"
+
+    def stages(self):
+        from . import gnmt_blocks as gb
+        h, v, p = self.hidden, self.vocab, self.dropout
+        return [gb.GnmtStage0(h, v, p), gb.GnmtStage1(h, v, p), gb.GnmtStage2(h, p), gb.GnmtStage3(h, v, p)]
+
+    def model(self, criterion):
+        s = self.stages()
+        return [
+            (s[0], ["input0", "input1"], ["out0", "out1"]),
+            (s[1], ["out0", "input1", "out1", "input2"], ["out12", "out13"]),
+            (s[2], ["out12", "out13"], ["out14", "out15", "out12again"]),
+            (s[3], ["out12again", "out14", "out15"], ["out18"]),
+            (criterion, ["out18"], ["loss"]),
+        ]
+
+    def full_model(self):
+        return torch.nn.ModuleList(self.stages())
+
+
+def gnmt_large(hidden=1024, vocab=32320, dropout=0.2, stage_to_rank_map=None):
+    return GnmtPackage(hidden, vocab, dropout, stage_to_rank_map)
+
+
+class SyntheticTranslation:
+    """Iterable of ((src, src_len), (tgt, tgt_len)) batches in the collate format of the reference's
+    loader (runtime/translation/seq2seq/data/dataset.py:54-61): [T,B] int64 token matrices, BOS first,
+    EOS last, PAD=0 beyond the length, batch sorted by source length (descending).  Lengths are uniform in
+    [min_len, max_len]; token ids follow a Zipf(s=1.1) rank distribution mapped onto ids 4..vocab_used-1
+    (stands in for WMT En-De, which is not available)."""
+
+    PAD, UNK, BOS, EOS = 0, 1, 2, 3
+
+    def __init__(self, batch, steps, seed=4321, min_len=20, max_len=50, vocab_used=32000, zipf_s=1.1):
+        self.batch, self.steps, self.seed = batch, steps, seed
+        self.min_len, self.max_len, self.vocab_used = min_len, max_len, vocab_used
+        ranks = torch.arange(1, vocab_used - 4 + 1, dtype=torch.float64)
+        self.weights = ranks.pow(-zipf_s)
+
+    def __len__(self):
+        return self.steps
+
+    def _side(self, lengths, g):
+        T, B = int(lengths.max()), len(lengths)
+        ids = torch.multinomial(self.weights, T * B, replacement=True, generator=g).view(T, B) + 4
+        out = torch.zeros(T, B, dtype=torch.int64)
+        for b, L in enumerate(lengths.tolist()):
+            out[:L, b] = ids[:L, b]
+            out[0, b] = self.BOS
+            out[L - 1, b] = self.EOS
+        return out
+
+    def __iter__(self):
+        for step in range(self.steps):
+            g = torch.Generator().manual_seed(self.seed + step)
+            src_len = torch.randint(self.min_len, self.max_len + 1, (self.batch,), generator=g)
+            tgt_len = torch.randint(self.min_len, self.max_len + 1, (self.batch,), generator=g)
+            order = torch.argsort(src_len, descending=True, stable=True)
+            src_len, tgt_len = src_len[order], tgt_len[order]
+            yield (self._side(src_len, g), src_len.tolist()), (self._side(tgt_len, g), tgt_len.tolist())

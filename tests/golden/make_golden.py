@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted (default /root/reference):
 
-    python tests/golden/make_golden.py [--ref /root/reference] [--only routing|stashing|vgg16]
+    python tests/golden/make_golden.py [--ref /root/reference] [--only routing|stashing|vgg16|gnmt]
 
 It imports the reference's runtime/ modules unmodified and records what they compute:
 
@@ -12,6 +12,8 @@ It imports the reference's runtime/ modules unmodified and records what they com
   stashing_golden.json  the weight-stashing truth table (runtime/tests/backprop/
                         sgd_with_stashing.py:57-70), per-stage version traces of the 1F1B loop
                         (runtime/optimizer.py), and a small SGD/Adam parameter trajectory
+  gnmt_large_golden.json  3 minibatches of the 8+8-layer GNMT stage modules with LabelSmoothing and
+                        AdamWithWeightStashing on CPU: losses, boundary-tensor and parameter checksums
   vgg16_cfg1_golden.json  20 minibatches of the 2-stage VGG-16 pipeline (cut after conv4_3) on two
                         gloo CPU ranks: per-minibatch loss, parameter checksums, version trace
 
@@ -362,6 +364,73 @@ def make_vgg16(ref, steps=20, batch=8):
     print("wrote vgg16_cfg1_golden.json; reference took %.1f s" % gold["reference_cpu_seconds"])
 
 
+# ----------------------------------------------------------------------------- GNMT (8+8 layers)
+def make_gnmt(ref, steps=3, batch=8):
+    """The reference's gnmt_large stage modules (4 stages run back to back in one process), its
+    LabelSmoothing criterion and AdamWithWeightStashing, on CPU.  The reference's pack_utils CUDA
+    extension does not build against current PyTorch; a pure-torch stand-in with the semantics of
+    csrc/pack_utils_kernel.cu:24-63 and pack_utils.cpp:13-31 is injected in its place."""
+    import types
+    _shim_cpu()
+    _import_reference(ref, "translation")
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from pipedream_b200.gnmt_blocks import _revert_varlen_torch
+    from pipedream_b200.stages import SyntheticTranslation
+    stub, c = types.ModuleType("pack_utils"), types.ModuleType("pack_utils._C")
+    c.revert_varlen_tensor = lambda x, lengths: _revert_varlen_torch(x, lengths)
+
+    def set_mask_cpp(lengths):
+        T = int(lengths[0])
+        return (torch.arange(T).unsqueeze(1) < lengths.unsqueeze(0)).to(torch.uint8)
+    c.set_mask_cpp = set_mask_cpp
+    stub._C = c
+    sys.modules["pack_utils"], sys.modules["pack_utils._C"] = stub, c
+    import adam as ref_adam
+    from seq2seq.train.smoothing import LabelSmoothing
+    torch.manual_seed(0)
+    module = importlib.import_module("models.gnmt_large.gpus=4")
+    model = module.model(LabelSmoothing(0, 0.1))
+    stages_ = [m for (m, _, _) in model[:-1]]
+    for m in stages_:
+        for sub in m.modules():
+            if isinstance(sub, torch.nn.Dropout):
+                sub.p = 0.0
+    params = [p for m in stages_ for p in m.parameters()]
+    opt = ref_adam.AdamWithWeightStashing(stages_, params, None, 1, num_versions=1, lr=2e-3, weight_decay=1e-4)
+    losses, tensors0 = [], {}
+    import time
+    t0 = time.time()
+    for step, ((src, src_len), (tgt, tgt_len)) in enumerate(SyntheticTranslation(batch, steps, min_len=4, max_len=10)):
+        t = {"input0": src, "input1": torch.LongTensor(src_len), "input2": tgt[:-1],
+             "target": tgt[1:].contiguous().view(-1)}
+        for (m, ins, outs) in model:
+            if outs == ["loss"]:
+                t["loss"] = m(t[ins[0]], t["target"])
+            else:
+                o = m(*[t[n] for n in ins])
+                o = o if isinstance(o, tuple) else (o,)
+                for n, v in zip(outs, o):
+                    t[n] = v
+        opt.zero_grad()
+        opt.load_old_params()
+        t["loss"].backward()
+        opt.load_new_params()
+        opt.step()
+        losses.append(float(t["loss"]))
+        if step == 0:
+            tensors0 = {k: tensor_checksum(v) for k, v in t.items() if k.startswith("out")}
+    out = {"config": {"module": "models.gnmt_large.gpus=4", "batch": batch, "steps": steps, "min_len": 4, "max_len": 10,
+                      "optimizer": "Adam lr 2e-3 wd 1e-4", "seed": 0, "data_seed": 4321, "smoothing": 0.1,
+                      "dropout": "disabled (p=0)"},
+           "losses": losses, "boundary_tensors_step0": tensors0,
+           "params": {"stage%d.%s" % (i, k): tensor_checksum(v) for i, m in enumerate(stages_)
+                      for k, v in m.state_dict().items() if v is not None and ("bidir" in k or "layer1." not in k and "layer2." not in k)},
+           "reference_cpu_seconds": time.time() - t0}
+    with open(os.path.join(HERE, "gnmt_large_golden.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+    print("wrote gnmt_large_golden.json; losses", losses, "in %.1f s" % out["reference_cpu_seconds"])
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -382,3 +451,6 @@ if __name__ == "__main__":
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_stashing(%r)" % (HERE, a.ref)])
         if a.only in (None, "vgg16"):
             make_vgg16(a.ref, a.steps, a.batch)
+        if a.only in (None, "gnmt"):
+            subprocess.check_call([sys.executable, "-O", "-c",
+                                   "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_gnmt(%r)" % (HERE, a.ref)])

@@ -355,3 +355,61 @@ def test_adam_ring():
              2e-3, 0.9, 0.999, 1e-8, 1e-4, step + 1, 1.0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         got = arena[(step + 1) % V].cpu()
         assert torch.allclose(got, p_ref.data, rtol=2e-5, atol=1e-6), "step %d" % step
+
+
+# ------------------------------------------------------------------ LSTM
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("T,B,I,H", [(5, 8, 64, 64), (12, 16, 128, 64), (1, 4, 64, 128)])
+def test_lstm_layer(dtype, T, B, I, H):
+    """NativeLSTM forward and every gradient against torch.nn.LSTM (fp32 autograd on the same weights)."""
+    from pipedream_b200 import layers
+    torch.manual_seed(3)
+    ref = torch.nn.LSTM(I, H).cuda()
+    nat = torch.nn.LSTM(I, H).cuda().to(dtype)
+    ref.load_state_dict({k: v.float() for k, v in nat.state_dict().items()})
+    nat = layers.NativeLSTM(nat)
+    x = rnd(T, B, I, dtype=dtype, seed=70)
+    dy = rnd(T, B, H, dtype=dtype, seed=71)
+    xr = x.float().detach().clone().requires_grad_(True)
+    yr, _ = ref(xr)
+    yr.backward(dy.float())
+    xn = x.detach().clone().requires_grad_(True)
+    yn, (hn, _) = nat(xn)
+    yn.backward(dy)
+    tol = TOL[dtype] if dtype == torch.bfloat16 else 1e-4
+    check(yn, yr, dtype, "lstm y")
+    assert torch.equal(hn[0], yn[-1])
+    check(xn.grad, xr.grad, dtype, "lstm dx")
+    for name in ("weight_ih_l0", "weight_hh_l0", "bias_ih_l0", "bias_hh_l0"):
+        g, gr = getattr(nat, name)._pd_grad, getattr(ref, name).grad
+        if T == 1 and name == "weight_hh_l0":
+            assert float(g.abs().max()) == 0.0
+            continue
+        e = rel_err(g, gr)
+        assert e <= 2 * tol, "%s: %.3e" % (name, e)
+
+
+def test_emu_bidir_lstm_and_embedding():
+    """The swapped bidirectional encoder layer and embedding against their torch formulations."""
+    from pipedream_b200 import layers, gnmt_blocks
+    torch.manual_seed(4)
+    T, B, H, V = 7, 6, 64, 50
+    emb = torch.nn.Embedding(V, H, padding_idx=0).cuda()
+    emu = gnmt_blocks.EmuBidirLSTM(H, H).cuda()
+    lengths = torch.tensor([7, 6, 4, 4, 2, 1])
+    ids = torch.randint(1, V, (T, B), generator=torch.Generator().manual_seed(5))
+    for b in range(B):
+        ids[lengths[b]:, b] = 0
+    ids = ids.cuda()
+    import copy
+    nemb, nemu = layers.nativize(copy.deepcopy(emb)), layers.nativize(copy.deepcopy(emu))
+    assert isinstance(nemb, layers.NativeEmbedding) and isinstance(nemu, layers.NativeEmuBidirLSTM)
+    out_ref = gnmt_blocks.emu_bidir_reference(emu, emb(ids), lengths)
+    out = nemu(nemb(ids), lengths.cuda())
+    check(out, out_ref, torch.float32, "emu bidir")
+    dy = rnd(T, B, 2 * H, dtype=torch.float32, seed=72)
+    out_ref.backward(dy)
+    out.backward(dy)
+    check(nemb.weight._pd_grad, emb.weight.grad, torch.float32, "embedding grad")
+    check(nemu.layer2.weight_hh_l0._pd_grad, emu.layer2.weight_hh_l0.grad, torch.float32, "reverse w_hh grad")
+    check(nemu.layer1.weight_ih_l0._pd_grad, emu.layer1.weight_ih_l0.grad, torch.float32, "forward w_ih grad")
