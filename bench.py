@@ -328,6 +328,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt"],
+                    help="vgg16 (default, the headline line) or gnmt (8+8-layer GNMT, 1 GPU)")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad"],
                     help="run a few launches of one convolution pass (for ncu) and exit")
     a = ap.parse_args()
@@ -342,6 +344,10 @@ def main():
     if a.warmup < 3:
         a.warmup = 3
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if a.model == "gnmt":
+        import bench_gnmt
+        print(json.dumps(bench_gnmt.run(a.steps, a.warmup, not a.no_cpu_baseline)))
+        return
     if a.gpus == 1 and world == 1:
         out = run_gpu_single(a.steps, a.warmup)
         if not a.no_cpu_baseline:

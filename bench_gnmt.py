@@ -1,0 +1,165 @@
+"""GNMT arm of bench.py (`python bench.py --model gnmt`): the 8+8-layer GNMT ("gnmt_large") in bf16,
+batch 128 sentence pairs, source/target lengths uniform in [20,50], Zipf(1.1) token ids, label-smoothed
+cross-entropy (0.1), Adam lr 2e-3 - all four stages in one process on one GPU."""
+import json
+import os
+import time
+
+import torch
+
+from bench import ClockSampler, peaks
+
+BATCH = 128
+METRIC = "gnmt8_train_samples_per_sec"
+
+
+class CyclingPairs:
+    """Endless stream of pre-generated batches; tensors live in pinned host memory (the runtime copies
+    them to the device every step, as the reference's loader path does) or already on the device."""
+
+    def __init__(self, batch, device, pool=6, seed=4321):
+        from pipedream_b200.stages import SyntheticTranslation
+        self.items, self.tokens = [], []
+        for (src, sl), (tgt, tl) in SyntheticTranslation(batch, pool, seed=seed):
+            if device == "pinned":
+                src, tgt = src.pin_memory(), tgt.pin_memory()
+            else:
+                src, tgt = src.to(device), tgt.to(device)
+            self.items.append(((src, sl), (tgt, tl)))
+            self.tokens.append(sum(sl) + sum(tl))
+        self.bytes_per_step = sum(i[0][0].numel() * 8 + i[1][0].numel() * 8 for i in self.items) // len(self.items)
+
+    def __iter__(self):
+        i = 0
+        while True:
+            yield self.items[i % len(self.items)]
+            i += 1
+
+
+def build(fp16=True, dropout=0.2):
+    from pipedream_b200 import adam, gnmt_blocks, runtime, stages
+    torch.manual_seed(0)
+    model = stages.gnmt_large(dropout=dropout).model(gnmt_blocks.LabelSmoothing(0, 0.1))
+    r = runtime.StageRuntime(
+        model=model, distributed_backend=None, fp16=fp16, loss_scale=1, training_tensor_shapes={},
+        eval_tensor_shapes={}, training_tensor_dtypes={}, inputs_module_destinations={"input0": 0, "input1": 0, "input2": 0},
+        target_tensor_names={"target", "target_length"},
+        configuration_maps={"module_to_stage_map": None, "stage_to_rank_map": None, "stage_to_depth_map": None},
+        master_addr=None, rank=None, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
+        model_type=runtime.TRANSLATION)
+    opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=1,
+                                      lr=2e-3, weight_decay=1e-4)
+    return r, opt
+
+
+def step(r, opt):
+    r.run_forward()          # includes the loss read-back the translation runtime does every step
+    opt.zero_grad()
+    opt.load_old_params()
+    r.run_backward()
+    opt.load_new_params()
+    opt.step()
+
+
+def loop(r, opt, steps, warmup):
+    for _ in range(warmup):
+        step(r, opt)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        step(r, opt)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e)
+
+
+def cpu_baseline(batch=16):
+    """The restated reference modules (plain torch) on the host cores: one minibatch of `batch` pairs."""
+    from oracle import pipedream_oracle as oracle
+    from pipedream_b200 import gnmt_blocks, stages
+    torch.manual_seed(0)
+    model = stages.gnmt_large().model(gnmt_blocks.LabelSmoothing(0, 0.1))
+    mods = [m for (m, _, _) in model[:-1]]
+    opt = oracle.StashingOracle("Adam", mods, 1, lr=2e-3, weight_decay=1e-4)
+    data = list(stages.SyntheticTranslation(batch, 2))
+    t0 = None
+    for i, ((src, sl), (tgt, _)) in enumerate(data):
+        if i == 1:
+            t0 = time.time()
+        t = {"input0": src, "input1": torch.LongTensor(sl), "input2": tgt[:-1], "target": tgt[1:].contiguous().view(-1)}
+        for (m, ins, outs) in model:
+            if outs == ["loss"]:
+                t["loss"] = m(t[ins[0]], t["target"])
+            else:
+                o = m(*[t[n] for n in ins])
+                for n, v in zip(outs, o if isinstance(o, tuple) else (o,)):
+                    t[n] = v
+        opt.zero_grad(); t["loss"].backward(); opt.step()
+    dt = time.time() - t0
+    return {"value": batch / dt, "unit": "samples/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "1 minibatch of %d sentence pairs (lengths 20-50), fp32, after 1 untimed minibatch" % batch}
+
+
+def run(steps, warmup, with_cpu):
+    from pipedream_b200 import _lib
+    from pipedream_b200 import functional as pf
+    torch.cuda.set_device(0)
+    r, opt = build()
+    r.train(steps + warmup)
+    dev_data = CyclingPairs(BATCH, "cuda")
+    r.set_loader(dev_data)
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(warmup):
+        step(r, opt)
+    torch.cuda.synchronize()
+    _lib.count_calls(True)
+    pf.timeline = pf.ContractionTimeline()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        step(r, opt)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    launches, calls = _lib.launches_counted(), dict(_lib.COUNTERS)
+    _lib.count_calls(False)
+    tl = pf.timeline.summary()
+    if os.environ.get("PD_BENCH_DETAIL"):
+        with open(os.environ["PD_BENCH_DETAIL"], "w") as f:
+            for k, v in sorted(pf.timeline.per_shape().items()):
+                f.write("%-40s launches/step %5.1f  ms/step %7.3f  TFLOP/s %7.1f\n" % (
+                    k, v[0] / steps, v[2] / steps, v[1] / max(v[2], 1e-9) / 1e9))
+    pf.timeline = None
+    clocks = sampler.stop()
+    host = CyclingPairs(BATCH, "pinned")
+    r.set_loader(host)
+    ms_e2e = loop(r, opt, steps, 2)
+    assert pf.gemm_poll_error() == 0
+    pk = peaks()
+    flops, tms = sum(v[1] for v in tl.values()), sum(v[2] for v in tl.values())
+    tok = sum(dev_data.tokens) / len(dev_data.tokens)
+    out = {
+        "metric": METRIC, "value": round(BATCH * steps / (ms * 1e-3), 2), "unit": "samples/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms / steps, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "GNMT 8+8 layers (hidden 1024, vocab 32320), bf16, batch 128 sentence pairs, lengths "
+                               "uniform in [20,50], Zipf(1.1) ids, label smoothing 0.1, Adam lr 2e-3, 4 stages in one process",
+                   "global_batch": BATCH, "tokens_per_step": tok, "tokens_per_sec": round(tok * steps / (ms * 1e-3), 1),
+                   "parallelism": "1 GPU", "l2": "no flush: weights + activations of a step exceed L2"},
+        "clocks": clocks,
+        "e2e": {"value": round(BATCH * steps / (ms_e2e * 1e-3), 2), "unit": "samples/s",
+                "h2d_bytes_per_step": host.bytes_per_step, "d2h_bytes_per_step": 8, "ms_per_step": round(ms_e2e / steps, 3)},
+        "gpu_launches": launches, "entry_point_calls": calls,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": round(flops / max(tms, 1e-9) / 1e9, 1),
+                     "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": round(flops / max(tms, 1e-9) / 1e9 / pk["bf16_tflops_sustained"], 4), "traffic": None,
+                     "kernel_ms_per_step": round(tms / steps, 3),
+                     "note": "lstm_fwd / lstm_bwd entries time the whole time loop (recurrent contraction + cell kernel per step)",
+                     "by_pass": {k: {"tflops": round(v[1] / max(v[2], 1e-9) / 1e9, 1), "ms_per_step": round(v[2] / steps, 3)}
+                                 for k, v in sorted(tl.items())}},
+    }
+    if with_cpu:
+        out["cpu_baseline"] = cpu_baseline()
+    return out

@@ -402,7 +402,9 @@ def lstm_fwd(gx, w_hh, b_hh, T, B, H):
     act = torch.empty((T, B, 4 * H), dtype=dtype, device=dev)
     c_all = torch.empty((T, B, H), dtype=torch.float32, device=dev)
     gh_ws = torch.empty((B, 4 * H), dtype=torch.float32, device=dev)
-    call("pd_lstm_fwd", dt(gx), _p(gx), _p(w_hh), _p(b_hh), T, B, H, _p(y), _p(act), _p(c_all), _p(gh_ws), _stream())
+    _timed("lstm_fwd", 2.0 * max(T - 1, 0) * B * 4 * H * H, lambda: call(
+        "pd_lstm_fwd", dt(gx), _p(gx), _p(w_hh), _p(b_hh), T, B, H, _p(y), _p(act), _p(c_all), _p(gh_ws), _stream()),
+        (T, B, H))
     return y, act, c_all
 
 
@@ -412,6 +414,7 @@ def lstm_bwd(dy, w_hh, act, c_all):
     dgates = torch.empty((T, B, 4 * H), dtype=dy.dtype, device=dy.device)
     dh_ws = torch.empty((B, H), dtype=torch.float32, device=dy.device)
     dc_ws = torch.empty((B, H), dtype=torch.float32, device=dy.device)
-    call("pd_lstm_bwd", dt(dy), _p(dy), _p(w_hh), _p(act), _p(c_all), T, B, H, _p(dgates), _p(dh_ws), _p(dc_ws),
-         _stream())
+    _timed("lstm_bwd", 2.0 * max(T - 1, 0) * B * 4 * H * H, lambda: call(
+        "pd_lstm_bwd", dt(dy), _p(dy), _p(w_hh), _p(act), _p(c_all), T, B, H, _p(dgates), _p(dh_ws), _p(dc_ws),
+        _stream()), (T, B, H))
     return dgates
