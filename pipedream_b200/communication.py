@@ -184,6 +184,10 @@ class CommunicationHandler(object):
         self.num_ranks_in_server = num_ranks_in_server
         self.world_size = world_size
         self.fp16 = fp16
+        # Translation batches change their sequence length every minibatch; the reference sends the
+        # shape ahead of every payload (runtime/communication.py:664-669).  Here the shape rides in the
+        # slot header and is only read back (a host wait) when this flag is set by the runtime.
+        self.variable_shapes = False
         assert num_ranks_in_server > 0
         if backend == LOCAL:
             self.transport = _LocalTransport(rank)
@@ -277,9 +281,11 @@ class CommunicationHandler(object):
 
     # ------------------------------------------------------------------ data path
     def _dtype(self, name):
-        if name in self.target_tensor_names or name == "ack":
+        if name == "ack":
             return torch.int64
-        return self.training_tensor_dtypes[name]
+        if name in self.training_tensor_dtypes:
+            return self.training_tensor_dtypes[name]
+        return torch.int64          # targets without a recorded dtype (runtime/communication.py:320)
 
     def recv(self, tensor_name, forward_minibatch_id, backward_minibatch_id, backward=False):
         if backward:

@@ -37,6 +37,7 @@ class PeerTransport:
         self.capacity = {}
         self.streams = {}
         self.keepalive = []
+        self.variable_shapes = False
         _lib.load()
 
     def _stream(self, kind):
@@ -66,6 +67,7 @@ class PeerTransport:
         """Create the rings this rank consumes, exchange their handles, map the ones it feeds.
         Collective: every rank calls it at the same points (StageRuntime.train / eval)."""
         torch.cuda.set_device(self.device)
+        self.variable_shapes = bool(getattr(handler, "variable_shapes", False))
         need = self._edges(handler, shapes)
         blobs = {}
         for key, cap in need.items():
@@ -118,9 +120,14 @@ class PeerTransport:
         ch = self.consumers.get(key)
         if ch is None:
             raise _lib.PipedreamB200Error("no peer channel for %r (tensor shapes were not set?)" % (key,))
-        out = torch.empty(tuple(shape), dtype=dtype, device=self.device)
         cur = torch.cuda.current_stream(self.device)
         side = self._stream("recv_bwd" if backward else "recv_fwd")
+        if self.variable_shapes:
+            # wait (on the host) for the message and take its shape from the slot header
+            hdr = (ctypes.c_int64 * 8)()
+            call("pd_chan_peek_header", ch, hdr, ctypes.c_void_p(side.cuda_stream))
+            shape = tuple(int(hdr[3 + i]) for i in range(int(hdr[2])))
+        out = torch.empty(tuple(shape), dtype=dtype, device=self.device)
         ev = torch.cuda.Event()
         ev.record(cur)
         side.wait_event(ev)          # `out` may reuse memory still read by queued compute kernels

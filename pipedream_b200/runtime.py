@@ -263,6 +263,7 @@ class StageRuntime:
         self.model_parameters = None
 
         if self.comm_handler is not None:
+            self.comm_handler.variable_shapes = (self.model_type == TRANSLATION)
             self.comm_handler.initialize(
                 self.receive_ranks, self.send_ranks, self.tensor_tags,
                 self.target_tensor_names, self.training_tensor_dtypes,
@@ -361,7 +362,8 @@ class StageRuntime:
                 self.tensors[-1]["input2"] = self._to_device(tgt[:-1])
                 self.tensors[-1]["target"] = self._to_device(tgt[1:]).contiguous().view(-1)
                 self.tensors[-1]["target_length"] = self._to_device(torch.tensor(
-                    [int(sum(torch.as_tensor(tgt_length, dtype=torch.int64) - 1))], dtype=torch.int))
+                    [int(sum(torch.as_tensor(tgt_length, dtype=torch.int64) - 1))],
+                    dtype=self.training_tensor_dtypes.get("target_length", torch.int)))
             elif self.model_type == IMAGE_CLASSIFICATION:
                 (input, target) = input
                 if self.fp16 and not self.native:

@@ -126,3 +126,63 @@ def test_two_stage_pipeline_over_peer_channels(fp16, tmp_path):
     for rank in (0, 1):
         g = json.load(open(os.path.join(str(tmp_path), "rank%d.json" % rank)))
         assert g["werr"] <= max(tol, 5e-3), g
+
+
+def _gnmt_worker(rank, world, port, out_dir):
+    """Stages 0-1 on GPU 0, stages 2-3 and the criterion on GPU 1, no input pipelining (one version),
+    so the arithmetic is that of the single-process golden run."""
+    sys.path.insert(0, ROOT)
+    os.environ["PIPEDREAM_MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    from pipedream_b200 import adam, gnmt_blocks, runtime, schedule, stages
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "gnmt_large_golden.json")))
+    cfg = gold["config"]
+    torch.manual_seed(cfg["seed"])
+    model = stages.gnmt_large().model(gnmt_blocks.LabelSmoothing(0, cfg["smoothing"]))
+    for (m, _, _) in model:
+        for sub in m.modules():
+            if isinstance(sub, torch.nn.Dropout):
+                sub.p = 0.0
+    B, Tm, H, V = cfg["batch"], cfg["max_len"], 1024, 32320
+    shapes = {"input0": (Tm, B), "input1": (B,), "input2": (Tm, B), "target": (Tm * B,), "target_length": (B,),
+              "out0": (Tm, B, H), "out1": (Tm, B, H), "out12": (Tm, B, H), "out13": (Tm, B, H), "out14": (Tm, B, H),
+              "out15": (Tm, B, 2 * H), "out12again": (Tm, B, H), "out18": (Tm, B, V)}
+    dtypes = {k: torch.float32 for k in shapes}
+    dtypes.update({"input0": torch.int64, "input1": torch.int64, "input2": torch.int64, "target": torch.int64,
+                   "target_length": torch.int64})
+    conf = {"module_to_stage_map": [0, 0, 1, 1, 1], "stage_to_rank_map": {0: [0], 1: [1]}, "stage_to_depth_map": None}
+    r = runtime.StageRuntime(
+        model=model, distributed_backend="p2p", fp16=False, loss_scale=1, training_tensor_shapes=shapes,
+        eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dtypes,
+        inputs_module_destinations={"input0": 0, "input1": 1, "input2": 1},
+        target_tensor_names={"target", "target_length"}, configuration_maps=conf, master_addr="127.0.0.1",
+        rank=rank, local_rank=rank, num_ranks_in_server=1, verbose_freq=0, model_type=runtime.TRANSLATION)
+    opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=1,
+                                      lr=2e-3, weight_decay=1e-4)
+    n = cfg["steps"]
+    r.train(n)
+    r.set_loader(stages.SyntheticTranslation(B, n, seed=cfg["data_seed"], min_len=cfg["min_len"], max_len=Tm)
+                 if r.stage == 0 else None)
+    losses = []
+    schedule.train_1f1b(r, opt, n, no_input_pipelining=True,
+                        on_forward=lambda i, rr: losses.append(float(rr.tensors[-1]["loss"])) if rr.is_criterion else None)
+    torch.cuda.synchronize()
+    json.dump({"losses": losses}, open(os.path.join(out_dir, "rank%d.json" % rank), "w"))
+    import torch.distributed as dist
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_gnmt_two_gpus_variable_length_batches(tmp_path):
+    """Translation stages over the peer channels: boundary tensors change shape every minibatch, model
+    inputs (lengths, decoder tokens) and targets are forwarded to the later stage."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_gnmt_worker, args=(2, 24510, str(tmp_path)), nprocs=2, join=True)
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "gnmt_large_golden.json")))
+    got = json.load(open(os.path.join(str(tmp_path), "rank1.json")))
+    assert len(got["losses"]) == len(gold["losses"])
+    for a, b in zip(got["losses"], gold["losses"]):
+        assert abs(a - b) <= 1e-3 * abs(b), (got["losses"], gold["losses"])
