@@ -516,8 +516,29 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are cached per host thread: the time loop of an LSTM layer launches the same
+// two maps once per step (only the row coordinate moves), and encoding costs more than the launch.
+struct MapKey {
+  const void* base; int64_t rows, cols, ld; int box_cols, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols && box_rows == o.box_rows;
+  }
+};
+struct MapCache {
+  static constexpr int kEntries = 16;
+  MapKey key[kEntries];
+  CUtensorMap map[kEntries];
+  bool valid[kEntries] = {};
+  int next = 0;
+};
+thread_local MapCache g_map_cache;
+
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols,
              int box_rows) {
+  const MapKey k{base, rows, cols, ld, box_cols, box_rows};
+  MapCache& c = g_map_cache;
+  for (int i = 0; i < MapCache::kEntries; ++i)
+    if (c.valid[i] && c.key[i] == k) { *map = c.map[i]; return PD_OK; }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { pd_set_error("cuTensorMapEncodeTiled is not available from the driver"); return PD_ERR_CUDA; }
   PD_REQUIRE(((uintptr_t)base & 15) == 0, "tcgen05 gemm: operand base must be 16-byte aligned");
@@ -535,6 +556,8 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
                  (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
     return PD_ERR_CUDA;
   }
+  c.key[c.next] = k; c.map[c.next] = *map; c.valid[c.next] = true;
+  c.next = (c.next + 1) % MapCache::kEntries;
   return PD_OK;
 }
 

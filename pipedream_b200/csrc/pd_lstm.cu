@@ -113,7 +113,9 @@ PD_EXPORT int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const voi
     if (t > 0) {
       PdGemm g; init_gemm(g);
       g.dtype = dtype;
-      g.a = (const char*)y + (int64_t)(t - 1) * BH * es; g.a_rows = B; g.a_cols = H; g.lda = H; g.a_major = 0;
+      // whole-sequence map, step selected by the row origin (fp32 path: plain pointer arithmetic inside)
+      g.a = y; g.a_rows = (int64_t)T * B; g.a_cols = H; g.lda = H; g.a_major = 0;
+      g.a_row0 = (t - 1) * B;
       g.b = w_hh; g.b_rows = 4 * H; g.b_cols = H; g.ldb = H; g.b_major = 0;
       g.M = B; g.N = 4 * H; g.K = H;
       g.out = gh_ws; g.out_dtype = PD_F32; g.ldo = 4 * H;
@@ -165,7 +167,8 @@ PD_EXPORT int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const voi
       // dh_{t-1} (+)= dgates_t . W_hh   ([B,4H] x [4H,H]); dh_ws was cleared by the cell kernel
       PdGemm g; init_gemm(g);
       g.dtype = dtype;
-      g.a = dg_t; g.a_rows = B; g.a_cols = 4 * H; g.lda = 4 * H; g.a_major = 0;
+      g.a = dgates; g.a_rows = (int64_t)T * B; g.a_cols = 4 * H; g.lda = 4 * H; g.a_major = 0;
+      g.a_row0 = t * B;
       g.b = w_hh; g.b_rows = 4 * H; g.b_cols = H; g.ldb = H; g.b_major = 1;
       g.M = B; g.N = H; g.K = 4 * H;
       g.out = dh_ws; g.out_dtype = PD_F32; g.ldo = H;
