@@ -447,9 +447,10 @@ class StageRuntime:
 
         self.output = tensors[input_names[0]]
         if self.is_criterion and self.model_type == TRANSLATION:
+            # per-token loss as in runtime/runtime.py:539-542, but divided on the device: reading the
+            # token count back here would drain the stream in the middle of every step
             loss_per_batch = tensors[output_names[0]] * tensors[self.criterion_input_name].size(1)
-            loss_per_token = loss_per_batch / tensors["target_length"][0].item()
-            self.loss = loss_per_token
+            self.loss = loss_per_batch / tensors["target_length"][0]
         elif self.is_criterion:
             self.loss = tensors[output_names[0]]
         else:
