@@ -180,6 +180,23 @@ int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const void* b_hh, i
 int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all,
                 int T, int B, int H, void* dgates, float* dh_ws, float* dc_ws, void* stream);
 
+/* Normalised additive attention (runtime/translation/seq2seq/models/attention.py:84-170:
+ * `calc_score`, mask, softmax, `bmm`) fused so that tanh(q + k + b) is never stored.  pq [b,tq,n] and
+ * pk [b,tk,n] are the projected queries / keys (pd_gemm_nt); v [n] fp32 is linear_att / |linear_att| *
+ * normalize_scalar; nb [n] is normalize_bias; ctx_len [b] int64 masks keys j >= ctx_len[b] (score
+ * -65504 as in the reference) or NULL.  keys / context / dkeys are addressed as base + batch*sb +
+ * time*st + channel (elements), so sequence-first tensors are used in place.  tk <= 128.
+ * Backward: dv, dnb fp32 [n] are accumulated into (clear them first); ds_ws [b,tq,tk] fp32 scratch.  */
+int pd_attn_bahdanau_fwd(int dtype, const void* pq, const void* pk, const void* keys, int64_t k_sb,
+                         int64_t k_st, const float* v, const void* nb, const int64_t* ctx_len, int b,
+                         int tq, int tk, int n, int nk, void* probs, void* context, int64_t c_sb,
+                         int64_t c_st, void* stream);
+int pd_attn_bahdanau_bwd(int dtype, const void* pq, const void* pk, const void* keys, int64_t k_sb,
+                         int64_t k_st, const float* v, const void* nb, const void* probs,
+                         const void* dcontext, int64_t c_sb, int64_t c_st, int b, int tq, int tk, int n,
+                         int nk, void* dpq, void* dpk, void* dkeys, int64_t dk_sb, int64_t dk_st,
+                         float* dv, float* dnb, float* ds_ws, void* stream);
+
 /* Reads and clears the error word the tcgen05 kernels set when a bounded wait runs out
  * (0 = none).  `code` is a HOST pointer; synchronises the device.                            */
 int pd_gemm_poll_error(int* code);

@@ -61,6 +61,8 @@ SIGNATURES = {
     "pd_conv2d_wgrad": (I, [I, P, P, I, I, I, I, I, P, L, I, I, P]),
     "pd_lstm_fwd": (I, [I, P, P, P, I, I, I, P, P, P, P, P]),
     "pd_lstm_bwd": (I, [I, P, P, P, P, I, I, I, P, P, P, P]),
+    "pd_attn_bahdanau_fwd": (I, [I, P, P, P, L, L, P, P, P, I, I, I, I, I, P, P, L, L, P]),
+    "pd_attn_bahdanau_bwd": (I, [I, P, P, P, L, L, P, P, P, P, L, L, I, I, I, I, I, P, P, P, L, L, P, P, P, P]),
     "pd_gemm_poll_error": (I, [POINTER(c_int)]),
     "pd_chan_create": (I, [L, I, I, POINTER(c_void_p)]),
     "pd_chan_export_handle": (I, [P, P]),

@@ -418,3 +418,35 @@ def lstm_bwd(dy, w_hh, act, c_all):
         "pd_lstm_bwd", dt(dy), _p(dy), _p(w_hh), _p(act), _p(c_all), T, B, H, _p(dgates), _p(dh_ws), _p(dc_ws),
         _stream()), (T, B, H))
     return dgates
+
+
+# --------------------------------------------------------------------------- #
+# additive attention
+# --------------------------------------------------------------------------- #
+def attn_fwd(pq, pk, keys_tbn, v, nb, ctx_len):
+    """pq [b,tq,n], pk [b,tk,n] contiguous; keys_tbn [tk,b,nk] (sequence first, contiguous); v fp32 [n].
+    Returns (probs [b,tq,tk], context [tq,b,nk])."""
+    _cuda(pq, pk, keys_tbn, v, nb)
+    b, tq, n = pq.shape
+    tk, _, nk = keys_tbn.shape
+    probs = torch.empty((b, tq, tk), dtype=pq.dtype, device=pq.device)
+    context = torch.empty((tq, b, nk), dtype=pq.dtype, device=pq.device)
+    call("pd_attn_bahdanau_fwd", dt(pq), _p(pq), _p(pk), _p(keys_tbn), nk, b * nk, _p(v), _p(nb), _p(ctx_len),
+         b, tq, tk, n, nk, _p(probs), _p(context), nk, b * nk, _stream())
+    return probs, context
+
+
+def attn_bwd(pq, pk, keys_tbn, v, nb, probs, dcontext_tbn):
+    """Returns (dpq, dpk, dkeys [tk,b,nk], dv fp32 [n], dnb fp32 [n])."""
+    b, tq, n = pq.shape
+    tk, _, nk = keys_tbn.shape
+    dev = pq.device
+    dpq, dpk = torch.empty_like(pq), torch.empty_like(pk)
+    dkeys = torch.empty_like(keys_tbn)
+    dv = torch.zeros(n, dtype=torch.float32, device=dev)
+    dnb = torch.zeros(n, dtype=torch.float32, device=dev)
+    ds_ws = torch.empty((b, tq, tk), dtype=torch.float32, device=dev)
+    call("pd_attn_bahdanau_bwd", dt(pq), _p(pq), _p(pk), _p(keys_tbn), nk, b * nk, _p(v), _p(nb), _p(probs),
+         _p(dcontext_tbn), nk, b * nk, b, tq, tk, n, nk, _p(dpq), _p(dpk), _p(dkeys), nk, b * nk, _p(dv), _p(dnb),
+         _p(ds_ws), _stream())
+    return dpq, dpk, dkeys, dv, dnb

@@ -542,6 +542,67 @@ class NativeEmbedding(nn.Module):
     def forward(self, ids):
         return _EmbeddingFn.apply(ids, self.weight, self.padding_idx)
 
+
+# --------------------------------------------------------------------------- #
+# additive attention
+# --------------------------------------------------------------------------- #
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pq, pk, keys, v, nb, ctx_len):
+        nbd = nb.detach()
+        if nbd.dtype != pq.dtype:
+            nbd = nbd.to(pq.dtype)
+        vf = v.detach().float().contiguous()
+        keys_c = keys if keys.is_contiguous() else keys.contiguous()
+        probs, context = pf.attn_fwd(pq.contiguous(), pk.contiguous(), keys_c, vf, nbd, ctx_len)
+        ctx.saved = (pq, pk, keys_c, vf, nbd, probs)
+        ctx.v_dtype, ctx.nb_dtype = v.dtype, nb.dtype
+        ctx.mark_non_differentiable(probs)
+        return context, probs
+
+    @staticmethod
+    def backward(ctx, dcontext, _dprobs):
+        pq, pk, keys_c, vf, nbd, probs = ctx.saved
+        dc = dcontext if dcontext.is_contiguous() else dcontext.contiguous()
+        dpq, dpk, dkeys, dv, dnb = pf.attn_bwd(pq.contiguous(), pk.contiguous(), keys_c, vf, nbd, probs, dc)
+        return dpq, dpk, dkeys, dv.to(ctx.v_dtype), dnb.to(ctx.nb_dtype), None
+
+
+class NativeBahdanauAttention(nn.Module):
+    """Normalised additive attention over sequence-first tensors (query [t_q,b,n], keys [t_k,b,n]); same
+    parameters as the block it replaces (linear_q, linear_k, linear_att, normalize_scalar, normalize_bias)."""
+
+    def __init__(self, att):
+        super().__init__()
+        self.num_units = att.num_units
+        self.linear_q = _swap_leaf(att.linear_q)
+        self.linear_k = _swap_leaf(att.linear_k)
+        self.linear_att = att.linear_att
+        self.normalize_scalar = att.normalize_scalar
+        self.normalize_bias = att.normalize_bias
+        self.register_buffer('mask', None)
+        self._ctx_len = None
+
+    @staticmethod
+    def supports(m):
+        return (type(m).__name__ == "BahdanauAttention" and getattr(m, "normalize", False)
+                and not getattr(m, "batch_first", True) and hasattr(m, "linear_att")
+                and getattr(getattr(m, "dropout", None), "p", 0) == 0)
+
+    def set_mask(self, context_len, context):
+        self._ctx_len = context_len.to(device=context.device, dtype=torch.int64).contiguous()
+        self.mask = torch.arange(context.size(0), device=context.device).unsqueeze(0) >= self._ctx_len.unsqueeze(1)
+
+    def forward(self, query, keys):
+        if query.dim() != 3:
+            raise NotImplementedError("single-step queries are an inference path")
+        pq = self.linear_q(query.transpose(0, 1))          # [b, t_q, n]
+        pk = self.linear_k(keys.transpose(0, 1))           # [b, t_k, n]
+        a = self.linear_att.float()
+        v = a / a.norm() * self.normalize_scalar.float()   # tiny [n] vector: autograd carries its chain rule
+        context, probs = _AttnFn.apply(pq, pk, keys, v, self.normalize_bias, self._ctx_len)
+        return context, probs.transpose(0, 1)
+
 # --------------------------------------------------------------------------- #
 # criteria
 # --------------------------------------------------------------------------- #
@@ -594,12 +655,12 @@ class NativeLabelSmoothing(nn.Module):
 # --------------------------------------------------------------------------- #
 _LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway)
 _NATIVE_TYPES = _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
-                                 NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding)
+                                 NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention)
 
 
 def _swap_leaf(m):
     if isinstance(m, _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
-                                      NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding)):
+                                      NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention)):
         return m
     if NativeConv2d.supports(m):
         return NativeConv2d(m)
@@ -615,6 +676,8 @@ def _swap_leaf(m):
         return NativeEmuBidirLSTM(m)
     if NativeEmbedding.supports(m):
         return NativeEmbedding(m)
+    if NativeBahdanauAttention.supports(m):
+        return NativeBahdanauAttention(m)
     if isinstance(m, nn.Dropout):
         return NativeDropout(m.p)
     if NativeCrossEntropyLoss.supports(m):

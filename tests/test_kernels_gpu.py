@@ -413,3 +413,42 @@ def test_emu_bidir_lstm_and_embedding():
     check(nemb.weight._pd_grad, emb.weight.grad, torch.float32, "embedding grad")
     check(nemu.layer2.weight_hh_l0._pd_grad, emu.layer2.weight_hh_l0.grad, torch.float32, "reverse w_hh grad")
     check(nemu.layer1.weight_ih_l0._pd_grad, emu.layer1.weight_ih_l0.grad, torch.float32, "forward w_ih grad")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_bahdanau_attention(dtype):
+    """Fused additive attention (forward, and every gradient) against the torch formulation of the block."""
+    import copy
+    from pipedream_b200 import layers, gnmt_blocks
+    torch.manual_seed(6)
+    tq, tk, b, n = 7, 9, 5, 64
+    ref = gnmt_blocks.BahdanauAttention(n, n, n).cuda()
+    with torch.no_grad():
+        ref.normalize_bias.uniform_(-0.1, 0.1)
+    nat = copy.deepcopy(ref).to(dtype)
+    ref.load_state_dict({k: v.float() for k, v in nat.state_dict().items() if v is not None}, strict=False)
+    nat = layers.nativize(nat)
+    assert isinstance(nat, layers.NativeBahdanauAttention) and isinstance(nat.linear_q, layers.NativeLinear)
+    q = rnd(tq, b, n, dtype=dtype, seed=80)
+    k = rnd(tk, b, n, dtype=dtype, seed=81)
+    lens = torch.tensor([9, 7, 4, 2, 1]).cuda()
+    dctx = rnd(tq, b, n, dtype=dtype, seed=82)
+    qr, kr = q.float().detach().clone().requires_grad_(True), k.float().detach().clone().requires_grad_(True)
+    ref.set_mask(lens, kr)
+    cr, pr = ref(qr, kr)
+    cr.backward(dctx.float())
+    qn, kn = q.detach().clone().requires_grad_(True), k.detach().clone().requires_grad_(True)
+    nat.set_mask(lens, kn)
+    cn, pn = nat(qn, kn)
+    cn.backward(dctx)
+    check(pn, pr, dtype, "attention probs")
+    check(cn, cr, dtype, "attention context")
+    check(qn.grad, qr.grad, dtype, "attention dquery")
+    check(kn.grad, kr.grad, dtype, "attention dkeys")
+    tol = 5e-2 if dtype == torch.bfloat16 else 1e-3
+    for name in ("linear_att", "normalize_scalar", "normalize_bias"):
+        e = rel_err(getattr(nat, name).grad, getattr(ref, name).grad)
+        assert e <= tol, "%s: %.3e" % (name, e)
+    for name in ("linear_q", "linear_k"):
+        e = rel_err(getattr(nat, name).weight._pd_grad, getattr(ref, name).weight.grad)
+        assert e <= tol, "%s: %.3e" % (name, e)
