@@ -629,9 +629,17 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
-  int* err = nullptr;
-  PD_CUDA(cudaGetSymbolAddress((void**)&err, g_gemm_error));
-  p.err = err;
+  // device address of the error word, looked up once per device
+  static int* err_addr[64] = {};
+  int dev_now = 0;
+  PD_CUDA(cudaGetDevice(&dev_now));
+  PD_REQUIRE(dev_now >= 0 && dev_now < 64, "tcgen05 gemm: device ordinal out of range");
+  if (err_addr[dev_now] == nullptr) {
+    int* e = nullptr;
+    PD_CUDA(cudaGetSymbolAddress((void**)&e, g_gemm_error));
+    err_addr[dev_now] = e;
+  }
+  p.err = err_addr[dev_now];
 
   CUtensorMap ma, mb;
   int rc = make_map(&ma, g.a, g.a_rows, g.a_cols, g.lda, 64, g.a_major ? kBlockK : kBlockM);
