@@ -332,8 +332,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt"],
-                    help="vgg16 (default, the headline line) or gnmt (8+8-layer GNMT, 1 GPU)")
+    ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50"],
+                    help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT) or resnet50, each on 1 GPU")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad"],
                     help="run a few launches of one convolution pass (for ncu) and exit")
     a = ap.parse_args()
@@ -351,6 +351,10 @@ def main():
     if a.model == "gnmt":
         import bench_gnmt
         print(json.dumps(bench_gnmt.run(a.steps, a.warmup, not a.no_cpu_baseline)))
+        return
+    if a.model == "resnet50":
+        import bench_resnet
+        print(json.dumps(bench_resnet.run(a.steps, a.warmup, not a.no_cpu_baseline)))
         return
     if a.gpus == 1 and world == 1:
         out = run_gpu_single(a.steps, a.warmup)

@@ -93,6 +93,38 @@ int pd_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, int64_t n, flo
 /* y = a + b: residual adds of the ResNet-50 / GNMT stage files.                             */
 int pd_add(const void* a, const void* b, void* y, int64_t n, int dtype, void* stream);
 
+/* torch.nn.BatchNorm2d of the ResNet-50 stages (runtime/image_classification/models/resnet50/gpus=4/
+ * stage1.py:12-55; cuDNN batch norm in the reference), on padded NHWC.  Training forward computes the
+ * batch statistics (mean, invstd: fp32 [C], saved), updates running_mean / running_var like torch
+ * (momentum, unbiased variance), applies gamma/beta and optionally the ReLU that follows.  Backward
+ * takes the saved statistics; y_pad != NULL means the forward fused a ReLU.  workspace: fp32 scratch
+ * of pd_bn_workspace_bytes(C) bytes; sums_ws: fp32 [2*C].  C <= 2048.                             */
+int64_t pd_bn_workspace_bytes(int C);
+int pd_bn_fwd(int dtype, const void* x_pad, int N, int H, int W, int C, const void* gamma, const void* beta,
+              float eps, float momentum, int relu, float* mean, float* invstd, float* running_mean,
+              float* running_var, void* y_pad, void* workspace, int64_t workspace_bytes, void* stream);
+int pd_bn_apply(int dtype, const void* x_pad, int N, int H, int W, int C, const void* gamma, const void* beta,
+                const float* mean, const float* invstd, int relu, void* y_pad, void* stream);
+int pd_bn_bwd(int dtype, const void* x_pad, const void* dy_pad, const void* y_pad, int N, int H, int W, int C,
+              const void* gamma, const float* mean, const float* invstd, float* dgamma, float* dbeta,
+              int accumulate, void* dx_pad, float* sums_ws, void* workspace, int64_t workspace_bytes,
+              void* stream);
+/* Convolution variants other than 3x3/stride 1 (resnet50/gpus=4/stage0.py:10: 7x7 stride 2; 1x1 and 3x3
+ * stride 2) run as a patch matrix through pd_gemm_*: pd_im2col builds [N*Ho*Wo, Kpad] (k = (r*kw+s)*C + c)
+ * from an any-stride NCHW source, pd_col2im_pnhwc gathers the patch-matrix gradient back into padded NHWC. */
+int pd_im2col(const void* src, int src_dtype, int64_t sN, int64_t sC, int64_t sH, int64_t sW, int N, int C,
+              int H, int W, int kh, int kw, int stride, int pad, int Ho, int Wo, int Kpad, void* dst,
+              int dst_dtype, void* stream);
+int pd_col2im_pnhwc(const void* dcol, int N, int C, int H, int W, int kh, int kw, int stride, int pad, int Ho,
+                    int Wo, int Kpad, void* dx_pad, int dtype, void* stream);
+/* MaxPool2d(3, stride 2, padding 1) and the global AvgPool2d(7) of resnet50 (stage0.py:13, stage2.py),
+ * padded NHWC in; the average pool writes / reads a contiguous [N, C] matrix.                       */
+int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, void* y_pad, int dtype, void* stream);
+int pd_maxpool3s2_bwd(const void* x_pad, const void* dy_pad, int N, int C, int H, int W, void* dx_pad, int dtype,
+                      void* stream);
+int pd_avgpool_fwd(const void* x_pad, int N, int C, int H, int W, void* y, int dtype, void* stream);
+int pd_avgpool_bwd(const void* dy, int N, int C, int H, int W, void* dx_pad, int dtype, void* stream);
+
 /* ---- criteria --------------------------------------------------------------------------
  * torch.nn.CrossEntropyLoss (runtime/image_classification/main_with_runtime.py:126) and
  * LabelSmoothing (runtime/translation/seq2seq/train/smoothing.py:23-34).  smoothing = 0 and

@@ -450,3 +450,87 @@ def attn_bwd(pq, pk, keys_tbn, v, nb, probs, dcontext_tbn):
          _p(dcontext_tbn), nk, b * nk, b, tq, tk, n, nk, _p(dpq), _p(dpk), _p(dkeys), nk, b * nk, _p(dv), _p(dnb),
          _p(ds_ws), _stream())
     return dpq, dpk, dkeys, dv, dnb
+
+
+# --------------------------------------------------------------------------- #
+# batch norm, generic convolutions, ResNet pools
+# --------------------------------------------------------------------------- #
+def _bn_ws(device, C):
+    return _workspace(device, _lib.load().pd_bn_workspace_bytes(C))
+
+
+def bn_fwd(x_pad, gamma, beta, eps, momentum, relu, running_mean, running_var):
+    N, Hp, Wp, C = x_pad.shape
+    dev = x_pad.device
+    mean = torch.empty(C, dtype=torch.float32, device=dev)
+    invstd = torch.empty(C, dtype=torch.float32, device=dev)
+    y = torch.empty_like(x_pad)
+    ws = _bn_ws(dev, C)
+    call("pd_bn_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), float(eps), float(momentum),
+         int(relu), _p(mean), _p(invstd), _p(running_mean), _p(running_var), _p(y), _p(ws), ws.numel(), _stream())
+    return y, mean, invstd
+
+
+def bn_apply(x_pad, gamma, beta, mean, invstd, relu):
+    N, Hp, Wp, C = x_pad.shape
+    y = torch.empty_like(x_pad)
+    call("pd_bn_apply", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), _p(mean), _p(invstd), int(relu),
+         _p(y), _stream())
+    return y
+
+
+def bn_bwd(x_pad, dy_pad, y_pad, gamma, mean, invstd, dgamma, dbeta, accumulate):
+    N, Hp, Wp, C = x_pad.shape
+    dev = x_pad.device
+    dx = torch.empty_like(x_pad)
+    sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
+    ws = _bn_ws(dev, C)
+    call("pd_bn_bwd", dt(x_pad), _p(x_pad), _p(dy_pad), _p(y_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(mean), _p(invstd),
+         _p(dgamma), _p(dbeta), int(accumulate), _p(dx), _p(sums), _p(ws), ws.numel(), _stream())
+    return dx
+
+
+def im2col(x, kh, kw, stride, pad, kpad, dtype):
+    """Any-stride [N,C,H,W] -> ([N*Ho*Wo, kpad] patch matrix, Ho, Wo)."""
+    N, C, H, W = x.shape
+    Ho, Wo = (H + 2 * pad - kh) // stride + 1, (W + 2 * pad - kw) // stride + 1
+    out = torch.empty((N * Ho * Wo, kpad), dtype=dtype, device=x.device)
+    sN, sC, sH, sW = x.stride()
+    call("pd_im2col", _p(x), dt(x), sN, sC, sH, sW, N, C, H, W, kh, kw, stride, pad, Ho, Wo, kpad, _p(out), _DT[dtype],
+         _stream())
+    return out, Ho, Wo
+
+
+def col2im_pnhwc(dcol, N, C, H, W, kh, kw, stride, pad, Ho, Wo):
+    dx = torch.empty((N, H + 2, W + 2, C), dtype=dcol.dtype, device=dcol.device)
+    call("pd_col2im_pnhwc", _p(dcol), N, C, H, W, kh, kw, stride, pad, Ho, Wo, dcol.shape[1], _p(dx), dt(dcol), _stream())
+    return dx
+
+
+def maxpool3s2_fwd(x_pad):
+    N, Hp, Wp, C = x_pad.shape
+    H, W = Hp - 2, Wp - 2
+    Ho, Wo = (H - 1) // 2 + 1, (W - 1) // 2 + 1
+    y = torch.empty((N, Ho + 2, Wo + 2, C), dtype=x_pad.dtype, device=x_pad.device)
+    call("pd_maxpool3s2_fwd", _p(x_pad), N, C, H, W, _p(y), dt(x_pad), _stream())
+    return y
+
+
+def maxpool3s2_bwd(x_pad, dy_pad):
+    N, Hp, Wp, C = x_pad.shape
+    dx = torch.empty_like(x_pad)
+    call("pd_maxpool3s2_bwd", _p(x_pad), _p(dy_pad), N, C, Hp - 2, Wp - 2, _p(dx), dt(x_pad), _stream())
+    return dx
+
+
+def avgpool_fwd(x_pad):
+    N, Hp, Wp, C = x_pad.shape
+    y = torch.empty((N, C, 1, 1), dtype=x_pad.dtype, device=x_pad.device)
+    call("pd_avgpool_fwd", _p(x_pad), N, C, Hp - 2, Wp - 2, _p(y), dt(x_pad), _stream())
+    return y
+
+
+def avgpool_bwd(dy, N, C, H, W):
+    dx = torch.empty((N, H + 2, W + 2, C), dtype=dy.dtype, device=dy.device)
+    call("pd_avgpool_bwd", _p(dy), N, C, H, W, _p(dx), dt(dy), _stream())
+    return dx

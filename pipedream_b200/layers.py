@@ -181,6 +181,237 @@ class NativeConv2d(nn.Module):
             self.in_channels, self.out_channels, self.fuse_relu)
 
 
+
+# --------------------------------------------------------------------------- #
+# ResNet pieces: batch norm, 1x1 and patch-matrix convolutions, 3x3/2 max-pool, global average pool
+# --------------------------------------------------------------------------- #
+class _BatchNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, mod, fuse_relu, out_nchw):
+        N, C, H, W = x.shape
+        g, b = weight.detach(), bias.detach()
+        x_pad = pf.as_padded(x, g.dtype)
+        y_pad, mean, invstd = pf.bn_fwd(x_pad, g, b, mod.eps, mod.momentum if mod.momentum is not None else 0.1,
+                                        fuse_relu, mod.running_mean, mod.running_var)
+        ctx.saved = (x_pad, y_pad if fuse_relu else None, mean, invstd)
+        ctx.params = (weight, bias)
+        ctx.geom = (N, C, H, W)
+        return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, H, W)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_pad, y_pad, mean, invstd = ctx.saved
+        weight, bias = ctx.params
+        N, C, H, W = ctx.geom
+        g = weight.detach()
+        dy_pad = pf.as_padded(dy, g.dtype)
+        acc = take_accumulate_flag(weight)
+        take_accumulate_flag(bias)
+        dx_pad = pf.bn_bwd(x_pad, dy_pad, y_pad, g, mean, invstd, grad_buffer(weight), grad_buffer(bias), acc)
+        return pf.nchw_view(dx_pad, N, C, H, W), None, None, None, None, None
+
+
+class NativeBatchNorm2d(nn.Module):
+    def __init__(self, bn):
+        super().__init__()
+        self.num_features, self.eps, self.momentum = bn.num_features, bn.eps, bn.momentum
+        self.fuse_relu = False
+        self.out_nchw = True
+        self.weight, self.bias = bn.weight, bn.bias
+        # statistics stay fp32 whatever the compute dtype (the reference keeps BN in fp32 under fp16 too,
+        # runtime/runtime.py:229)
+        self.register_buffer("running_mean", bn.running_mean.detach().float().clone())
+        self.register_buffer("running_var", bn.running_var.detach().float().clone())
+        self.register_buffer("num_batches_tracked", bn.num_batches_tracked.detach().clone())
+        _mark_native(self.weight, self.bias)
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.BatchNorm2d) and m.affine and m.track_running_stats and m.num_features % 8 == 0
+                and m.num_features <= 2048)
+
+    def forward(self, x):
+        if self.training:
+            self.num_batches_tracked.add_(1)
+            return _BatchNormFn.apply(x, self.weight, self.bias, self, self.fuse_relu, self.out_nchw)
+        N, C, H, W = x.shape
+        invstd = torch.rsqrt(self.running_var + self.eps)
+        y_pad = pf.bn_apply(pf.as_padded(x, self.weight.dtype), self.weight.detach(), self.bias.detach(),
+                            self.running_mean, invstd, self.fuse_relu)
+        return pf.unpack_pnhwc(y_pad) if self.out_nchw else pf.nchw_view(y_pad, N, C, H, W)
+
+
+def _dense_nhwc(t, dtype):
+    """[N*H*W, C] dense matrix of a logical NCHW tensor of any strides (a 1x1 patch matrix)."""
+    N, C, H, W = t.shape
+    if t.dtype == dtype and t.stride() == (H * W * C, 1, W * C, C):
+        return t.permute(0, 2, 3, 1).reshape(N * H * W, C)
+    return pf.im2col(t, 1, 1, 1, 0, C, dtype)[0]
+
+
+class _Conv1x1Fn(torch.autograd.Function):
+    """1x1 / stride 1 convolution: a plain contraction over the padded pixel rows."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, out_nchw):
+        w = weight.detach()
+        N, Cin, H, W = x.shape
+        Cout = w.shape[0]
+        x_pad = pf.as_padded(x, w.dtype)
+        y2d = pf.gemm_nt(x_pad.view(-1, Cin), _dense2d(w, Cout, Cin), bias=bias.detach() if bias is not None else None,
+                         pad_hw=(H + 2, W + 2))
+        ctx.x_pad, ctx.params, ctx.geom = x_pad, (weight, bias), (N, Cin, H, W, Cout)
+        y_pad = y2d.view(N, H + 2, W + 2, Cout)
+        return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, Cout, H, W)
+
+    @staticmethod
+    def backward(ctx, dy):
+        weight, bias = ctx.params
+        N, Cin, H, W, Cout = ctx.geom
+        w = weight.detach()
+        dy2d = pf.as_padded(dy, w.dtype).view(-1, Cout)
+        gw = grad_buffer(weight)
+        pf.gemm_tn(dy2d, ctx.x_pad.view(-1, Cin), _dense2d(gw, Cout, Cin), accumulate=take_accumulate_flag(weight))
+        if bias is not None:
+            pf.relu_bwd_colsum(dy2d, None, None, grad_buffer(bias), take_accumulate_flag(bias))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx_pad = pf.gemm_nn(dy2d, _dense2d(w, Cout, Cin)).view(N, H + 2, W + 2, Cin)
+            dx = pf.nchw_view(dx_pad, N, Cin, H, W)
+        return dx, None, None, None
+
+
+class _ConvPatchFn(torch.autograd.Function):
+    """Any other convolution (7x7 stride 2, 1x1 / 3x3 stride 2, ...): patch matrix + contraction."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, geom):
+        kh, kw, stride, pad = geom
+        w = weight.detach()
+        N, Cin, H, W = x.shape
+        Cout, kpad = w.shape[0], w.stride(0)
+        col, Ho, Wo = pf.im2col(x, kh, kw, stride, pad, kpad, w.dtype)
+        y2d = pf.gemm_nt(col, _dense2d(w, Cout, kpad), bias=bias.detach() if bias is not None else None)
+        ctx.col, ctx.params, ctx.geom = col, (weight, bias), (N, Cin, H, W, Cout, Ho, Wo, kh, kw, stride, pad, kpad)
+        return y2d.view(N, Ho, Wo, Cout).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        weight, bias = ctx.params
+        N, Cin, H, W, Cout, Ho, Wo, kh, kw, stride, pad, kpad = ctx.geom
+        w = weight.detach()
+        dy2d = _dense_nhwc(dy, w.dtype)
+        gw = grad_buffer(weight)
+        pf.gemm_tn(dy2d, ctx.col, _dense2d(gw, Cout, kpad), accumulate=take_accumulate_flag(weight))
+        if bias is not None:
+            pf.relu_bwd_colsum(dy2d, None, None, grad_buffer(bias), take_accumulate_flag(bias))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dcol = pf.gemm_nn(dy2d, _dense2d(w, Cout, kpad))
+            dx = pf.nchw_view(pf.col2im_pnhwc(dcol, N, Cin, H, W, kh, kw, stride, pad, Ho, Wo), N, Cin, H, W)
+        return dx, None, None, None
+
+
+class NativeConvGeneric(nn.Module):
+    """Conv2d with a square kernel, any stride / padding, groups = 1, dilation 1, that is not 3x3 / stride 1."""
+
+    def __init__(self, conv):
+        super().__init__()
+        self.in_channels, self.out_channels = conv.in_channels, conv.out_channels
+        self.kernel_size, self.stride, self.padding = conv.kernel_size, conv.stride, conv.padding
+        self.out_nchw = True
+        self.is_1x1 = conv.kernel_size == (1, 1) and conv.stride == (1, 1) and conv.padding == (0, 0) \
+            and conv.in_channels % 8 == 0
+        w = conv.weight.data
+        cout, cin, kh, kw = w.shape
+        if not self.is_1x1:
+            K = kh * kw * cin
+            kpad = K if K % 8 == 0 else ((K + 31) // 32) * 32
+            store = torch.zeros(cout * kpad, dtype=w.dtype, device=w.device)
+            view = store.as_strided((cout, cin, kh, kw), (kpad, 1, kw * cin, cin))
+            view.copy_(w)
+            conv.weight.data = view
+        self.weight, self.bias = conv.weight, conv.bias
+        _mark_native(self.weight, self.bias)
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.Conv2d) and m.groups == 1 and m.dilation == (1, 1) and m.padding_mode == "zeros"
+                and m.kernel_size[0] == m.kernel_size[1] and m.stride[0] == m.stride[1]
+                and m.padding[0] == m.padding[1] and m.out_channels % 8 == 0 and not NativeConv2d.supports(m))
+
+    def forward(self, x):
+        if self.is_1x1:
+            return _Conv1x1Fn.apply(x, self.weight, self.bias, self.out_nchw)
+        return _ConvPatchFn.apply(x, self.weight, self.bias,
+                                  (self.kernel_size[0], self.kernel_size[1], self.stride[0], self.padding[0]))
+
+
+class _MaxPool3s2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_nchw):
+        N, C, H, W = x.shape
+        x_pad = pf.as_padded(x)
+        y_pad = pf.maxpool3s2_fwd(x_pad)
+        ctx.x_pad, ctx.geom = x_pad, (N, C, H, W)
+        Ho, Wo = y_pad.shape[1] - 2, y_pad.shape[2] - 2
+        return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, Ho, Wo)
+
+    @staticmethod
+    def backward(ctx, dy):
+        N, C, H, W = ctx.geom
+        return pf.nchw_view(pf.maxpool3s2_bwd(ctx.x_pad, pf.as_padded(dy)), N, C, H, W), None
+
+
+class NativeMaxPool3s2(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.out_nchw = True
+
+    @staticmethod
+    def supports(m):
+        def eq(v, k):
+            return v == k or v == (k, k)
+        return (isinstance(m, nn.MaxPool2d) and eq(m.kernel_size, 3) and eq(m.stride, 2) and eq(m.padding, 1)
+                and eq(m.dilation, 1) and not m.ceil_mode and not m.return_indices)
+
+    def forward(self, x):
+        return _MaxPool3s2Fn.apply(x, self.out_nchw)
+
+
+class _GlobalAvgPoolFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        N, C, H, W = x.shape
+        ctx.geom = (N, C, H, W)
+        return pf.avgpool_fwd(pf.as_padded(x))
+
+    @staticmethod
+    def backward(ctx, dy):
+        N, C, H, W = ctx.geom
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        return pf.nchw_view(pf.avgpool_bwd(dyc, N, C, H, W), N, C, H, W)
+
+
+class NativeGlobalAvgPool(nn.Module):
+    """AvgPool2d whose window is the whole feature map (AvgPool2d(7) on the 7x7 map of ResNet-50)."""
+
+    def __init__(self, kernel):
+        super().__init__()
+        self.kernel = kernel
+
+    @staticmethod
+    def supports(m):
+        k = m.kernel_size if isinstance(m, nn.AvgPool2d) else None
+        return isinstance(m, nn.AvgPool2d) and (m.padding in (0, (0, 0))) and not m.ceil_mode and k is not None
+
+    def forward(self, x):
+        k = self.kernel if isinstance(self.kernel, tuple) else (self.kernel, self.kernel)
+        if (x.shape[2], x.shape[3]) != k:
+            raise pf._lib.PipedreamB200Error("NativeGlobalAvgPool: window %s does not cover the %dx%d map" % (
+                k, x.shape[2], x.shape[3]))
+        return _GlobalAvgPoolFn.apply(x)
+
 # --------------------------------------------------------------------------- #
 # ReLU / MaxPool / Dropout
 # --------------------------------------------------------------------------- #
@@ -653,9 +884,16 @@ class NativeLabelSmoothing(nn.Module):
 # --------------------------------------------------------------------------- #
 # stage rewriting
 # --------------------------------------------------------------------------- #
-_LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway)
+_LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway, NativeBatchNorm2d, NativeConvGeneric,
+                 NativeMaxPool3s2, NativeGlobalAvgPool)
 _NATIVE_TYPES = _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
-                                 NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention)
+                                 NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention,
+                                 NativeBatchNorm2d, NativeConvGeneric, NativeMaxPool3s2, NativeGlobalAvgPool)
+
+
+_PADDED_PRODUCERS = (NativeConv2d, NativeReLU, NativeMaxPool2d, NativeBatchNorm2d, NativeMaxPool3s2, NativeConvGeneric)
+_PADDED_CONSUMERS = (NativeConv2d, NativeReLU, NativeMaxPool2d, NativeBatchNorm2d, NativeConvGeneric, NativeMaxPool3s2,
+                     NativeGlobalAvgPool)
 
 
 def _swap_leaf(m):
@@ -664,6 +902,14 @@ def _swap_leaf(m):
         return m
     if NativeConv2d.supports(m):
         return NativeConv2d(m)
+    if NativeConvGeneric.supports(m):
+        return NativeConvGeneric(m)
+    if NativeBatchNorm2d.supports(m):
+        return NativeBatchNorm2d(m)
+    if NativeMaxPool3s2.supports(m):
+        return NativeMaxPool3s2()
+    if NativeGlobalAvgPool.supports(m):
+        return NativeGlobalAvgPool(m.kernel_size)
     if isinstance(m, nn.ReLU):
         return NativeReLU()
     if NativeMaxPool2d.supports(m):
@@ -699,14 +945,12 @@ def nativize(module):
     single = _swap_leaf(module)
     if single is not module:
         return single
-    def swap_children(parent):
-        for n, child in list(parent.named_children()):
-            new = _swap_leaf(child)
-            if new is not child:
-                setattr(parent, n, new)
-            elif not isinstance(child, _NATIVE_TYPES) and any(True for _ in child.children()):
-                swap_children(child)        # a container (e.g. an attention block): look inside
-    swap_children(module)
+    for n, child in list(module.named_children()):
+        new = _swap_leaf(child)
+        if new is not child:
+            setattr(module, n, new)
+        elif not isinstance(child, _NATIVE_TYPES) and any(True for _ in child.children()):
+            nativize(child)             # a container (residual block, attention block): plan it on its own
     try:
         import torch.fx as fx
 
@@ -724,7 +968,7 @@ def nativize(module):
     # 1. fold ReLU into its producer
     for node in graph.nodes:
         m = target_mod(node)
-        if isinstance(m, (NativeConv2d, NativeLinear)) and len(node.users) == 1:
+        if isinstance(m, (NativeConv2d, NativeLinear, NativeBatchNorm2d)) and len(node.users) == 1:
             user = next(iter(node.users))
             um = target_mod(user)
             if isinstance(um, NativeReLU) and user.args == (node,):
@@ -739,7 +983,7 @@ def nativize(module):
     decided = {}
     for node in graph.nodes:
         m = target_mod(node)
-        if not isinstance(m, (NativeConv2d, NativeReLU, NativeMaxPool2d)):
+        if not isinstance(m, _PADDED_PRODUCERS):
             continue
         frontier, ok = list(node.users), len(node.users) > 0
         while frontier and ok:
@@ -748,7 +992,7 @@ def nativize(module):
             if isinstance(um, FusedAway):
                 frontier.extend(u.users)
                 ok = len(u.users) > 0
-            elif not isinstance(um, (NativeConv2d, NativeReLU, NativeMaxPool2d)):
+            elif not isinstance(um, _PADDED_CONSUMERS):
                 ok = False
         decided[id(m)] = decided.get(id(m), True) and ok
         m.out_nchw = not decided[id(m)]

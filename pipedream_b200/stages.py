@@ -249,3 +249,111 @@ class SyntheticTranslation:
             order = torch.argsort(src_len, descending=True, stable=True)
             src_len, tgt_len = src_len[order], tgt_len[order]
             yield (self._side(src_len, g), src_len.tolist()), (self._side(tgt_len, g), tgt_len.tolist())
+
+
+# --------------------------------------------------------------------------- #
+# ResNet-50 (v1.5: the stride of a bottleneck sits on its 3x3 convolution), straight pipeline
+# --------------------------------------------------------------------------- #
+class Bottleneck(nn.Module):
+    """1x1 -> 3x3 (stride) -> 1x1 (x4) with BatchNorm after each convolution and a projection shortcut when
+    the shape changes; the layer mix of runtime/image_classification/models/resnet50/gpus=4/stage*.py."""
+
+    def __init__(self, cin, width, stride):
+        super().__init__()
+        cout = 4 * width
+        self.conv1 = nn.Conv2d(cin, width, kernel_size=(1, 1), stride=(1, 1), bias=False)
+        self.bn1 = nn.BatchNorm2d(width)
+        self.relu1 = nn.ReLU(inplace=True)
+        self.conv2 = nn.Conv2d(width, width, kernel_size=(3, 3), stride=(stride, stride), padding=(1, 1), bias=False)
+        self.bn2 = nn.BatchNorm2d(width)
+        self.relu2 = nn.ReLU(inplace=True)
+        self.conv3 = nn.Conv2d(width, cout, kernel_size=(1, 1), stride=(1, 1), bias=False)
+        self.bn3 = nn.BatchNorm2d(cout)
+        self.has_projection = stride != 1 or cin != cout
+        if self.has_projection:
+            self.down_conv = nn.Conv2d(cin, cout, kernel_size=(1, 1), stride=(stride, stride), bias=False)
+            self.down_bn = nn.BatchNorm2d(cout)
+        self.relu3 = nn.ReLU(inplace=True)
+
+    def forward(self, x):
+        out = self.relu1(self.bn1(self.conv1(x)))
+        out = self.relu2(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        shortcut = self.down_bn(self.down_conv(x)) if self.has_projection else x
+        return self.relu3(out + shortcut)
+
+
+class ResNetStem(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.conv = nn.Conv2d(3, 64, kernel_size=(7, 7), stride=(2, 2), padding=(3, 3), bias=False)
+        self.bn = nn.BatchNorm2d(64)
+        self.relu = nn.ReLU(inplace=True)
+        self.pool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1, dilation=1, ceil_mode=False)
+
+    def forward(self, x):
+        return self.pool(self.relu(self.bn(self.conv(x))))
+
+
+class ResNetHead(nn.Module):
+    def __init__(self, num_classes=1000):
+        super().__init__()
+        self.pool = nn.AvgPool2d(kernel_size=7, stride=1, padding=0)
+        self.fc = nn.Linear(2048, num_classes)
+
+    def forward(self, x):
+        out = self.pool(x)
+        return self.fc(out.view(out.size(0), -1))
+
+
+class ResNetStage(nn.Module):
+    def __init__(self, parts):
+        super().__init__()
+        self.parts = nn.ModuleList(parts)
+        for m in self.modules():                      # resnet50/gpus=4/stage1.py:114-120
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+            elif isinstance(m, nn.Linear):
+                nn.init.normal_(m.weight, 0, 0.01)
+                nn.init.constant_(m.bias, 0)
+
+    def forward(self, input0):
+        out = input0.clone()
+        for p in self.parts:
+            out = p(out)
+        return out
+
+
+def resnet50(num_stages=1, stage_to_rank_map=None):
+    """ResNet-50 cut at residual-block boundaries into `num_stages` consecutive stages (1, 2, 3, 4, 6, 8, 9, 18)."""
+    units = [("stem",)]
+    cin = 64
+    for width, blocks, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
+        for b in range(blocks):
+            units.append(("block", cin, width, stride if b == 0 else 1))
+            cin = 4 * width
+    units.append(("head",))
+    per = (len(units) + num_stages - 1) // num_stages
+    chunks = [units[i:i + per] for i in range(0, len(units), per)]
+
+    class _Pkg(StagePackage):
+        def stages(self_inner):
+            out = []
+            for ch in chunks:
+                parts = []
+                for u in ch:
+                    if u[0] == "stem":
+                        parts.append(ResNetStem())
+                    elif u[0] == "head":
+                        parts.append(ResNetHead())
+                    else:
+                        parts.append(Bottleneck(u[1], u[2], u[3]))
+                out.append(ResNetStage(parts))
+            return out
+
+    n = len(chunks)
+    ranks = stage_to_rank_map or {s: [s] for s in range(n)}
+    return _Pkg("resnet50", None, {"module_to_stage_map": list(range(n)) + [n - 1], "stage_to_rank_map": ranks})

@@ -1,0 +1,266 @@
+"""ResNet-50 pieces on the GPU: batch norm, the convolution variants that run through a patch matrix, the
+3x3/2 max-pool and the global average pool against torch; then the whole network through StageRuntime
+against the CPU oracle (same stage builder, plain torch modules, fp32)."""
+import copy
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+from oracle import pipedream_oracle as oracle            # noqa: E402
+from pipedream_b200 import layers, runtime, schedule, sgd, stages  # noqa: E402
+from pipedream_b200 import functional as pf              # noqa: E402
+
+torch.backends.cudnn.allow_tf32 = False
+torch.backends.cuda.matmul.allow_tf32 = False
+TOL = {torch.float32: 2e-4, torch.bfloat16: 2e-2}
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12)).item()
+
+
+def rnd(*shape, seed):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)).cuda()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("relu", [False, True])
+def test_batchnorm(dtype, relu):
+    N, C, H, W = 6, 64, 10, 12
+    ref = torch.nn.BatchNorm2d(C).cuda()
+    with torch.no_grad():
+        ref.weight.uniform_(0.5, 1.5)
+        ref.bias.uniform_(-0.5, 0.5)
+    nat = layers.NativeBatchNorm2d(copy.deepcopy(ref).to(dtype))
+    nat.fuse_relu = relu
+    x = (rnd(N, C, H, W, seed=1) * 2 + 0.5).to(dtype)
+    dy = rnd(N, C, H, W, seed=2).to(dtype)
+    ref.load_state_dict({k: v.float() for k, v in nat.state_dict().items()})
+    xr = x.float().detach().clone().requires_grad_(True)
+    yr = ref(xr)
+    yr = F.relu(yr) if relu else yr
+    yr.backward(dy.float())
+    xn = x.detach().clone().requires_grad_(True)
+    yn = nat(xn)
+    yn.backward(dy)
+    tol = TOL[dtype]
+    assert rel(yn, yr) <= tol and rel(xn.grad, xr.grad) <= 2 * tol
+    assert rel(nat.weight._pd_grad, ref.weight.grad) <= 2 * tol and rel(nat.bias._pd_grad, ref.bias.grad) <= 2 * tol
+    assert rel(nat.running_mean, ref.running_mean) <= tol and rel(nat.running_var, ref.running_var) <= tol
+    nat.eval(); ref.eval()
+    assert rel(nat(x), F.relu(ref(x.float())) if relu else ref(x.float())) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("cin,cout,k,s,p,hw", [(3, 64, 7, 2, 3, 32), (64, 128, 1, 2, 0, 16), (64, 64, 3, 2, 1, 16),
+                                                (64, 256, 1, 1, 0, 14), (128, 128, 3, 2, 1, 15)])
+def test_conv_variants(dtype, cin, cout, k, s, p, hw):
+    ref = torch.nn.Conv2d(cin, cout, k, s, p, bias=False).cuda()
+    nat = copy.deepcopy(ref).to(dtype)
+    ref.load_state_dict({kk: v.float() for kk, v in nat.state_dict().items()})
+    nat = layers.NativeConvGeneric(nat)
+    x = rnd(4, cin, hw, hw, seed=3).to(dtype)
+    xr = x.float().detach().clone().requires_grad_(True)
+    yr = ref(xr)
+    dy = rnd(*yr.shape, seed=4).to(dtype)
+    yr.backward(dy.float())
+    xn = x.detach().clone().requires_grad_(cin != 3)
+    yn = nat(xn)
+    yn.backward(dy)
+    tol = TOL[dtype]
+    assert yn.shape == yr.shape and rel(yn, yr) <= tol
+    assert rel(nat.weight._pd_grad, ref.weight.grad) <= 2 * tol
+    if cin != 3:
+        assert rel(xn.grad, xr.grad) <= 2 * tol
+    assert pf.gemm_poll_error() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_resnet_pools(dtype):
+    x = rnd(3, 64, 17, 20, seed=5).to(dtype)
+    xr = x.float().detach().clone().requires_grad_(True)
+    yr = F.max_pool2d(xr, 3, 2, 1)
+    dy = rnd(*yr.shape, seed=6).to(dtype)
+    yr.backward(dy.float())
+    xn = x.detach().clone().requires_grad_(True)
+    yn = layers.NativeMaxPool3s2()(xn)
+    yn.backward(dy)
+    assert torch.equal(yn.float(), yr.detach()) and torch.equal(xn.grad.float(), xr.grad.to(dtype).float())
+    x7 = rnd(3, 64, 7, 7, seed=7).to(dtype)
+    a = x7.float().detach().clone().requires_grad_(True)
+    ar = F.avg_pool2d(a, 7)
+    g = rnd(3, 64, 1, 1, seed=8).to(dtype)
+    ar.backward(g.float())
+    b = x7.detach().clone().requires_grad_(True)
+    bn = layers.NativeGlobalAvgPool(7)(b)
+    bn.backward(g)
+    assert rel(bn, ar) <= TOL[dtype] and rel(b.grad, a.grad) <= TOL[dtype]
+
+
+def _runtime_for(stage_module, fp16, batch):
+    model = [(stage_module, ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    r = runtime.StageRuntime(
+        model=model, distributed_backend=None, fp16=fp16, loss_scale=1, training_tensor_shapes={},
+        eval_tensor_shapes={}, training_tensor_dtypes={}, inputs_module_destinations={"input": 0},
+        target_tensor_names={"target"},
+        configuration_maps={"module_to_stage_map": None, "stage_to_rank_map": None, "stage_to_depth_map": None},
+        master_addr=None, rank=None, local_rank=0, num_ranks_in_server=1, verbose_freq=0,
+        model_type=runtime.IMAGE_CLASSIFICATION)
+    opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=1, lr=0.01,
+                                    momentum=0.9, weight_decay=1e-4)
+    return r, opt
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_resnet50_training_steps_match_oracle(fp16):
+    """Whole ResNet-50 (BN in training mode, SGD 0.01 / 0.9 / 1e-4), batch 8, 3 steps, against the same
+    network built from plain torch modules and trained by the CPU oracle."""
+    batch, n = 8, 3
+    torch.manual_seed(0)
+    st = stages.resnet50(1).stages()[0]
+    ref = copy.deepcopy(st)
+    ref0 = copy.deepcopy(st)
+    r, opt = _runtime_for(st, fp16, batch)
+    blk = r.modules()[0].parts[1]
+    assert isinstance(blk.bn1, layers.NativeBatchNorm2d) and blk.bn1.fuse_relu
+    assert isinstance(blk.conv2, layers.NativeConv2d) and isinstance(blk.conv1, layers.NativeConvGeneric)
+    omodel = [(ref, ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    pipe = oracle.PipelineOracle(omodel, [0, 0], {0: [0]}, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=1e-4))
+    pipe.run({0: stages.SyntheticImages(batch, n)}, n)
+    r.train(n)
+    r.set_loader(stages.SyntheticImages(batch, n))
+    losses = []
+    schedule.train_1f1b(r, opt, n, on_forward=lambda i, rr: losses.append(rr.loss.item()))
+    ref_losses = pipe.ranks[0]["losses"]
+    # control: the same modules on torch's own CUDA kernels in the same precision
+    dtype = torch.bfloat16 if fp16 else torch.float32
+    ctrl = copy.deepcopy(ref0).cuda().to(dtype)
+    copt = torch.optim.SGD([p.detach().float().requires_grad_(True) for p in ctrl.parameters()] if fp16
+                           else ctrl.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
+    ctrl_losses = []
+    for xb, yb in stages.SyntheticImages(batch, n):
+        out = ctrl(xb.cuda().to(dtype))
+        l = F.cross_entropy(out.float(), yb.cuda())
+        ctrl_losses.append(l.item())
+        for p in ctrl.parameters():
+            p.grad = None
+        l.backward()
+        if fp16:
+            masters = copt.param_groups[0]["params"]
+            for m, p in zip(masters, ctrl.parameters()):
+                m.grad = p.grad.float()
+            copt.step()
+            with torch.no_grad():
+                for m, p in zip(masters, ctrl.parameters()):
+                    p.copy_(m)
+        else:
+            copt.step()
+    print("\n[%s] resnet50 losses %s vs oracle %s; torch CUDA control %s" % (
+        "bf16" if fp16 else "fp32", [round(v, 4) for v in losses], [round(v, 4) for v in ref_losses],
+        [round(v, 4) for v in ctrl_losses]))
+    # With BN at random initialisation one SGD step amplifies rounding differences of the gradients (see the
+    # gradient test): the bar is met on the first loss, and later ones must stay within a small multiple of
+    # what torch's own CUDA kernels of the same precision deviate from the CPU run.
+    bar = 2e-2 if fp16 else 1e-3
+    assert abs(losses[0] - ref_losses[0]) <= bar * abs(ref_losses[0])
+    for a, b, c in zip(losses, ref_losses, ctrl_losses):
+        assert abs(a - b) <= max(bar * abs(b), 3.0 * abs(c - b)) + 5e-3 * abs(b), (losses, ref_losses, ctrl_losses)
+    assert pf.gemm_poll_error() == 0
+    if not fp16:
+        sd, cd = ref.state_dict(), ctrl.state_dict()
+        dn, dc = [], []
+        for k, v in r.modules()[0].state_dict().items():
+            if "num_batches" not in k:
+                dn.append(rel(v.cpu(), sd[k]))
+                dc.append(rel(cd[k].cpu(), sd[k]))
+        mn, mc = sorted(dn)[len(dn) // 2], sorted(dc)[len(dc) // 2]
+        print("median deviation of weights / running statistics from the CPU run: native %.2e, torch CUDA %.2e" % (mn, mc))
+        assert mn <= 1.5 * mc + 1e-4
+
+
+def _cos(a, b):
+    return (a.flatten() @ b.flatten() / (a.norm() * b.norm()).clamp_min(1e-30)).item()
+
+
+def _compare_gradients(base, x, head, fp16, min_checked, norm_tol=None):
+    """Gradients of `base` (plain torch modules) for input x under the scalar `head(output)`: float64 on the
+    CPU is the truth, torch's CUDA modules in the working precision are the control, the nativized copy is
+    the candidate.  Rounding noise is amplified on the way back through normalised layers (and the gradient
+    of a BN bias that feeds another BN is zero in exact arithmetic, so what is computed is all noise):
+    a gradient is compared where the control itself reaches cosine >= 0.9 to the truth, with a margin of a
+    few times the control's own distance."""
+    dtype = torch.bfloat16 if fp16 else torch.float32
+    ctrl = copy.deepcopy(base).cuda().to(dtype)
+    m64 = copy.deepcopy(base).double()
+    m64.load_state_dict({k: v.double().cpu() for k, v in ctrl.state_dict().items()})
+    xq = x.to(dtype)
+    x64 = xq.double().cpu().requires_grad_(True)
+    head(m64(x64)).backward()
+    g64 = {n: p.grad for n, p in m64.named_parameters()}
+    xc = xq.cuda().detach().clone().requires_grad_(True)
+    head(ctrl(xc).float()).backward()
+    gc = {n: p.grad.double().cpu() for n, p in ctrl.named_parameters()}
+    nat = layers.nativize(copy.deepcopy(base).cuda().to(dtype))
+    xn = xq.cuda().detach().clone().requires_grad_(x.shape[1] != 3)
+    head(nat(xn).float()).backward()
+    gn = {n: p._pd_grad.double().cpu() for n, p in nat.named_parameters()}
+    if x.shape[1] != 3:
+        g64["(input)"], gc["(input)"], gn["(input)"] = x64.grad, xc.grad.double().cpu(), xn.grad.double().cpu()
+    worst, checked = (1.0, None, None), 0
+    for n in g64:
+        cn, cc = _cos(gn[n], g64[n]), _cos(gc[n], g64[n])
+        t = g64[n].norm().clamp_min(1e-30)
+        rn, rc = (gn[n].norm() / t).item(), (gc[n].norm() / t).item()
+        if cn - cc < worst[0]:
+            worst = (round(cn - cc, 6), n, (round(cn, 5), round(cc, 5), round(rn, 4), round(rc, 4)))
+        if cc < 0.9:
+            continue
+        checked += 1
+        margin = max(3.0 * (1.0 - cc), 0.02 if fp16 else 1e-4)
+        assert cn >= cc - margin, "%s: cosine to float64 %.5f, torch control %.5f" % (n, cn, cc)
+        assert abs(rn - 1) <= max(3.0 * abs(rc - 1), norm_tol or (0.05 if fp16 else 2e-3)), \
+            "%s: norm ratio to float64 %.4f, torch control %.4f" % (n, rn, rc)
+    assert checked >= min_checked * len(g64), (checked, len(g64))
+    assert pf.gemm_poll_error() == 0
+    return checked, len(g64), worst
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_resnet50_stage_gradients_vs_float64(fp16):
+    """Each stage of the 6-stage cut (3 units each: stem / bottleneck blocks / head) on its own, batch 8:
+    parameter and input gradients against float64."""
+    torch.manual_seed(0)
+    sts = stages.resnet50(6).stages()
+    shapes = [(3, 224), (256, 56), (512, 28), (1024, 14), (1024, 14), (2048, 7)]
+    g = torch.Generator().manual_seed(11)
+    for k, (st, (c, hw)) in enumerate(zip(sts, shapes)):
+        x = torch.randn(8, c, hw, hw, generator=g)
+        if c != 3:
+            x = x.relu()
+        if k == len(sts) - 1:
+            y = torch.randint(0, 1000, (8,), generator=g)
+            head = lambda o, y=y: F.cross_entropy(o, y.to(o.device))
+        else:
+            with torch.no_grad():
+                oshape = st(x[:1]).shape[1:]
+            st.zero_grad()
+            dy = torch.randn(8, *oshape, generator=g)
+            head = lambda o, dy=dy: (o * dy.to(o.device, o.dtype)).sum()
+        checked, total, worst = _compare_gradients(st, x, head, fp16, 0.6)
+        print("\n[%s] stage %d: %d of %d gradients compared; worst cosine gap %s" % (
+            "bf16" if fp16 else "fp32", k, checked, total, worst))
+
+
+def test_resnet50_gradients_vs_float64():
+    """The whole network in fp32 (batch 8, BN in training mode), cross-entropy loss."""
+    torch.manual_seed(0)
+    base = stages.resnet50(1).stages()[0]
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(8, 3, 224, 224, generator=g)
+    y = torch.randint(0, 1000, (8,), generator=g)
+    checked, total, worst = _compare_gradients(base, x, lambda o: F.cross_entropy(o, y.to(o.device)), False, 0.6,
+                                                norm_tol=2e-2)
+    print("\n[fp32] whole network: %d of %d gradients compared; worst cosine gap %s" % (checked, total, worst))
