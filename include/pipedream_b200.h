@@ -96,19 +96,21 @@ int pd_add(const void* a, const void* b, void* y, int64_t n, int dtype, void* st
 /* torch.nn.BatchNorm2d of the ResNet-50 stages (runtime/image_classification/models/resnet50/gpus=4/
  * stage1.py:12-55; cuDNN batch norm in the reference), on padded NHWC.  Training forward computes the
  * batch statistics (mean, invstd: fp32 [C], saved), updates running_mean / running_var like torch
- * (momentum, unbiased variance), applies gamma/beta and optionally the ReLU that follows.  Backward
- * takes the saved statistics; y_pad != NULL means the forward fused a ReLU.  workspace: fp32 scratch
- * of pd_bn_workspace_bytes(C) bytes; sums_ws: fp32 [2*C].  C <= 2048.                             */
+ * (momentum, unbiased variance), applies gamma/beta, then optionally adds res_pad (the shortcut of a
+ * bottleneck block, stage1.py forward: `out = out + identity`) and applies the ReLU that follows.
+ * Backward takes the saved statistics; y_pad != NULL means the forward applied a ReLU; dres_pad (may be
+ * NULL) receives the masked dy, the gradient of the residual input.  workspace: fp32 scratch of
+ * pd_bn_workspace_bytes(C) bytes; sums_ws: fp32 [2*C].  C <= 2048.                                 */
 int64_t pd_bn_workspace_bytes(int C);
-int pd_bn_fwd(int dtype, const void* x_pad, int N, int H, int W, int C, const void* gamma, const void* beta,
-              float eps, float momentum, int relu, float* mean, float* invstd, float* running_mean,
+int pd_bn_fwd(int dtype, const void* x_pad, const void* res_pad, int N, int H, int W, int C, const void* gamma,
+              const void* beta, float eps, float momentum, int relu, float* mean, float* invstd, float* running_mean,
               float* running_var, void* y_pad, void* workspace, int64_t workspace_bytes, void* stream);
-int pd_bn_apply(int dtype, const void* x_pad, int N, int H, int W, int C, const void* gamma, const void* beta,
-                const float* mean, const float* invstd, int relu, void* y_pad, void* stream);
+int pd_bn_apply(int dtype, const void* x_pad, const void* res_pad, int N, int H, int W, int C, const void* gamma,
+                const void* beta, const float* mean, const float* invstd, int relu, void* y_pad, void* stream);
 int pd_bn_bwd(int dtype, const void* x_pad, const void* dy_pad, const void* y_pad, int N, int H, int W, int C,
               const void* gamma, const float* mean, const float* invstd, float* dgamma, float* dbeta,
-              int accumulate, void* dx_pad, float* sums_ws, void* workspace, int64_t workspace_bytes,
-              void* stream);
+              int accumulate, void* dx_pad, void* dres_pad, float* sums_ws, void* workspace,
+              int64_t workspace_bytes, void* stream);
 /* Convolution variants other than 3x3/stride 1 (resnet50/gpus=4/stage0.py:10: 7x7 stride 2; 1x1 and 3x3
  * stride 2) run as a patch matrix through pd_gemm_*: pd_im2col builds [N*Ho*Wo, Kpad] (k = (r*kw+s)*C + c)
  * from an any-stride NCHW source, pd_col2im_pnhwc gathers the patch-matrix gradient back into padded NHWC. */

@@ -157,6 +157,197 @@ avgpool_bwd_kernel(const T* __restrict__ dy, int N, int C, int H, int W, T* __re
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// 16-byte variants (bf16, channels innermost, C % 8 == 0): one thread per 8 channels
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 t = __bfloat1622float2(p[k]);
+    f[2 * k] = t.x;
+    f[2 * k + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  return u;
+}
+
+// src: bf16, element strides sN/sH/sW (multiples of 8), channel stride 1.  dst: [rows, Kpad] bf16.
+__global__ void __launch_bounds__(kThreads)
+im2col_v8_kernel(const __nv_bfloat16* __restrict__ src, int64_t sN, int64_t sH, int64_t sW, int N, int C, int H, int W,
+                 int kh, int kw, int stride, int pad, int Ho, int Wo, int Kpad, uint4* __restrict__ dst) {
+  const int KV = Kpad / 8;
+  const int64_t total = (int64_t)N * Ho * Wo * KV;
+  const int K = kh * kw * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int k = (int)(i % KV) * 8;
+    const int64_t p = i / KV;
+    const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (k < K) {
+      const int t = k / C, c = k - t * C;
+      const int h = ho * stride - pad + t / kw, w = wo * stride - pad + t % kw;
+      if (h >= 0 && h < H && w >= 0 && w < W)
+        v = *reinterpret_cast<const uint4*>(src + n * sN + h * sH + w * sW + c);
+    }
+    dst[i] = v;
+  }
+}
+
+// Any source layout / channel count (the 3-channel fp32 NCHW network input): 8 consecutive patch-matrix
+// columns per thread, gathered one by one, stored as one 16-byte vector.
+template <typename S>
+__global__ void __launch_bounds__(kThreads)
+im2col_gather8_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW, int N, int C, int H, int W,
+                      int kh, int kw, int stride, int pad, int Ho, int Wo, int Kpad, uint4* __restrict__ dst) {
+  const int KV = Kpad / 8;
+  const int64_t total = (int64_t)N * Ho * Wo * KV;
+  const int K = kh * kw * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int k0 = (int)(i % KV) * 8;
+    const int64_t p = i / KV;
+    const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
+    const int hb = ho * stride - pad, wb = wo * stride - pad;
+    const S* base = src + n * sN;
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = k0 + j;
+      float v = 0.f;
+      if (k < K) {
+        const int t = k / C, c = k - t * C;
+        const int r = t / kw;
+        const int h = hb + r, w = wb + (t - r * kw);
+        if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(base[c * sC + h * sH + w * sW]);
+      }
+      f[j] = v;
+    }
+    dst[i] = pack8(f);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+col2im_v8_kernel(const __nv_bfloat16* __restrict__ dcol, int N, int C, int H, int W, int kh, int kw, int stride, int pad,
+                 int Ho, int Wo, int Kpad, uint4* __restrict__ dx) {
+  const int Hp = H + 2, Wp = W + 2, C8 = C / 8;
+  const int64_t total = (int64_t)N * Hp * Wp * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8) * 8;
+    const int64_t p = i / C8;
+    const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), n = (int)(p / ((int64_t)Wp * Hp));
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    if (hp >= 1 && hp <= H && wp >= 1 && wp <= W) {
+      const int h = hp - 1, w = wp - 1;
+      for (int r = 0; r < kh; ++r) {
+        const int hn = h + pad - r;
+        if (hn < 0 || hn % stride) continue;
+        const int ho = hn / stride;
+        if (ho >= Ho) continue;
+        for (int s = 0; s < kw; ++s) {
+          const int wn = w + pad - s;
+          if (wn < 0 || wn % stride) continue;
+          const int wo = wn / stride;
+          if (wo >= Wo) continue;
+          const uint4 v = *reinterpret_cast<const uint4*>(dcol + (((int64_t)n * Ho + ho) * Wo + wo) * Kpad + (r * kw + s) * C + c);
+          float f[8];
+          unpack8(v, f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        }
+      }
+    }
+    dx[i] = pack8(acc);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+maxpool3s2_fwd_v8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int W, int Ho, int Wo, uint4* __restrict__ y) {
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const int64_t total = (int64_t)N * Hop * Wop * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int wop = (int)(p % Wop), hop = (int)((p / Wop) % Hop), n = (int)(p / ((int64_t)Wop * Hop));
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (hop >= 1 && hop <= Ho && wop >= 1 && wop <= Wo) {
+      float m[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) m[k] = -INFINITY;
+      const int h0 = (hop - 1) * 2 - 1, w0 = (wop - 1) * 2 - 1;
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+          const int h = h0 + r, w = w0 + s;
+          if (h >= 0 && h < H && w >= 0 && w < W) {
+            float f[8];
+            unpack8(x[(((int64_t)n * Hp + h + 1) * Wp + w + 1) * C8 + c], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m[k] = fmaxf(m[k], f[k]);
+          }
+        }
+      out = pack8(m);
+    }
+    y[i] = out;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+maxpool3s2_bwd_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, int N, int C8, int H, int W, int Ho, int Wo,
+                         uint4* __restrict__ dx) {
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const int64_t total = (int64_t)N * Hp * Wp * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), n = (int)(p / ((int64_t)Wp * Hp));
+    float g[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = 0.f;
+    if (hp >= 1 && hp <= H && wp >= 1 && wp <= W) {
+      const int h = hp - 1, w = wp - 1;
+      for (int ho = max(0, h / 2); ho <= min(Ho - 1, (h + 1) / 2); ++ho)
+        for (int wo = max(0, w / 2); wo <= min(Wo - 1, (w + 1) / 2); ++wo) {
+          const int h0 = ho * 2 - 1, w0 = wo * 2 - 1;
+          const int mine = (h - h0) * 3 + (w - w0);
+          float m[8];
+          int am[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { m[k] = -INFINITY; am[k] = -1; }
+#pragma unroll
+          for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+              const int hh = h0 + r, ww = w0 + s;
+              if (hh >= 0 && hh < H && ww >= 0 && ww < W) {
+                float f[8];
+                unpack8(x[(((int64_t)n * Hp + hh + 1) * Wp + ww + 1) * C8 + c], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  if (f[k] > m[k]) { m[k] = f[k]; am[k] = r * 3 + s; }
+              }
+            }
+          float d[8];
+          unpack8(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C8 + c], d);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (am[k] == mine) g[k] += d[k];
+        }
+    }
+    dx[i] = pack8(g);
+  }
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 }  // namespace
 
 #define PD_T2(dtype, ...)                                               \
@@ -174,7 +365,19 @@ PD_EXPORT int pd_im2col(const void* src, int src_dtype, int64_t sN, int64_t sC, 
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * Ho * Wo * Kpad;
   const int grid = grid_for(total);
-  if (src_dtype == PD_F32 && dst_dtype == PD_F32)
+  if (src_dtype == PD_BF16 && dst_dtype == PD_BF16 && sC == 1 && (C % 8) == 0 && (Kpad % 8) == 0 && (sN % 8) == 0 &&
+      (sH % 8) == 0 && (sW % 8) == 0 && aligned16(src) && aligned16(dst)) {
+    im2col_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sH, sW, N, C, H, W, kh, kw, stride, pad,
+                                                              Ho, Wo, Kpad, (uint4*)dst);
+  } else if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && aligned16(dst)) {
+    if (src_dtype == PD_F32)
+      im2col_gather8_kernel<float><<<grid_for(total / 8), kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, kh, kw,
+                                                                            stride, pad, Ho, Wo, Kpad, (uint4*)dst);
+    else if (src_dtype == PD_BF16)
+      im2col_gather8_kernel<__nv_bfloat16><<<grid_for(total / 8), kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H,
+                                                                                    W, kh, kw, stride, pad, Ho, Wo, Kpad, (uint4*)dst);
+    else PD_REQUIRE(false, "pd_im2col: bad dtype combination");
+  } else if (src_dtype == PD_F32 && dst_dtype == PD_F32)
     im2col_kernel<float, float><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, kh, kw, stride, pad, Ho, Wo, Kpad, (float*)dst);
   else if (src_dtype == PD_F32 && dst_dtype == PD_BF16)
     im2col_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, kh, kw, stride, pad, Ho, Wo, Kpad, (__nv_bfloat16*)dst);
@@ -193,7 +396,12 @@ PD_EXPORT int pd_col2im_pnhwc(const void* dcol, int N, int C, int H, int W, int 
              "pd_col2im_pnhwc: bad arguments");
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
-  PD_T2(dtype, col2im_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)dcol, N, C, H, W, kh, kw, stride, pad, Ho, Wo, Kpad, (T*)dx_pad);)
+  if (dtype == PD_BF16 && (C % 8) == 0 && (Kpad % 8) == 0 && aligned16(dcol) && aligned16(dx_pad)) {
+    col2im_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const __nv_bfloat16*)dcol, N, C, H, W, kh, kw, stride, pad, Ho, Wo, Kpad,
+                                                              (uint4*)dx_pad);
+  } else {
+    PD_T2(dtype, col2im_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)dcol, N, C, H, W, kh, kw, stride, pad, Ho, Wo, Kpad, (T*)dx_pad);)
+  }
   PD_LAUNCH_CHECK("col2im_kernel");
   return PD_OK;
 }
@@ -205,7 +413,11 @@ PD_EXPORT int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, v
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * (Ho + 2) * (Wo + 2) * C;
-  PD_T2(dtype, maxpool3s2_fwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, N, C, H, W, Ho, Wo, (T*)y_pad);)
+  if (dtype == PD_BF16 && (C % 8) == 0 && aligned16(x_pad) && aligned16(y_pad)) {
+    maxpool3s2_fwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint4*)x_pad, N, C / 8, H, W, Ho, Wo, (uint4*)y_pad);
+  } else {
+    PD_T2(dtype, maxpool3s2_fwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, N, C, H, W, Ho, Wo, (T*)y_pad);)
+  }
   PD_LAUNCH_CHECK("maxpool3s2_fwd_kernel");
   return PD_OK;
 }
@@ -218,7 +430,12 @@ PD_EXPORT int pd_maxpool3s2_bwd(const void* x_pad, const void* dy_pad, int N, in
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
-  PD_T2(dtype, maxpool3s2_bwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, (const T*)dy_pad, N, C, H, W, Ho, Wo, (T*)dx_pad);)
+  if (dtype == PD_BF16 && (C % 8) == 0 && aligned16(x_pad) && aligned16(dy_pad) && aligned16(dx_pad)) {
+    maxpool3s2_bwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint4*)x_pad, (const uint4*)dy_pad, N, C / 8, H, W, Ho, Wo,
+                                                                      (uint4*)dx_pad);
+  } else {
+    PD_T2(dtype, maxpool3s2_bwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, (const T*)dy_pad, N, C, H, W, Ho, Wo, (T*)dx_pad);)
+  }
   PD_LAUNCH_CHECK("maxpool3s2_bwd_kernel");
   return PD_OK;
 }

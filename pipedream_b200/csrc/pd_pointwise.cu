@@ -347,6 +347,19 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
   return v;
 }
+
+__global__ void __launch_bounds__(kThreads)
+add_bf16x8_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ y, int64_t nvec) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float fa[8], fb[8];
+    const uint4 va = a[i], vb = b[i];
+    unpack8(va, fa);
+    unpack8(vb, fb);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) fa[k] += fb[k];
+    y[i] = pack8(fa);
+  }
+}
 __device__ __forceinline__ uint4 max8(const uint4& a, const uint4& b) {
   uint4 r;
   const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
@@ -730,7 +743,12 @@ PD_EXPORT int pd_add(const void* a, const void* b, void* y, int64_t n, int dtype
   PD_REQUIRE(a && b && y && n >= 0, "pd_add: bad arguments");
   if (n == 0) return PD_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  PD_DISPATCH_T(dtype, add_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)y, n);)
+  const bool aligned = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)y) & 15) == 0;
+  if (dtype == PD_BF16 && aligned && (n % 8) == 0) {
+    add_bf16x8_kernel<<<grid_cap((n / 8 + kThreads - 1) / kThreads), kThreads, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)y, n / 8);
+  } else {
+    PD_DISPATCH_T(dtype, add_kernel<T><<<grid_cap((n + kThreads - 1) / kThreads), kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)y, n);)
+  }
   PD_LAUNCH_CHECK("add_kernel");
   return PD_OK;
 }

@@ -459,35 +459,36 @@ def _bn_ws(device, C):
     return _workspace(device, _lib.load().pd_bn_workspace_bytes(C))
 
 
-def bn_fwd(x_pad, gamma, beta, eps, momentum, relu, running_mean, running_var):
+def bn_fwd(x_pad, gamma, beta, eps, momentum, relu, running_mean, running_var, res_pad=None):
     N, Hp, Wp, C = x_pad.shape
     dev = x_pad.device
     mean = torch.empty(C, dtype=torch.float32, device=dev)
     invstd = torch.empty(C, dtype=torch.float32, device=dev)
     y = torch.empty_like(x_pad)
     ws = _bn_ws(dev, C)
-    call("pd_bn_fwd", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), float(eps), float(momentum),
+    call("pd_bn_fwd", dt(x_pad), _p(x_pad), _p(res_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), float(eps), float(momentum),
          int(relu), _p(mean), _p(invstd), _p(running_mean), _p(running_var), _p(y), _p(ws), ws.numel(), _stream())
     return y, mean, invstd
 
 
-def bn_apply(x_pad, gamma, beta, mean, invstd, relu):
+def bn_apply(x_pad, gamma, beta, mean, invstd, relu, res_pad=None):
     N, Hp, Wp, C = x_pad.shape
     y = torch.empty_like(x_pad)
-    call("pd_bn_apply", dt(x_pad), _p(x_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), _p(mean), _p(invstd), int(relu),
+    call("pd_bn_apply", dt(x_pad), _p(x_pad), _p(res_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(beta), _p(mean), _p(invstd), int(relu),
          _p(y), _stream())
     return y
 
 
-def bn_bwd(x_pad, dy_pad, y_pad, gamma, mean, invstd, dgamma, dbeta, accumulate):
+def bn_bwd(x_pad, dy_pad, y_pad, gamma, mean, invstd, dgamma, dbeta, accumulate, want_dres=False):
     N, Hp, Wp, C = x_pad.shape
     dev = x_pad.device
     dx = torch.empty_like(x_pad)
+    dres = torch.empty_like(x_pad) if want_dres else None
     sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
     ws = _bn_ws(dev, C)
     call("pd_bn_bwd", dt(x_pad), _p(x_pad), _p(dy_pad), _p(y_pad), N, Hp - 2, Wp - 2, C, _p(gamma), _p(mean), _p(invstd),
-         _p(dgamma), _p(dbeta), int(accumulate), _p(dx), _p(sums), _p(ws), ws.numel(), _stream())
-    return dx
+         _p(dgamma), _p(dbeta), int(accumulate), _p(dx), _p(dres), _p(sums), _p(ws), ws.numel(), _stream())
+    return (dx, dres) if want_dres else dx
 
 
 def im2col(x, kh, kw, stride, pad, kpad, dtype):

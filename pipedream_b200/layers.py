@@ -187,15 +187,17 @@ class NativeConv2d(nn.Module):
 # --------------------------------------------------------------------------- #
 class _BatchNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, mod, fuse_relu, out_nchw):
+    def forward(ctx, x, res, weight, bias, mod, fuse_relu, out_nchw):
         N, C, H, W = x.shape
         g, b = weight.detach(), bias.detach()
         x_pad = pf.as_padded(x, g.dtype)
+        res_pad = pf.as_padded(res, g.dtype) if res is not None else None
         y_pad, mean, invstd = pf.bn_fwd(x_pad, g, b, mod.eps, mod.momentum if mod.momentum is not None else 0.1,
-                                        fuse_relu, mod.running_mean, mod.running_var)
+                                        fuse_relu, mod.running_mean, mod.running_var, res_pad)
         ctx.saved = (x_pad, y_pad if fuse_relu else None, mean, invstd)
         ctx.params = (weight, bias)
         ctx.geom = (N, C, H, W)
+        ctx.has_res = res is not None
         return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, H, W)
 
     @staticmethod
@@ -207,8 +209,17 @@ class _BatchNormFn(torch.autograd.Function):
         dy_pad = pf.as_padded(dy, g.dtype)
         acc = take_accumulate_flag(weight)
         take_accumulate_flag(bias)
-        dx_pad = pf.bn_bwd(x_pad, dy_pad, y_pad, g, mean, invstd, grad_buffer(weight), grad_buffer(bias), acc)
-        return pf.nchw_view(dx_pad, N, C, H, W), None, None, None, None, None
+        dres = None
+        if ctx.has_res and ctx.needs_input_grad[1] and y_pad is not None:
+            # the masked upstream gradient is the shortcut's gradient: written by the same pass
+            dx_pad, dres_pad = pf.bn_bwd(x_pad, dy_pad, y_pad, g, mean, invstd, grad_buffer(weight), grad_buffer(bias),
+                                         acc, want_dres=True)
+            dres = pf.nchw_view(dres_pad, N, C, H, W)
+        else:
+            dx_pad = pf.bn_bwd(x_pad, dy_pad, y_pad, g, mean, invstd, grad_buffer(weight), grad_buffer(bias), acc)
+            if ctx.has_res and ctx.needs_input_grad[1]:
+                dres = pf.nchw_view(dy_pad, N, C, H, W)
+        return pf.nchw_view(dx_pad, N, C, H, W), dres, None, None, None, None, None
 
 
 class NativeBatchNorm2d(nn.Module):
@@ -230,15 +241,46 @@ class NativeBatchNorm2d(nn.Module):
         return (isinstance(m, nn.BatchNorm2d) and m.affine and m.track_running_stats and m.num_features % 8 == 0
                 and m.num_features <= 2048)
 
-    def forward(self, x):
+    def forward(self, x, res=None):
+        """res: optional tensor of x's shape that is added after the normalisation (before the fused ReLU)."""
         if self.training:
             self.num_batches_tracked.add_(1)
-            return _BatchNormFn.apply(x, self.weight, self.bias, self, self.fuse_relu, self.out_nchw)
+            return _BatchNormFn.apply(x, res, self.weight, self.bias, self, self.fuse_relu, self.out_nchw)
         N, C, H, W = x.shape
         invstd = torch.rsqrt(self.running_var + self.eps)
         y_pad = pf.bn_apply(pf.as_padded(x, self.weight.dtype), self.weight.detach(), self.bias.detach(),
-                            self.running_mean, invstd, self.fuse_relu)
+                            self.running_mean, invstd, self.fuse_relu,
+                            pf.as_padded(res, self.weight.dtype) if res is not None else None)
         return pf.unpack_pnhwc(y_pad) if self.out_nchw else pf.nchw_view(y_pad, N, C, H, W)
+
+
+class _ForkFn(torch.autograd.Function):
+    """Two aliases of one padded tensor; the two gradients are summed by one dense pass over the padded
+    buffers (autograd's own accumulation would add strided views and lose the layout)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.geom = x.shape
+        return x.view_as(x), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, d1, d2):
+        if d1 is None or d2 is None:
+            return d1 if d2 is None else d2
+        p1, p2 = pf.padded_of(d1), pf.padded_of(d2)
+        if p1 is None or p2 is None or p1.dtype != p2.dtype:
+            return d1 + d2
+        N, C, H, W = ctx.geom
+        return pf.nchw_view(pf.add(p1, p2), N, C, H, W)
+
+
+class NativeFork(nn.Module):
+    """Inserted by nativize() where a padded result has two consumers (a residual block's input)."""
+
+    def forward(self, x):
+        if not (torch.is_grad_enabled() and x.requires_grad):
+            return x, x
+        return _ForkFn.apply(x)
 
 
 def _dense_nhwc(t, dtype):
@@ -933,24 +975,93 @@ def _swap_leaf(m):
     return m
 
 
+def _is_add(node):
+    import operator
+    if node.op == "call_function":
+        return node.target in (operator.add, operator.iadd, torch.add)
+    return node.op == "call_method" and node.target in ("add", "add_", "__add__", "__iadd__")
+
+
+def _fuse_residual_tails(module, graph, mods):
+    """BatchNorm -> add(shortcut) -> ReLU becomes one call of the BatchNorm module with the shortcut as its
+    second argument; a value with two layout-aware consumers goes through a NativeFork.  Returns True when
+    the graph was changed (the stage then has to run from the rewritten graph, not from its own forward)."""
+    import operator
+    changed = False
+
+    def target_mod(node):
+        return mods.get(node.target) if node.op == "call_module" else None
+
+    def call_sites(target):
+        return sum(1 for n in graph.nodes if n.op == "call_module" and n.target == target)
+
+    for node in list(graph.nodes):
+        if not _is_add(node) or node.kwargs or len(node.args) != 2 or len(node.users) != 1:
+            continue
+        a, b = node.args
+        if not (hasattr(a, "op") and hasattr(b, "op")):
+            continue
+        relu = next(iter(node.users))
+        if not isinstance(target_mod(relu), NativeReLU) or relu.args != (node,) or call_sites(relu.target) != 1:
+            continue
+        for bn_node, other in ((a, b), (b, a)):
+            bm = target_mod(bn_node)
+            if (isinstance(bm, NativeBatchNorm2d) and not bm.fuse_relu and len(bn_node.users) == 1
+                    and len(bn_node.args) == 1 and call_sites(bn_node.target) == 1):
+                with graph.inserting_before(relu):
+                    fused = graph.call_module(bn_node.target, (bn_node.args[0], other))
+                relu.replace_all_uses_with(fused)
+                graph.erase_node(relu)
+                graph.erase_node(node)
+                graph.erase_node(bn_node)
+                bm.fuse_relu = True
+                changed = True
+                break
+    if not changed:
+        return False
+    k = 0
+    for node in list(graph.nodes):
+        if node.op not in ("placeholder", "call_module") or len(node.users) != 2:
+            continue
+        users = list(node.users)
+        if not all(isinstance(target_mod(u), _PADDED_CONSUMERS) for u in users):
+            continue
+        name = "pd_fork%d" % k
+        k += 1
+        module.add_module(name, NativeFork())
+        mods[name] = getattr(module, name)
+        with graph.inserting_after(node):
+            f = graph.call_module(name, (node,))
+        with graph.inserting_after(f):
+            g0 = graph.call_function(operator.getitem, (f, 0))
+        with graph.inserting_after(g0):
+            g1 = graph.call_function(operator.getitem, (f, 1))
+        users[0].replace_input_with(node, g0)
+        users[1].replace_input_with(node, g1)
+    graph.lint()
+    return True
+
+
 def nativize(module):
     """Swap the leaf modules of a stage for native ones and plan fusions.
 
-    The stage's own forward() keeps running as written.  A torch.fx trace of it
-    is used only to prove that a fusion / layout choice is safe: a ReLU is folded
-    into the producing conv or linear when it is that node's only consumer, and a
-    4-D result stays in padded NHWC only when every consumer is layout aware.
-    Without a trace every native module emits plain contiguous tensors.
+    The stage's own forward() keeps running as written, with one exception: a container in which a
+    BatchNorm -> add -> ReLU tail (residual block) is found is replaced by a torch.fx GraphModule of its
+    own trace, with that tail fused (parameter and buffer names are unchanged).  Otherwise the torch.fx
+    trace is used only to prove that a fusion / layout choice is safe: a ReLU is folded into the producing
+    conv, linear or batch norm when it is that node's only consumer, and a 4-D result stays in padded NHWC
+    only when every consumer is layout aware.  Without a trace every native module emits plain contiguous
+    tensors.
     """
     single = _swap_leaf(module)
     if single is not module:
         return single
     for n, child in list(module.named_children()):
         new = _swap_leaf(child)
+        if new is child and not isinstance(child, _NATIVE_TYPES) and any(True for _ in child.children()):
+            new = nativize(child)       # a container (residual block, attention block): plan it on its own
         if new is not child:
             setattr(module, n, new)
-        elif not isinstance(child, _NATIVE_TYPES) and any(True for _ in child.children()):
-            nativize(child)             # a container (residual block, attention block): plan it on its own
     try:
         import torch.fx as fx
 
@@ -979,21 +1090,60 @@ def nativize(module):
                     parent, _, attr = user.target.rpartition(".")
                     setattr(mods[parent] if parent else module, attr, FusedAway())
                     mods[user.target] = FusedAway()
-    # 2. keep 4-D results in padded NHWC when every consumer (of every call site) understands it
-    decided = {}
-    for node in graph.nodes:
-        m = target_mod(node)
-        if not isinstance(m, _PADDED_PRODUCERS):
-            continue
+    # 1b. residual tails (BatchNorm -> add -> ReLU) and forks: these rewrite the graph
+    result = module
+    try:
+        rewritten = _fuse_residual_tails(module, graph, mods)
+    except Exception:
+        rewritten = False
+        graph = _Tracer().trace(module)
+    if rewritten:
+        result = fx.GraphModule(module, graph)
+        result.train(module.training)
+        # children in the order of the original module, so that parameters() / state_dict() keep their order
+        kids = result._modules
+        order = [k for k in module._modules if k in kids] + [k for k in kids if k not in module._modules]
+        result._modules = type(kids)((k, kids[k]) for k in order)
+    # 2. keep 4-D results in padded NHWC when every consumer (of every call site) understands it.  A nested
+    # container that was planned before counts as a producer through the module that feeds its output,
+    # and as a consumer when everything that reads its input is layout aware.
+    import operator
+
+    def producer_of(m):
+        if isinstance(m, _PADDED_PRODUCERS):
+            return m
+        return getattr(m, "_pd_out_module", None) if m is not None else None
+
+    def all_users_accept(node):
         frontier, ok = list(node.users), len(node.users) > 0
         while frontier and ok:
             u = frontier.pop()
             um = target_mod(u)
-            if isinstance(um, FusedAway):
+            if isinstance(um, (FusedAway, NativeFork)) or (u.op == "call_function" and u.target is operator.getitem):
                 frontier.extend(u.users)
                 ok = len(u.users) > 0
-            elif not isinstance(um, _PADDED_CONSUMERS):
+            elif not (isinstance(um, _PADDED_CONSUMERS) or getattr(um, "_pd_accepts_padded", False)):
                 ok = False
-        decided[id(m)] = decided.get(id(m), True) and ok
+        return ok
+
+    decided = {}
+    for node in graph.nodes:
+        m = producer_of(target_mod(node))
+        if m is None:
+            continue
+        decided[id(m)] = decided.get(id(m), True) and all_users_accept(node)
         m.out_nchw = not decided[id(m)]
-    return module
+    # what the enclosing container may assume about this one
+    placeholders = [n for n in graph.nodes if n.op == "placeholder"]
+    outputs = [n for n in graph.nodes if n.op == "output"]
+    result._pd_accepts_padded = len(placeholders) == 1 and all_users_accept(placeholders[0])
+    object.__setattr__(result, "_pd_out_module", None)     # plain attribute: not a registered submodule
+    if len(outputs) == 1 and len(outputs[0].args) == 1 and hasattr(outputs[0].args[0], "op"):
+        last = outputs[0].args[0]
+        while isinstance(target_mod(last), FusedAway) and len(last.args) == 1 and len(last.users) == 1:
+            last = last.args[0]
+        m = producer_of(target_mod(last))
+        if m is not None and len(last.users) == 1 and sum(1 for n in graph.nodes if n.op == "call_module"
+                                                          and n.target == last.target) == 1:
+            object.__setattr__(result, "_pd_out_module", m)
+    return result
