@@ -352,7 +352,7 @@ def main():
         import bench_gnmt
         print(json.dumps(bench_gnmt.run(a.steps, a.warmup, not a.no_cpu_baseline)))
         return
-    if a.model == "resnet50":
+    if a.model == "resnet50" and a.gpus == 1 and world == 1:
         import bench_resnet
         print(json.dumps(bench_resnet.run(a.steps, a.warmup, not a.no_cpu_baseline)))
         return
@@ -363,7 +363,7 @@ def main():
         print(json.dumps(out))
         return
     from bench_multi import run_gpu_multi     # pipeline / hybrid partitions over NVLink peer channels
-    out = run_gpu_multi(a.gpus, a.steps, a.warmup)
+    out = run_gpu_multi(a.gpus, a.steps, a.warmup, a.model)
     if out is not None:
         print(json.dumps(out), flush=True)
     import torch.distributed as dist

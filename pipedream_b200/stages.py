@@ -327,17 +327,62 @@ class ResNetStage(nn.Module):
         return out
 
 
-def resnet50(num_stages=1, stage_to_rank_map=None):
-    """ResNet-50 cut at residual-block boundaries into `num_stages` consecutive stages (1, 2, 3, 4, 6, 8, 9, 18)."""
-    units = [("stem",)]
-    cin = 64
+def _resnet50_units():
+    """(kind, args, forward MACs per sample, output shape (C, H)) of the 18 cut units: stem, 16 blocks, head."""
+    units = [("stem", (), 112 * 112 * 64 * 147, (64, 56))]
+    cin, hw = 64, 56
     for width, blocks, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
         for b in range(blocks):
-            units.append(("block", cin, width, stride if b == 0 else 1))
-            cin = 4 * width
-    units.append(("head",))
-    per = (len(units) + num_stages - 1) // num_stages
-    chunks = [units[i:i + per] for i in range(0, len(units), per)]
+            st = stride if b == 0 else 1
+            ho, cout = hw // st, 4 * width
+            macs = hw * hw * cin * width + ho * ho * 9 * width * width + ho * ho * width * cout
+            if st != 1 or cin != cout:
+                macs += ho * ho * cin * cout
+            units.append(("block", (cin, width, st), macs, (cout, ho)))
+            cin, hw = cout, ho
+    units.append(("head", (), 2048 * 1000, (1000, None)))
+    return units
+
+
+def _balanced_cuts(costs, k):
+    """Split `costs` into k contiguous non-empty groups minimising the largest group sum (what the
+    reference's partitioner optimises for a straight pipeline, optimizer_graph_hierarchical.py:20-100);
+    returns the group sizes."""
+    n = len(costs)
+    pre = [0]
+    for c in costs:
+        pre.append(pre[-1] + c)
+    INF = float("inf")
+    best = [[INF] * (n + 1) for _ in range(k + 1)]
+    arg = [[0] * (n + 1) for _ in range(k + 1)]
+    best[0][0] = 0
+    for j in range(1, k + 1):
+        for i in range(j, n + 1):
+            for m in range(j - 1, i):
+                v = max(best[j - 1][m], pre[i] - pre[m])
+                if v < best[j][i]:
+                    best[j][i], arg[j][i] = v, m
+    sizes, i = [], n
+    for j in range(k, 0, -1):
+        m = arg[j][i]
+        sizes.append(i - m)
+        i = m
+    return sizes[::-1]
+
+
+def resnet50(num_stages=1, stage_to_rank_map=None):
+    """ResNet-50 cut at residual-block boundaries into `num_stages` (1..18) consecutive stages of balanced
+    forward FLOPs; one tensor crosses each boundary.  (The reference's generated partitions cut inside
+    blocks, so that the block input travels beside the main path, models/resnet50/gpus=4/__init__.py:13-18;
+    cutting between blocks moves the same bytes once instead.)"""
+    units = _resnet50_units()
+    if not 1 <= num_stages <= len(units):
+        raise ValueError("resnet50: 1..%d stages" % len(units))
+    sizes = _balanced_cuts([u[2] for u in units], num_stages)
+    chunks, i = [], 0
+    for sz in sizes:
+        chunks.append(units[i:i + sz])
+        i += sz
 
     class _Pkg(StagePackage):
         def stages(self_inner):
@@ -350,9 +395,20 @@ def resnet50(num_stages=1, stage_to_rank_map=None):
                     elif u[0] == "head":
                         parts.append(ResNetHead())
                     else:
-                        parts.append(Bottleneck(u[1], u[2], u[3]))
+                        parts.append(Bottleneck(*u[1]))
                 out.append(ResNetStage(parts))
             return out
+
+        def boundary_shapes(self_inner, batch):
+            """{tensor name: shape} of the network input, every stage output and the target."""
+            shapes = {"input0": (batch, 3, 224, 224), "target": (batch,)}
+            for k, ch in enumerate(chunks):
+                c, hw = ch[-1][3]
+                shapes["out%d" % k] = (batch, c) if hw is None else (batch, c, hw, hw)
+            return shapes
+
+        def stage_macs(self_inner):
+            return [sum(u[2] for u in ch) for ch in chunks]
 
     n = len(chunks)
     ranks = stage_to_rank_map or {s: [s] for s in range(n)}

@@ -267,8 +267,10 @@ def test_resnet50_stage_gradients_vs_float64(fp16):
     """Each stage of the 6-stage cut (3 units each: stem / bottleneck blocks / head) on its own, batch 8:
     parameter and input gradients against float64."""
     torch.manual_seed(0)
-    sts = stages.resnet50(6).stages()
-    shapes = [(3, 224), (256, 56), (512, 28), (1024, 14), (1024, 14), (2048, 7)]
+    pkg = stages.resnet50(6)
+    sts = pkg.stages()
+    bs = pkg.boundary_shapes(8)
+    shapes = [(3, 224)] + [(bs["out%d" % k][1], bs["out%d" % k][2]) for k in range(5)]
     g = torch.Generator().manual_seed(11)
     for k, (st, (c, hw)) in enumerate(zip(sts, shapes)):
         x = torch.randn(8, c, hw, hw, generator=g)
@@ -298,3 +300,50 @@ def test_resnet50_gradients_vs_float64():
     checked, total, worst = _compare_gradients(base, x, lambda o: F.cross_entropy(o, y.to(o.device)), False, 0.6,
                                                 norm_tol=2e-2)
     print("\n[fp32] whole network: %d of %d gradients compared; worst cosine gap %s" % (checked, total, worst))
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_resnet50_four_stage_pipeline_matches_oracle(fp16):
+    """ResNet-50 as a 4-stage straight pipeline (1F1B, weight stashing depth 4..1) with every stage in this
+    process, against the CPU oracle of the same pipeline: (minibatch, forward version, backward version)
+    traces bit-exact, first loss at the stated bar, later losses within the noise band measured for this
+    network (see the single-stage test)."""
+    import pipeline_util as pu
+    batch, n = 8, 6
+    pkg = stages.resnet50(4)
+    conf = dict(pkg.conf, stage_to_depth_map=None)
+    torch.manual_seed(0)
+    omodel = pkg.model(torch.nn.CrossEntropyLoss())
+    pipe_o = oracle.PipelineOracle(omodel, conf["module_to_stage_map"], conf["stage_to_rank_map"], None, "SGD",
+                                   dict(lr=0.01, momentum=0.9, weight_decay=1e-4))
+    pipe_o.run({0: stages.SyntheticImages(batch, n)}, n)
+    ref_losses = pipe_o.ranks[3]["losses"]
+    shapes = ({k: tuple(v) for k, v in pkg.boundary_shapes(batch).items()},
+              {k: (torch.int64 if k in ("input0", "target") else torch.float32) for k in pkg.boundary_shapes(batch)})
+    pu.schedule.reset_local()
+    torch.manual_seed(0)
+    workers = [pu.make_worker(pkg, conf, rank, batch, fp16, pu.communication.LOCAL, shapes=shapes, lr=0.01,
+                              weight_decay=1e-4, seed=0) for rank in range(4)]
+    pipe = pu.schedule.LocalPipeline(workers)
+    workers[0][0].set_loader(stages.SyntheticImages(batch, n))
+    for r, _ in workers[1:]:
+        r.set_loader(None)
+    losses = []
+    pipe.run([n] * 4, on_loss=lambda k, i, rr: losses.append(float(rr.loss)))
+    print("\n[%s] 4-stage resnet50 losses %s vs oracle %s" % ("bf16" if fp16 else "fp32", [round(v, 4) for v in losses],
+                                                               [round(v, 4) for v in ref_losses]))
+    for k, (r, opt) in enumerate(workers):
+        assert opt.num_versions == 4 - k
+        got, b = [], 0
+        for kind, v in opt.trace:          # the optimizer records (event, version); F entries are not its business
+            if kind == "load_old":
+                got.append(("B", b, v if opt.num_versions > 1 else b))   # one version: B runs on the latest, v_b
+            elif kind == "step":
+                got.append(("S", b, v))
+                b += 1
+        want = [tuple(t) for t in pipe_o.ranks[k]["trace"] if t[0] != "F"]
+        assert got == want, (k, got[:6], want[:6])
+    bar = 2e-2 if fp16 else 1e-3
+    assert len(losses) == n and abs(losses[0] - ref_losses[0]) <= bar * abs(ref_losses[0])
+    assert max(abs(a - b) / abs(b) for a, b in zip(losses, ref_losses)) <= (4e-2 if fp16 else 2e-2)
+    assert pf.gemm_poll_error() == 0
