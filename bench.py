@@ -299,22 +299,40 @@ def run_reference(steps, warmup, n_gpus):
 
 
 def run_profile_case(name):
-    """A few launches of one convolution pass at one layer shape, for `ncu` captures of the
-    tensor-core kernel on a case that is larger than L2 but only a few hundred MB:
-    name = fwd|dgrad|wgrad : batch 64, 56x56, 256 -> 256 channels, bf16."""
+    """A few launches of one contraction at one layer shape, for `ncu` captures of the tensor-core kernel on
+    a case that is larger than L2 but well under 1 GB:
+    fwd|dgrad|wgrad : batch 64, 56x56, 256 -> 256 channels, bf16 (a tensor-bound layer);
+    narrow_fwd|narrow_dgrad : batch 16, 224x224, 64 -> 64 channels (a layer bound by shared-memory fill);
+    patch_fwd : the first layer's patch-matrix contraction, [16*226*226, 32] x [64, 32]^T with bias + ReLU."""
     from pipedream_b200 import functional as pf
     torch.cuda.set_device(0)
     g = torch.Generator().manual_seed(0)
-    N, H, W, Cin, Cout = 64, 56, 56, 256, 256
+    if name.startswith("narrow"):
+        N, H, W, Cin, Cout = 16, 224, 224, 64, 64
+    elif name == "patch_fwd":
+        N, H, W, Cin, Cout = 16, 224, 224, 3, 64
+    else:
+        N, H, W, Cin, Cout = 64, 56, 56, 256, 256
+    bias = torch.zeros(Cout, device="cuda", dtype=torch.bfloat16)
+    if name == "patch_fwd":
+        col = torch.randn(N * (H + 2) * (W + 2), 32, generator=g).cuda().to(torch.bfloat16)
+        w = (torch.randn(Cout, 32, generator=g) * 0.1).cuda().to(torch.bfloat16)
+        for _ in range(4):
+            pf.gemm_nt(col, w, bias=bias, relu=True, pad_hw=(H + 2, W + 2))
+        torch.cuda.synchronize()
+        assert pf.gemm_poll_error() == 0
+        print(json.dumps({"case": name, "shape": [col.shape[0], Cout, 32],
+                          "algorithmic_flop_per_launch": 2.0 * N * H * W * 27 * Cout,
+                          "algorithmic_bytes_per_launch": int(col.numel() * 2 + col.shape[0] * Cout * 2)}))
+        return
     x = pf.pack_pnhwc(torch.randn(N, Cin, H, W, generator=g).cuda().to(torch.bfloat16))
     dy = pf.pack_pnhwc(torch.randn(N, Cout, H, W, generator=g).cuda().to(torch.bfloat16))
     w = (torch.randn(Cout, 9 * Cin, generator=g) * 0.02).cuda().to(torch.bfloat16)
-    bias = torch.zeros(Cout, device="cuda", dtype=torch.bfloat16)
     dw = torch.zeros(Cout, 9 * Cin, device="cuda")
     for _ in range(4):
-        if name == "fwd":
+        if name.endswith("fwd"):
             pf.conv2d_fwd(x, w, 9 * Cin, Cout, bias, True)
-        elif name == "dgrad":
+        elif name.endswith("dgrad"):
             pf.conv2d_dgrad(dy, w, 9 * Cin, Cin, relu_aux=x)
         else:
             pf.conv2d_wgrad(x, dy, dw, 9 * Cin, accumulate=False)
@@ -334,7 +352,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50"],
                     help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT) or resnet50, each on 1 GPU")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd"],
                     help="run a few launches of one convolution pass (for ncu) and exit")
     a = ap.parse_args()
     if a.profile_case:

@@ -30,6 +30,7 @@ struct PdGemm {
   int num_z; int z_b_row[PD_MAX_TAPS]; int64_t z_out_col;
   int z_group;                // tcgen05: up to this many z outputs share one CTA (and its A tiles)
   int split_k;
+  int share_tap_rows;         // tcgen05: taps 3r..3r+2 read rows that differ by 0/1/2 - let them share one A box
   // epilogue
   void* out; int out_dtype; int64_t ldo;
   int atomic;                 // fp32 atomicAdd into out (out_dtype must be PD_F32)

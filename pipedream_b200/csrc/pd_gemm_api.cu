@@ -127,6 +127,7 @@ PD_EXPORT int pd_conv2d_fwd(int dtype, const void* x_pad, int N, int H, int W, i
   g.num_taps = 9;
   int shift[9]; conv_taps(Wp, shift);
   for (int t = 0; t < 9; ++t) { g.a_tap_row[t] = shift[t]; g.b_tap_col[t] = t * Cin; }
+  g.share_tap_rows = 1;
   g.out = y_pad; g.out_dtype = dtype; g.ldo = Cout;
   g.bias = bias; g.bias_dtype = bias_dtype; g.relu = relu;
   g.pad_hp = Hp; g.pad_wp = Wp;
@@ -148,6 +149,7 @@ PD_EXPORT int pd_conv2d_dgrad(int dtype, const void* dy_pad, int N, int H, int W
   g.num_taps = 9;
   int shift[9]; conv_taps(Wp, shift);
   for (int t = 0; t < 9; ++t) { g.a_tap_row[t] = -shift[t]; g.b_tap_col[t] = t * Cin; }
+  g.share_tap_rows = 1;
   g.out = dx_pad; g.out_dtype = dtype; g.ldo = Cin;
   g.pad_hp = Hp; g.pad_wp = Wp;
   g.relu_aux = relu_aux; g.ld_aux = Cin;

@@ -12,7 +12,9 @@
 // MN-major (output index contiguous); the latter is what lets the data- and
 // weight-gradient passes read activations and weights in place, without
 // transposed copies.  Convolution taps are extra row offsets of the same 2-D
-// tensor maps, so a 3x3 convolution is nine shifted box loads per K-block.
+// tensor maps, so a 3x3 convolution is nine shifted box loads per K-block - or, for narrow layers that are
+// bound by shared-memory fill bandwidth rather than by the tensor pipe, three boxes of 136 rows, each read by
+// the three taps of one filter row through descriptors that start 0, 1 or 2 rows into the box.
 //
 // Every mbarrier wait is bounded: when the bound is hit the role records a code
 // in an error word, stops, and the CTA still frees its tensor memory.
@@ -29,6 +31,8 @@ constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;   // 16 KiB
 constexpr uint32_t kAtomBytes = 64 * kBlockK * 2;     // one 64-wide MN-major atom: 8 KiB
+constexpr int kBox3Rows = kBlockM + 8;                 // A box shared by the three taps of one filter row
+constexpr uint32_t kA3Bytes = kBox3Rows * kBlockK * 2; // 17 KiB (a multiple of 1024)
 constexpr long long kWaitCycles = 400000000ll;        // ~0.2 s at 2 GHz
 
 struct KParams {
@@ -48,6 +52,10 @@ struct KParams {
   const void* relu_aux; long long ld_aux;
   uint32_t idesc;
   int num_stages;
+  // tap3: the taps come in triples whose A rows differ by 0/1/2 (the three taps of one filter row of a 3x3
+  // convolution): one A box of kBox3Rows rows serves all three, num_taps counts triples
+  int tap3;
+  int t3_base[3], t3_off[PD_MAX_TAPS];
   int* err;
 };
 
@@ -263,7 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t b_bytes = (uint32_t)p.block_n * kBlockK * 2;
-  const uint32_t stage_bytes = kABytes + (uint32_t)p.acc_count * b_bytes;
+  const uint32_t stage_bytes = p.tap3 ? kA3Bytes + 3u * b_bytes : kABytes + (uint32_t)p.acc_count * b_bytes;
   const int S = p.num_stages;
   const uint32_t acc_cols = (uint32_t)(p.acc_count * p.block_n);   // TMEM columns of one buffer
   const int tiles_mn = p.m_tiles * p.n_tiles;
@@ -314,7 +322,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // The whole warp walks the loop; lane 0 arms the barrier, lanes 0..boxes-1 each issue one box,
     // so the (up to six) box loads of a stage go out in one instruction slot.
     // Two boxes per stage (both operands K-major): one lane issues both, nothing to coordinate.
-    if (!p.a_major && !p.b_major && p.acc_count == 1) {
+    if (p.tap3) {
+      // lane 0: the shared A box; lanes 1..: the B boxes of the triple's three taps
+      const int b_boxes = p.b_major ? p.block_n / 64 : 1;
+      const bool is_a = lane == 0;
+      const int bl = lane - 1;
+      const int s3 = is_a ? 0 : min(bl / b_boxes, 2);
+      const int j = is_a ? 0 : bl % b_boxes;
+      const bool has_box = is_a || bl < 3 * b_boxes;
+      uint32_t g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        PD_DECODE_TILE(tile)
+        (void)iters; (void)accn; (void)acc0; (void)z;
+        for (int r = 0; r < 3 && ok; ++r) {
+          int x0, y0, xk, yk;
+          uint32_t dst_off, bytes;
+          bool issue = has_box;
+          if (is_a) {
+            x0 = p.a_col0; y0 = p.a_row0 + m0 + p.t3_base[r]; xk = kBlockK; yk = 0;
+            dst_off = 0; bytes = kA3Bytes;
+          } else {
+            const int t = 3 * r + s3;
+            if (p.b_major) {
+              x0 = p.b_col0 + p.b_tap_col[t] + n0 + j * 64; y0 = p.b_row0 + p.b_tap_row[t]; xk = 0; yk = kBlockK;
+              dst_off = kA3Bytes + (uint32_t)s3 * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              issue = issue && x0 < p.b_cols;
+            } else {
+              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0 + p.b_tap_row[t]; xk = kBlockK; yk = 0;
+              dst_off = kA3Bytes + (uint32_t)s3 * b_bytes; bytes = b_bytes;
+            }
+          }
+          uint32_t tx = issue ? bytes : 0u;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+          const CUtensorMap* map = is_a ? &tma_a : &tma_b;
+          for (int kb = kb_begin; kb < kb_begin + kbn; ++kb, ++g) {
+            const int s = (int)(g % (uint32_t)S);
+            const uint32_t ph = (g / (uint32_t)S) & 1u;
+            if (lane == 0) ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) break;
+            const uint32_t fb = smem_u32(&full_bar[s]);
+            if (lane == 0) mbar_expect_tx(fb, tx);
+            __syncwarp();
+            if (issue)
+              tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+          }
+        }
+      }
+    } else if (!p.a_major && !p.b_major && p.acc_count == 1) {
       if (lane == 0) {
         uint32_t g = 0;
         bool ok = true;
@@ -421,6 +478,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, p.err, 2)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
+          if (p.tap3) {
+            const int r = it / kbn;
+#pragma unroll
+            for (int s3 = 0; s3 < 3; ++s3) {
+              // the tap's rows start t3_off (0..2) rows into the shared box; the swizzle is a function of
+              // the shared-memory address, so a descriptor may start on any 128-byte row of the box
+              const uint64_t da3 = make_desc(sa + (uint32_t)p.t3_off[3 * r + s3] * 128u, 0);
+              const uint64_t db3 = make_desc(sa + kA3Bytes + (uint32_t)s3 * b_bytes, p.b_major);
+#pragma unroll
+              for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
+                umma_bf16(tmem_d, da3 + (uint64_t)(kk * adv_a), db3 + (uint64_t)(kk * adv_b), p.idesc,
+                          (uint32_t)((it | s3 | kk) != 0));
+            }
+            umma_commit(smem_u32(&empty_bar[s]));
+            continue;
+          }
           const uint64_t da = make_desc(sa, p.a_major);
           for (int a = 0; a < accn; ++a) {
             const uint64_t db = make_desc(sa + kABytes + (uint32_t)a * b_bytes, p.b_major);
@@ -625,7 +698,26 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.a_major ? 1 : 0) << 15) |
             ((uint32_t)(g.b_major ? 1 : 0) << 16) | ((uint32_t)(block_n >> 3) << 17) |
             ((uint32_t)(kBlockM >> 4) << 24);
-  const uint32_t stage_bytes = kABytes + (uint32_t)p.acc_count * (uint32_t)block_n * kBlockK * 2;
+  // shared A boxes for the three taps of a filter row: narrow output tiles only (wide ones are bound by the
+  // tensor pipe and want more, smaller stages)
+  bool tap3 = g.share_tap_rows && g.num_taps == 9 && !g.a_major && block_n <= 128 && g.num_z == 1 && p.split_k == 1 &&
+              p.acc_count == 1;
+  for (int r = 0; r < 3 && tap3; ++r) {
+    int base = g.a_tap_row[3 * r];
+    for (int s3 = 1; s3 < 3; ++s3) base = g.a_tap_row[3 * r + s3] < base ? g.a_tap_row[3 * r + s3] : base;
+    p.t3_base[r] = base;
+    bool seen[3] = {false, false, false};
+    for (int s3 = 0; s3 < 3; ++s3) {
+      const int off = g.a_tap_row[3 * r + s3] - base;
+      if (off < 0 || off > 2 || seen[off] || g.a_tap_col[3 * r + s3] != 0) { tap3 = false; break; }
+      seen[off] = true;
+      p.t3_off[3 * r + s3] = off;
+    }
+  }
+  p.tap3 = tap3 ? 1 : 0;
+  if (tap3) p.num_taps = 3;
+  const uint32_t stage_bytes = tap3 ? kA3Bytes + 3u * (uint32_t)block_n * kBlockK * 2
+                                    : kABytes + (uint32_t)p.acc_count * (uint32_t)block_n * kBlockK * 2;
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
@@ -642,7 +734,7 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   p.err = err_addr[dev_now];
 
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, g.a, g.a_rows, g.a_cols, g.lda, 64, g.a_major ? kBlockK : kBlockM);
+  int rc = make_map(&ma, g.a, g.a_rows, g.a_cols, g.lda, 64, g.a_major ? kBlockK : (tap3 ? kBox3Rows : kBlockM));
   if (rc != PD_OK) return rc;
   rc = make_map(&mb, g.b, g.b_rows, g.b_cols, g.ldb, 64, g.b_major ? kBlockK : block_n);
   if (rc != PD_OK) return rc;
