@@ -5,8 +5,9 @@
 //              stages with 128B-swizzled operand boxes
 //   warp 1   : allocates tensor memory, issues tcgen05.mma (one elected lane),
 //              releases stages through tcgen05.commit
-//   warps 2-5: epilogue - tcgen05.ld the accumulator, apply bias / ReLU / border
-//              mask, store (or fp32 atomic-add for split-K weight gradients)
+//   warps 2-9: epilogue, two sets of four warps that take alternate tiles - tcgen05.ld the
+//              accumulator, apply bias / ReLU / border mask, store (or fp32 atomic-add for
+//              split-K weight gradients)
 //
 // Both operands may be K-major (contraction index contiguous in memory) or
 // MN-major (output index contiguous); the latter is what lets the data- and
@@ -27,7 +28,8 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;                       // bf16 elements = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;                     // producer, MMA issuer, 2 x 4 epilogue warps
+constexpr int kMaxAccBufs = 4;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;   // 16 KiB
 constexpr uint32_t kAtomBytes = 64 * kBlockK * 2;     // one 64-wide MN-major atom: 8 KiB
@@ -52,6 +54,7 @@ struct KParams {
   const void* relu_aux; long long ld_aux;
   uint32_t idesc;
   int num_stages;
+  int acc_bufs;               // accumulator buffers in tensor memory (2..4): tiles in flight between MMA and epilogue
   // tap3: the taps come in triples whose A rows differ by 0/1/2 (the three taps of one filter row of a 3x3
   // convolution): one A box of kBox3Rows rows serves all three, num_taps counts triples
   int tap3;
@@ -217,7 +220,21 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t*
     }
   } else if (p.out_dtype == PD_BF16) {
     __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)m * p.ldo + out_col0 + nb;
-    if (full && (((uintptr_t)o) & 15) == 0) {
+    if (full && (((uintptr_t)o) & 31) == 0) {
+      // 32-byte stores: a lane writes whole sectors, so the two halves of a sector do not travel separately
+      uint32_t w[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+        w[q] = *reinterpret_cast<uint32_t*>(&h);
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"l"(o + q * 16), "r"(w[q * 8]), "r"(w[q * 8 + 1]), "r"(w[q * 8 + 2]), "r"(w[q * 8 + 3]),
+                       "r"(w[q * 8 + 4]), "r"(w[q * 8 + 5]), "r"(w[q * 8 + 6]), "r"(w[q * 8 + 7])
+                     : "memory");
+    } else if (full && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint4 pk;
@@ -254,17 +271,18 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Persistent: each CTA walks the tile list with stride gridDim.x.  The accumulator is double
-// buffered in tensor memory (2 x block_n columns), so the epilogue of one tile runs under the
-// MMAs of the next one; the shared-memory stage ring runs on across tile boundaries.
+// Persistent: each CTA walks the tile list with stride gridDim.x.  Tensor memory holds 2..4 accumulator
+// buffers, so the epilogues of earlier tiles (two warp sets, alternate tiles) run under the MMAs of the
+// next ones - short-K tiles are bound by the epilogue's latency chain otherwise; the shared-memory stage
+// ring runs on across tile boundaries.
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-  __shared__ __align__(8) uint64_t tmem_full_bar[2];
-  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ __align__(8) uint64_t tmem_full_bar[kMaxAccBufs];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[kMaxAccBufs];
   __shared__ uint32_t tmem_base_holder;
 
   const int warp = threadIdx.x >> 5;
@@ -277,16 +295,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int tiles_mn = p.m_tiles * p.n_tiles;
   const int total_tiles = tiles_mn * p.num_z * p.split_k;
 
-  // TMEM columns: power of two >= 32 covering two accumulators
+  // TMEM columns: power of two >= 32 covering all accumulator buffers
+  const uint32_t nbuf = (uint32_t)p.acc_bufs;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 2u * acc_cols) tmem_cols <<= 1;
+  while (tmem_cols < nbuf * acc_cols) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kMaxAccBufs; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[b]), 4);     // one arrival per epilogue warp
     }
@@ -466,8 +485,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         PD_DECODE_TILE(tile)
         (void)m0; (void)n0; (void)kb_begin; (void)acc0;
         if (iters == 0) continue;             // (cannot happen: the host never creates empty splits)
-        const uint32_t buf = local & 1u;
-        const uint32_t use = local >> 1;
+        const uint32_t buf = local % nbuf;
+        const uint32_t use = local / nbuf;
         // the epilogue must have drained this accumulator (passes at once on its first use)
         if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), (use & 1u) ^ 1u, p.err, 4)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -495,6 +514,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             continue;
           }
           const uint64_t da = make_desc(sa, p.a_major);
+          if (p.b_major && accn > 1 && accn * p.block_n <= 256) {
+            // MN-major B tiles of the accumulators of a z group lie back to back, 64-column atom after atom,
+            // and so do their accumulators in tensor memory: one MMA of N = accn * block_n does the work of
+            // accn narrow ones (an MMA costs about the same up to N = 128, so narrow ones waste the pipe)
+            const uint64_t db = make_desc(sa + kABytes, 1);
+            const uint32_t idesc_n = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((accn * p.block_n) >> 3) << 17);
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
+              umma_bf16(tmem_d, da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b), idesc_n,
+                        (uint32_t)((it | kk) != 0));
+            umma_commit(smem_u32(&empty_bar[s]));
+            continue;
+          }
           for (int a = 0; a < accn; ++a) {
             const uint64_t db = make_desc(sa + kABytes + (uint32_t)a * b_bytes, p.b_major);
 #pragma unroll
@@ -511,14 +543,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   } else {
     // -------------------------------- epilogue --------------------------------
     const int lg = warp & 3;                 // TMEM lane group this warp may read
+    const uint32_t set = (uint32_t)(warp - 2) >> 2;   // which of the two epilogue sets
     uint32_t local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       PD_DECODE_TILE(tile)
       (void)kb_begin;
       if (iters == 0) continue;
-      const uint32_t buf = local & 1u;
-      const uint32_t use = local >> 1;
+      if ((local & 1u) != set) { ++local; continue; }
+      const uint32_t buf = local % nbuf;
+      const uint32_t use = local / nbuf;
       ok = mbar_wait(smem_u32(&tmem_full_bar[buf]), use & 1u, p.err, 3);
       // the wait result can differ between lanes only when the bound ran out; make it uniform
       ok = __all_sync(0xffffffffu, ok);
@@ -721,6 +755,11 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
+  {
+    const int acc_cols = p.acc_count * block_n;
+    int bufs = 512 / acc_cols;
+    p.acc_bufs = bufs > kMaxAccBufs ? kMaxAccBufs : (bufs < 2 ? 2 : bufs);
+  }
   // device address of the error word, looked up once per device
   static int* err_addr[64] = {};
   int dev_now = 0;
