@@ -366,9 +366,18 @@ def main():
     if a.warmup < 3:
         a.warmup = 3
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if a.model == "gnmt":
+    if a.model == "gnmt" and a.gpus == 1 and world == 1:
         import bench_gnmt
         print(json.dumps(bench_gnmt.run(a.steps, a.warmup, not a.no_cpu_baseline)))
+        return
+    if a.model == "gnmt":
+        import bench_gnmt
+        import torch.distributed as dist
+        out = bench_gnmt.run_multi(a.gpus, a.steps, a.warmup)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        if dist.is_initialized():
+            dist.destroy_process_group()
         return
     if a.model == "resnet50" and a.gpus == 1 and world == 1:
         import bench_resnet

@@ -178,3 +178,87 @@ def run(steps, warmup, with_cpu):
     if with_cpu:
         out["cpu_baseline"] = cpu_baseline()
     return out
+
+
+def partition_for(n):
+    """(module_to_stage_map, stage_to_rank_map, label) of the multi-GPU GNMT runs: N=2 two stages (encoder half /
+    decoder half), N=4 the reference's four-stage split, N=8 the same four stages with two replicas each."""
+    if n == 2:
+        return [0, 0, 1, 1, 1], {0: [0], 1: [1]}, "2-stage pipeline"
+    if n == 4:
+        return [0, 1, 2, 3, 3], {s: [s] for s in range(4)}, "4-stage pipeline"
+    if n == 8:
+        return [0, 1, 2, 3, 3], {s: [2 * s, 2 * s + 1] for s in range(4)}, "4-stage pipeline x 2 replicas"
+    raise ValueError("GNMT multi-GPU partitions exist for 2, 4 and 8 GPUs")
+
+
+def run_multi(gpus, steps, warmup):
+    """One process per GPU (torch.distributed.run): stages over NVLink peer channels, replicas over NCCL."""
+    import torch.distributed as dist
+    from bench_multi import run_phase
+    from pipedream_b200 import _lib, adam, gnmt_blocks, runtime, stages
+    from pipedream_b200 import functional as pf
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    world = int(os.environ["WORLD_SIZE"])
+    assert world == gpus, "launch with torch.distributed.run --nproc-per-node %d" % gpus
+    torch.cuda.set_device(local_rank)
+    m2s, s2r, label = partition_for(world)
+    torch.manual_seed(0)
+    model = stages.gnmt_large(dropout=0.2).model(gnmt_blocks.LabelSmoothing(0, 0.1))
+    B, Tm, H, V = BATCH, 50, 1024, 32320
+    shapes = {"input0": (Tm, B), "input1": (B,), "input2": (Tm, B), "target": (Tm * B,), "target_length": (B,),
+              "out0": (Tm, B, H), "out1": (Tm, B, H), "out12": (Tm, B, H), "out13": (Tm, B, H), "out14": (Tm, B, H),
+              "out15": (Tm, B, 2 * H), "out12again": (Tm, B, H), "out18": (Tm, B, V)}
+    dtypes = {k: torch.bfloat16 for k in shapes}
+    dtypes.update({k: torch.int64 for k in ("input0", "input1", "input2", "target", "target_length")})
+    conf = {"module_to_stage_map": m2s, "stage_to_rank_map": s2r, "stage_to_depth_map": None}
+    r = runtime.StageRuntime(
+        model=model, distributed_backend="p2p", fp16=True, loss_scale=1, training_tensor_shapes=shapes,
+        eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dtypes,
+        inputs_module_destinations={"input0": 0, "input1": 1, "input2": 1},
+        target_tensor_names={"target", "target_length"}, configuration_maps=conf,
+        master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"), rank=rank, local_rank=local_rank,
+        num_ranks_in_server=1, verbose_freq=0, model_type=runtime.TRANSLATION)
+    opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
+                                      num_versions=r.num_warmup_minibatches + 1, lr=2e-3, weight_decay=1e-4)
+    first = r.stage == 0
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    # the untimed head of the phase (>= 6 minibatches) covers every batch shape of the pool (allocator growth)
+    dev = CyclingPairs(BATCH, "cuda", seed=4321 + 1000 * rank) if first else None
+    _lib.count_calls(True)
+    ms = run_phase(r, opt, dev, steps, max(warmup, 6), False)
+    launches = _lib.launches_counted()
+    _lib.count_calls(False)
+    clocks = sampler.stop() if sampler else None
+    host = CyclingPairs(BATCH, "pinned", seed=4321 + 1000 * rank) if first else None
+    ms_e2e = run_phase(r, opt, host, steps, 3, True)
+    if pf.gemm_poll_error() != 0:
+        raise RuntimeError("a tcgen05 kernel reported a bounded wait that ran out")
+    t = torch.tensor([ms, ms_e2e, float(launches)], dtype=torch.float64, device="cuda")
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    r0 = len(s2r[0])
+    if rank != 0:
+        return None
+    samples = BATCH * r0 * steps
+    return {
+        "metric": METRIC, "value": round(samples / (tmax[0].item() * 1e-3), 2), "unit": "samples/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(tmax[0].item() / steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "GNMT 8+8 layers (hidden 1024, vocab 32320), bf16, batch 128 sentence pairs per stage-0 "
+                               "replica, lengths uniform in [20,50], Zipf(1.1) ids, label smoothing 0.1, Adam lr 2e-3, "
+                               "1F1B with weight stashing", "global_batch": BATCH * r0, "parallelism": label,
+                   "l2": "no flush: weights + activations of a step exceed L2"},
+        "clocks": clocks,
+        "e2e": {"value": round(samples / (tmax[1].item() * 1e-3), 2), "unit": "samples/s",
+                "h2d_bytes_per_step": (dev.bytes_per_step if dev else 0) * r0, "d2h_bytes_per_step": 8 * len(s2r[max(s2r)]),
+                "ms_per_step": round(tmax[1].item() / steps, 3)},
+        "gpu_launches": int(t[2].item()),
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": None, "peak": peaks()["bf16_tflops_sustained"],
+                     "unit": "TFLOP/s", "frac": None, "traffic": None,
+                     "note": "per-kernel figures are reported by the 1-GPU run (python bench.py --model gnmt)"},
+    }
