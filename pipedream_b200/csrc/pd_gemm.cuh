@@ -41,4 +41,15 @@ struct PdGemm {
 };
 
 int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream);
+// 128-byte-swizzle bf16 tensor map of a row-major [rows, cols] matrix (leading dim ld elements), cached per host
+// thread; box = box_cols x box_rows elements (box_cols * 2 bytes <= 128).
+int pd_gemm_error_word(int** out);
+// Whole-sequence LSTM forward as one cooperative kernel; returns 1 when it does not apply (pd_lstm_persist.cu).
+int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, int T, int B, int H, void* y, void* act,
+                           float* c_all, unsigned int* counter, cudaStream_t s);
+int pd_lstm_bwd_persistent(const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int B, int H,
+                           void* dgates, float* dh_ws, float* dc_ws, cudaStream_t s);
+struct CUtensorMap_st;
+int pd_make_map_2d(CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols,
+                   int box_rows);
 int pd_gemm_launch_simt(const PdGemm& g, cudaStream_t stream);

@@ -4,9 +4,11 @@
 // The input projection x_t . W_ih^T (+ b_ih) for all time steps is one large contraction done by the
 // caller (pd_gemm_nt).  These entry points run the recurrence: per step one contraction with W_hh on
 // the tensor cores (bf16; CUDA cores for fp32) and one fused cell kernel (gate activations, cell and
-// hidden update, all statistics in fp32).  The whole loop is enqueued from C++ so that a layer costs
+// hidden update, all statistics in fp32).  For bf16 with B <= 128 and H <= 1184 the forward recurrence runs
+// instead as one cooperative kernel for the whole sequence (pd_lstm_persist.cu).  The whole loop is enqueued from C++ so that a layer costs
 // one call from the host language, not two per time step.  Gate order is torch's: i, f, g, o.
 #include "pd_gemm.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -101,6 +103,14 @@ PD_EXPORT int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const voi
   PD_REQUIRE(dtype == PD_F32 || dtype == PD_BF16, "pd_lstm_fwd: bad dtype");
   PD_REQUIRE(dtype == PD_F32 || (H % 8) == 0, "pd_lstm_fwd: H must be a multiple of 8 for bf16");
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_BF16) {
+    // the whole sequence as one cooperative kernel where it applies (PD_LSTM_PERSISTENT=0 switches it off)
+    static const bool enabled = [] { const char* e = getenv("PD_LSTM_PERSISTENT"); return !(e && e[0] == '0'); }();
+    if (enabled) {
+      const int prc = pd_lstm_fwd_persistent(gx, w_hh, b_hh, T, B, H, y, act, c_all, (unsigned int*)gh_ws, s);
+      if (prc != 1) return prc;
+    }
+  }
   const int es = pd_elem_size(dtype);
   const int64_t BH = (int64_t)B * H;
   const int grid = cell_grid(B, H);
@@ -145,6 +155,13 @@ PD_EXPORT int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const voi
   PD_REQUIRE(dy && w_hh && act && c_all && dgates && dh_ws && dc_ws && T > 0 && B > 0 && H > 0, "pd_lstm_bwd: bad arguments");
   PD_REQUIRE(dtype == PD_F32 || dtype == PD_BF16, "pd_lstm_bwd: bad dtype");
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PD_BF16) {
+    static const bool enabled = [] { const char* e = getenv("PD_LSTM_PERSISTENT"); return !(e && e[0] == '0'); }();
+    if (enabled) {
+      const int prc = pd_lstm_bwd_persistent(dy, w_hh, act, c_all, T, B, H, dgates, dh_ws, dc_ws, s);
+      if (prc != 1) return prc;
+    }
+  }
   const int es = pd_elem_size(dtype);
   const int64_t BH = (int64_t)B * H;
   const int grid = cell_grid(B, H);

@@ -359,9 +359,12 @@ def test_adam_ring():
 
 # ------------------------------------------------------------------ LSTM
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("T,B,I,H", [(5, 8, 64, 64), (12, 16, 128, 64), (1, 4, 64, 128)])
+@pytest.mark.parametrize("T,B,I,H", [(5, 8, 64, 64), (12, 16, 128, 64), (1, 4, 64, 128), (7, 128, 256, 1024),
+                                     (4, 100, 64, 320), (6, 32, 64, 256)])
 def test_lstm_layer(dtype, T, B, I, H):
-    """NativeLSTM forward and every gradient against torch.nn.LSTM (fp32 autograd on the same weights)."""
+    """NativeLSTM forward and every gradient against torch.nn.LSTM (fp32 autograd on the same weights).  In bf16
+    the forward recurrence of all but the T = 1 case runs as the whole-sequence cooperative kernel (8, 128 and 40
+    CTAs; the (7, 128, 256, 1024) case is the translation model's layer shape and wraps the stage ring)."""
     from pipedream_b200 import layers
     torch.manual_seed(3)
     ref = torch.nn.LSTM(I, H).cuda()
