@@ -208,7 +208,12 @@ int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int
  * [T,B,4H] and cell states `c_all` [T,B,H] (fp32).  pd_lstm_bwd walks back through time and
  * produces the gate pre-activation gradients `dgates` [T,B,4H]; dx, dW_ih, dW_hh and the bias
  * gradients are then pd_gemm_nn / pd_gemm_tn / pd_relu_bwd_colsum calls over dgates.
- * gh_ws [B,4H], dh_ws and dc_ws [B,H]: fp32 scratch provided by the caller.                      */
+ * gh_ws [B,4H], dh_ws and dc_ws [B,H]: fp32 scratch provided by the caller.
+ * In bf16 with B <= 128 the recurrences run as ONE cooperative kernel per call where the sizes allow
+ * (forward: H a multiple of 64, H/8 <= number of SMs; backward: H a power of two in 128..1024): weights
+ * stay in shared memory for the whole sequence, the cell update is fused in, steps are separated by a
+ * grid-wide counter; results and saved tensors are the same.  PD_LSTM_PERSISTENT=0 in the environment
+ * selects the per-step launches everywhere.                                                            */
 int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const void* b_hh, int T, int B, int H,
                 void* y, void* act, float* c_all, float* gh_ws, void* stream);
 int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all,
