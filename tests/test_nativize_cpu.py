@@ -36,3 +36,38 @@ def test_stage_boundary_emits_plain_tensors():
 def test_vgg_and_gnmt_stages_keep_their_own_forward():
     v = stages.vgg16("gpus=1").stages()[0]
     assert layers.nativize(v) is v
+
+
+def test_balanced_cuts_are_optimal():
+    import itertools
+    import random
+    rnd = random.Random(7)
+    for _ in range(30):
+        n = rnd.randint(3, 9)
+        k = rnd.randint(1, n)
+        costs = [rnd.randint(1, 50) for _ in range(n)]
+        sizes = stages._balanced_cuts(costs, k)
+        assert len(sizes) == k and sum(sizes) == n and min(sizes) >= 1
+        got, i = 0, 0
+        for sz in sizes:
+            got = max(got, sum(costs[i:i + sz]))
+            i += sz
+        best = min(max(sum(costs[a:b]) for a, b in zip((0,) + cut, cut + (n,)))
+                   for cut in itertools.combinations(range(1, n), k - 1))
+        assert got == best
+
+
+def test_resnet_partitions_cover_the_network_and_report_their_boundaries():
+    for k in (1, 3, 8):
+        pkg = stages.resnet50(k)
+        sts = pkg.stages()
+        assert len(sts) == k and sum(len(s.parts) for s in sts) == 18
+        assert sum(p.numel() for s in sts for p in s.parameters()) == 25557032
+        shapes = pkg.boundary_shapes(2)
+        x = torch.randn(*shapes["input0"])
+        with torch.no_grad():
+            for i, s in enumerate(sts):
+                s.eval()
+                x = s(x)
+                assert tuple(x.shape) == tuple(shapes["out%d" % i])
+        assert abs(2 * sum(pkg.stage_macs()) / 1e9 - 8.18) < 0.01       # forward GFLOP per sample
