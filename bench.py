@@ -350,8 +350,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50"],
-                    help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT) or resnet50, each on 1 GPU")
+    ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50", "gpt"],
+                    help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT), resnet50 or gpt (24-layer 2BW decoder)")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd"],
                     help="run a few launches of one convolution pass (for ncu) and exit")
     a = ap.parse_args()
@@ -374,6 +374,18 @@ def main():
         import bench_gnmt
         import torch.distributed as dist
         out = bench_gnmt.run_multi(a.gpus, a.steps, a.warmup)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        return
+    if a.model == "gpt":
+        import bench_gpt
+        if a.gpus == 1 and world == 1:
+            print(json.dumps(bench_gpt.run(a.steps, a.warmup)))
+            return
+        import torch.distributed as dist
+        out = bench_gpt.run_multi(a.gpus, a.steps, a.warmup)
         if out is not None:
             print(json.dumps(out), flush=True)
         if dist.is_initialized():

@@ -121,9 +121,10 @@ int pd_col2im_pnhwc(const void* dcol, int N, int C, int H, int W, int kh, int kw
                     int Wo, int Kpad, void* dx_pad, int dtype, void* stream);
 /* MaxPool2d(3, stride 2, padding 1) and the global AvgPool2d(7) of resnet50 (stage0.py:13, stage2.py),
  * padded NHWC in; the average pool writes / reads a contiguous [N, C] matrix.                       */
-int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, void* y_pad, int dtype, void* stream);
-int pd_maxpool3s2_bwd(const void* x_pad, const void* dy_pad, int N, int C, int H, int W, void* dx_pad, int dtype,
-                      void* stream);
+int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, void* y_pad, unsigned char* argmax, int dtype,
+                      void* stream);   /* argmax: [N,Ho,Wo,C] bytes (position r*3+s of the window maximum) or NULL */
+int pd_maxpool3s2_bwd(const unsigned char* argmax, const void* dy_pad, int N, int C, int H, int W, void* dx_pad,
+                      int dtype, void* stream);
 int pd_avgpool_fwd(const void* x_pad, int N, int C, int H, int W, void* y, int dtype, void* stream);
 int pd_avgpool_bwd(const void* dy, int N, int C, int H, int W, void* dx_pad, int dtype, void* stream);
 
@@ -200,6 +201,19 @@ int pd_conv2d_dgrad(int dtype, const void* dy_pad, int N, int H, int W, int Cout
                     int64_t ldw, int Cin, const void* relu_aux, void* dx_pad, void* stream);
 int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, int N, int H, int W, int Cin,
                     int Cout, float* dw, int64_t lddw, int accumulate, int split_k, void* stream);
+/* torch.nn.LayerNorm over the last dimension and torch.nn.GELU, for transformer stage modules (the 2BW
+ * configuration; the reference itself ships no such stage files, its runtime would reach ATen's kernels through
+ * torch.nn).  x, y, dy, dx: [rows, C] (C <= 1024); gamma, beta in `dtype`; mean, rstd: fp32 [rows] saved by the
+ * forward; dgamma, dbeta: fp32 [C], stored or accumulated; workspace: pd_layernorm_workspace_bytes(rows, C) bytes.
+ * GELU: tanh_form != 0 selects the tanh approximation, else the erf form.                                       */
+int64_t pd_layernorm_workspace_bytes(int64_t rows, int C);
+int pd_layernorm_fwd(int dtype, const void* x, int64_t rows, int C, const void* gamma, const void* beta, float eps,
+                     void* y, float* mean, float* rstd, void* stream);
+int pd_layernorm_bwd(int dtype, const void* x, const void* dy, const void* gamma, const float* mean,
+                     const float* rstd, int64_t rows, int C, void* dx, float* dgamma, float* dbeta, int accumulate,
+                     void* workspace, int64_t workspace_bytes, void* stream);
+int pd_gelu_fwd(int dtype, const void* x, void* y, int64_t n, int tanh_form, void* stream);
+int pd_gelu_bwd(int dtype, const void* x, const void* dy, void* dx, int64_t n, int tanh_form, void* stream);
 /* torch.nn.LSTM(I, H), one layer, one direction, [T,B,*] sequences (runtime/translation/models/
  * gnmt_large/gpus=4/stage0.py:11-19; the reference reaches cuDNN's RNN through it): the time loop.
  * The caller computes the input projections gx = x . W_ih^T + b_ih for all steps with pd_gemm_nt;

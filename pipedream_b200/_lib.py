@@ -44,13 +44,18 @@ SIGNATURES = {
     "pd_dropout_fwd": (I, [P, P, P, L, F, U64, U64, I, P]),
     "pd_dropout_bwd": (I, [P, P, P, L, F, I, P]),
     "pd_add": (I, [P, P, P, L, I, P]),
+    "pd_layernorm_workspace_bytes": (L, [L, I]),
+    "pd_layernorm_fwd": (I, [I, P, L, I, P, P, F, P, P, P, P]),
+    "pd_layernorm_bwd": (I, [I, P, P, P, P, P, L, I, P, P, P, I, P, L, P]),
+    "pd_gelu_fwd": (I, [I, P, P, L, I, P]),
+    "pd_gelu_bwd": (I, [I, P, P, P, L, I, P]),
     "pd_bn_workspace_bytes": (L, [I]),
     "pd_bn_fwd": (I, [I, P, P, I, I, I, I, P, P, F, F, I, P, P, P, P, P, P, L, P]),
     "pd_bn_apply": (I, [I, P, P, I, I, I, I, P, P, P, P, I, P, P]),
     "pd_bn_bwd": (I, [I, P, P, P, I, I, I, I, P, P, P, P, P, I, P, P, P, P, L, P]),
     "pd_im2col": (I, [P, I, L, L, L, L, I, I, I, I, I, I, I, I, I, I, I, P, I, P]),
     "pd_col2im_pnhwc": (I, [P, I, I, I, I, I, I, I, I, I, I, I, P, I, P]),
-    "pd_maxpool3s2_fwd": (I, [P, I, I, I, I, P, I, P]),
+    "pd_maxpool3s2_fwd": (I, [P, I, I, I, I, P, P, I, P]),
     "pd_maxpool3s2_bwd": (I, [P, P, I, I, I, I, P, I, P]),
     "pd_avgpool_fwd": (I, [P, I, I, I, I, P, I, P]),
     "pd_avgpool_bwd": (I, [P, I, I, I, I, P, I, P]),

@@ -71,7 +71,8 @@ col2im_kernel(const T* __restrict__ dcol, int N, int C, int H, int W, int kh, in
 // MaxPool2d(kernel 3, stride 2, padding 1) on padded NHWC; the padding of the pool counts as -inf.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-maxpool3s2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, int Ho, int Wo, T* __restrict__ y) {
+maxpool3s2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, int Ho, int Wo, T* __restrict__ y,
+                      unsigned char* __restrict__ amax) {
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
   const int64_t total = (int64_t)N * Hop * Wop * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -81,23 +82,28 @@ maxpool3s2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, int H
     float m = 0.f;
     if (hop >= 1 && hop <= Ho && wop >= 1 && wop <= Wo) {
       m = -INFINITY;
+      int am = 0;
       const int h0 = (hop - 1) * 2 - 1, w0 = (wop - 1) * 2 - 1;
       for (int r = 0; r < 3; ++r)
         for (int s = 0; s < 3; ++s) {
           const int h = h0 + r, w = w0 + s;
-          if (h >= 0 && h < H && w >= 0 && w < W)
-            m = fmaxf(m, pd_to_float(x[(((int64_t)n * Hp + h + 1) * Wp + w + 1) * C + c]));
+          if (h >= 0 && h < H && w >= 0 && w < W) {
+            const float v = pd_to_float(x[(((int64_t)n * Hp + h + 1) * Wp + w + 1) * C + c]);
+            if (v > m) { m = v; am = r * 3 + s; }
+          }
         }
+      if (amax != nullptr) amax[(((int64_t)n * Ho + hop - 1) * Wo + wop - 1) * C + c] = (unsigned char)am;
     }
     y[i] = pd_from_float<T>(m);
   }
 }
 
-// The gradient of a window goes to its first maximum in (h,w) scan order, as ATen's max_pool2d does.
+// The gradient of a window goes to its first maximum in (h,w) scan order, as ATen's max_pool2d does; the forward
+// recorded that position (r*3+s) per output element.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-maxpool3s2_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, int N, int C, int H, int W, int Ho, int Wo,
-                      T* __restrict__ dx) {
+maxpool3s2_bwd_kernel(const unsigned char* __restrict__ amax, const T* __restrict__ dy, int N, int C, int H, int W, int Ho,
+                      int Wo, T* __restrict__ dx) {
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
   const int64_t total = (int64_t)N * Hp * Wp * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -107,20 +113,11 @@ maxpool3s2_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, int N, 
     float g = 0.f;
     if (hp >= 1 && hp <= H && wp >= 1 && wp <= W) {
       const int h = hp - 1, w = wp - 1;
-      // output windows that contain (h, w): ho in [ceil((h-1)/2), floor((h+1)/2)]
-      for (int ho = max(0, (h - 1 + 1) / 2); ho <= min(Ho - 1, (h + 1) / 2); ++ho)
-        for (int wo = max(0, (w - 1 + 1) / 2); wo <= min(Wo - 1, (w + 1) / 2); ++wo) {
-          const int h0 = ho * 2 - 1, w0 = wo * 2 - 1;
-          float m = -INFINITY; int ah = -1, aw = -1;
-          for (int r = 0; r < 3; ++r)
-            for (int s = 0; s < 3; ++s) {
-              const int hh = h0 + r, ww = w0 + s;
-              if (hh >= 0 && hh < H && ww >= 0 && ww < W) {
-                const float v = pd_to_float(x[(((int64_t)n * Hp + hh + 1) * Wp + ww + 1) * C + c]);
-                if (v > m) { m = v; ah = hh; aw = ww; }
-              }
-            }
-          if (ah == h && aw == w) g += pd_to_float(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C + c]);
+      for (int ho = max(0, h / 2); ho <= min(Ho - 1, (h + 1) / 2); ++ho)
+        for (int wo = max(0, w / 2); wo <= min(Wo - 1, (w + 1) / 2); ++wo) {
+          const int mine = (h - (ho * 2 - 1)) * 3 + (w - (wo * 2 - 1));
+          if (amax[(((int64_t)n * Ho + ho) * Wo + wo) * C + c] == mine)
+            g += pd_to_float(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C + c]);
         }
     }
     dx[i] = pd_from_float<T>(g);
@@ -206,27 +203,36 @@ template <typename S>
 __global__ void __launch_bounds__(kThreads)
 im2col_gather8_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW, int N, int C, int H, int W,
                       int kh, int kw, int stride, int pad, int Ho, int Wo, int Kpad, uint4* __restrict__ dst) {
+  // per patch-matrix column: offset of (c, r, s) inside an image and (r, s) packed; built once per block so
+  // that the inner loop has no integer division
+  extern __shared__ int tab[];
+  const int K = kh * kw * C;
+  for (int k = threadIdx.x; k < Kpad; k += kThreads) {
+    int off = 0, rs = 0xffff;
+    if (k < K) {
+      const int t = k / C, c = k - t * C;
+      const int r = t / kw, s_ = t - r * kw;
+      off = (int)(c * sC + r * sH + s_ * sW);
+      rs = (r << 8) | s_;
+    }
+    tab[2 * k] = off;
+    tab[2 * k + 1] = rs;
+  }
+  __syncthreads();
   const int KV = Kpad / 8;
   const int64_t total = (int64_t)N * Ho * Wo * KV;
-  const int K = kh * kw * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int k0 = (int)(i % KV) * 8;
     const int64_t p = i / KV;
     const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
     const int hb = ho * stride - pad, wb = wo * stride - pad;
-    const S* base = src + n * sN;
+    const S* base = src + n * sN + hb * sH + wb * sW;
     float f[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int k = k0 + j;
-      float v = 0.f;
-      if (k < K) {
-        const int t = k / C, c = k - t * C;
-        const int r = t / kw;
-        const int h = hb + r, w = wb + (t - r * kw);
-        if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(base[c * sC + h * sH + w * sW]);
-      }
-      f[j] = v;
+      const int off = tab[2 * (k0 + j)], rs = tab[2 * (k0 + j) + 1];
+      const int h = hb + (rs >> 8), w = wb + (rs & 0xff);
+      f[j] = (rs != 0xffff && h >= 0 && h < H && w >= 0 && w < W) ? pd_to_float(base[off]) : 0.f;
     }
     dst[i] = pack8(f);
   }
@@ -269,7 +275,8 @@ col2im_v8_kernel(const __nv_bfloat16* __restrict__ dcol, int N, int C, int H, in
 }
 
 __global__ void __launch_bounds__(kThreads)
-maxpool3s2_fwd_v8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int W, int Ho, int Wo, uint4* __restrict__ y) {
+maxpool3s2_fwd_v8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int W, int Ho, int Wo, uint4* __restrict__ y,
+                         uint2* __restrict__ amax) {
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
   const int64_t total = (int64_t)N * Hop * Wop * C8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -279,8 +286,9 @@ maxpool3s2_fwd_v8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int 
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (hop >= 1 && hop <= Ho && wop >= 1 && wop <= Wo) {
       float m[8];
+      unsigned int am[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) m[k] = -INFINITY;
+      for (int k = 0; k < 8; ++k) { m[k] = -INFINITY; am[k] = 0u; }
       const int h0 = (hop - 1) * 2 - 1, w0 = (wop - 1) * 2 - 1;
 #pragma unroll
       for (int r = 0; r < 3; ++r)
@@ -291,18 +299,22 @@ maxpool3s2_fwd_v8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int 
             float f[8];
             unpack8(x[(((int64_t)n * Hp + h + 1) * Wp + w + 1) * C8 + c], f);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) m[k] = fmaxf(m[k], f[k]);
+            for (int k = 0; k < 8; ++k)
+              if (f[k] > m[k]) { m[k] = f[k]; am[k] = (unsigned int)(r * 3 + s); }
           }
         }
       out = pack8(m);
+      if (amax != nullptr)
+        amax[(((int64_t)n * Ho + hop - 1) * Wo + wop - 1) * C8 + c] =
+            make_uint2(am[0] | (am[1] << 8) | (am[2] << 16) | (am[3] << 24), am[4] | (am[5] << 8) | (am[6] << 16) | (am[7] << 24));
     }
     y[i] = out;
   }
 }
 
 __global__ void __launch_bounds__(kThreads)
-maxpool3s2_bwd_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, int N, int C8, int H, int W, int Ho, int Wo,
-                         uint4* __restrict__ dx) {
+maxpool3s2_bwd_v8_kernel(const uint2* __restrict__ amax, const uint4* __restrict__ dy, int N, int C8, int H, int W, int Ho,
+                         int Wo, uint4* __restrict__ dx) {
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
   const int64_t total = (int64_t)N * Hp * Wp * C8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -316,30 +328,15 @@ maxpool3s2_bwd_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ 
       const int h = hp - 1, w = wp - 1;
       for (int ho = max(0, h / 2); ho <= min(Ho - 1, (h + 1) / 2); ++ho)
         for (int wo = max(0, w / 2); wo <= min(Wo - 1, (w + 1) / 2); ++wo) {
-          const int h0 = ho * 2 - 1, w0 = wo * 2 - 1;
-          const int mine = (h - h0) * 3 + (w - w0);
-          float m[8];
-          int am[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) { m[k] = -INFINITY; am[k] = -1; }
-#pragma unroll
-          for (int r = 0; r < 3; ++r)
-#pragma unroll
-            for (int s = 0; s < 3; ++s) {
-              const int hh = h0 + r, ww = w0 + s;
-              if (hh >= 0 && hh < H && ww >= 0 && ww < W) {
-                float f[8];
-                unpack8(x[(((int64_t)n * Hp + hh + 1) * Wp + ww + 1) * C8 + c], f);
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                  if (f[k] > m[k]) { m[k] = f[k]; am[k] = r * 3 + s; }
-              }
-            }
+          const unsigned int mine = (unsigned int)((h - (ho * 2 - 1)) * 3 + (w - (wo * 2 - 1)));
+          const uint2 a = amax[(((int64_t)n * Ho + ho) * Wo + wo) * C8 + c];
           float d[8];
           unpack8(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C8 + c], d);
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            if (am[k] == mine) g[k] += d[k];
+          for (int k = 0; k < 8; ++k) {
+            const unsigned int ak = ((k < 4 ? a.x : a.y) >> (8 * (k & 3))) & 0xffu;
+            if (ak == mine) g[k] += d[k];
+          }
         }
     }
     dx[i] = pack8(g);
@@ -369,12 +366,13 @@ PD_EXPORT int pd_im2col(const void* src, int src_dtype, int64_t sN, int64_t sC, 
       (sH % 8) == 0 && (sW % 8) == 0 && aligned16(src) && aligned16(dst)) {
     im2col_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sH, sW, N, C, H, W, kh, kw, stride, pad,
                                                               Ho, Wo, Kpad, (uint4*)dst);
-  } else if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && aligned16(dst)) {
+  } else if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && Kpad <= 4096 && kh < 255 && kw < 255 && aligned16(dst) &&
+             (int64_t)C * sC + (int64_t)kh * sH + (int64_t)kw * sW < (1ll << 31)) {
     if (src_dtype == PD_F32)
-      im2col_gather8_kernel<float><<<grid_for(total / 8), kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, kh, kw,
+      im2col_gather8_kernel<float><<<grid_for(total / 8), kThreads, (size_t)Kpad * 8, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, kh, kw,
                                                                             stride, pad, Ho, Wo, Kpad, (uint4*)dst);
     else if (src_dtype == PD_BF16)
-      im2col_gather8_kernel<__nv_bfloat16><<<grid_for(total / 8), kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H,
+      im2col_gather8_kernel<__nv_bfloat16><<<grid_for(total / 8), kThreads, (size_t)Kpad * 8, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, C, H,
                                                                                     W, kh, kw, stride, pad, Ho, Wo, Kpad, (uint4*)dst);
     else PD_REQUIRE(false, "pd_im2col: bad dtype combination");
   } else if (src_dtype == PD_F32 && dst_dtype == PD_F32)
@@ -406,35 +404,37 @@ PD_EXPORT int pd_col2im_pnhwc(const void* dcol, int N, int C, int H, int W, int 
   return PD_OK;
 }
 
-PD_EXPORT int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, void* y_pad, int dtype, void* stream) {
+PD_EXPORT int pd_maxpool3s2_fwd(const void* x_pad, int N, int C, int H, int W, void* y_pad, unsigned char* argmax, int dtype,
+                                void* stream) {
   int rc = pd_check_device();
   if (rc != PD_OK) return rc;
   PD_REQUIRE(x_pad && y_pad && N > 0 && C > 0 && H > 0 && W > 0, "pd_maxpool3s2_fwd: bad arguments");
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * (Ho + 2) * (Wo + 2) * C;
-  if (dtype == PD_BF16 && (C % 8) == 0 && aligned16(x_pad) && aligned16(y_pad)) {
-    maxpool3s2_fwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint4*)x_pad, N, C / 8, H, W, Ho, Wo, (uint4*)y_pad);
+  if (dtype == PD_BF16 && (C % 8) == 0 && aligned16(x_pad) && aligned16(y_pad) && (((uintptr_t)argmax) & 7) == 0) {
+    maxpool3s2_fwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint4*)x_pad, N, C / 8, H, W, Ho, Wo, (uint4*)y_pad,
+                                                                      (uint2*)argmax);
   } else {
-    PD_T2(dtype, maxpool3s2_fwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, N, C, H, W, Ho, Wo, (T*)y_pad);)
+    PD_T2(dtype, maxpool3s2_fwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, N, C, H, W, Ho, Wo, (T*)y_pad, argmax);)
   }
   PD_LAUNCH_CHECK("maxpool3s2_fwd_kernel");
   return PD_OK;
 }
 
-PD_EXPORT int pd_maxpool3s2_bwd(const void* x_pad, const void* dy_pad, int N, int C, int H, int W, void* dx_pad, int dtype,
-                                void* stream) {
+PD_EXPORT int pd_maxpool3s2_bwd(const unsigned char* argmax, const void* dy_pad, int N, int C, int H, int W, void* dx_pad,
+                                int dtype, void* stream) {
   int rc = pd_check_device();
   if (rc != PD_OK) return rc;
-  PD_REQUIRE(x_pad && dy_pad && dx_pad && N > 0 && C > 0 && H > 0 && W > 0, "pd_maxpool3s2_bwd: bad arguments");
+  PD_REQUIRE(argmax && dy_pad && dx_pad && N > 0 && C > 0 && H > 0 && W > 0, "pd_maxpool3s2_bwd: bad arguments");
   const int Ho = (H + 2 - 3) / 2 + 1, Wo = (W + 2 - 3) / 2 + 1;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
-  if (dtype == PD_BF16 && (C % 8) == 0 && aligned16(x_pad) && aligned16(dy_pad) && aligned16(dx_pad)) {
-    maxpool3s2_bwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint4*)x_pad, (const uint4*)dy_pad, N, C / 8, H, W, Ho, Wo,
-                                                                      (uint4*)dx_pad);
+  if (dtype == PD_BF16 && (C % 8) == 0 && (((uintptr_t)argmax) & 7) == 0 && aligned16(dy_pad) && aligned16(dx_pad)) {
+    maxpool3s2_bwd_v8_kernel<<<grid_for(total / 8), kThreads, 0, s>>>((const uint2*)argmax, (const uint4*)dy_pad, N, C / 8, H, W, Ho,
+                                                                      Wo, (uint4*)dx_pad);
   } else {
-    PD_T2(dtype, maxpool3s2_bwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>((const T*)x_pad, (const T*)dy_pad, N, C, H, W, Ho, Wo, (T*)dx_pad);)
+    PD_T2(dtype, maxpool3s2_bwd_kernel<T><<<grid_for(total), kThreads, 0, s>>>(argmax, (const T*)dy_pad, N, C, H, W, Ho, Wo, (T*)dx_pad);)
   }
   PD_LAUNCH_CHECK("maxpool3s2_bwd_kernel");
   return PD_OK;

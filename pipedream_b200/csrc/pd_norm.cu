@@ -131,13 +131,15 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* 
 }
 
 // ------------------------------------------------------------------------------------------------
-// second level of the reductions (both paths): one block per 32 channels, 8 slices of the partials each
+// second level of the reductions (both paths): one block per 32 channels, 32 slices of the partials each
+// (the loop over the partials is a chain of L2 round trips: short and wide beats long and narrow)
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void sum_partials(const float* __restrict__ partial, int nblocks, int C, int c,
-                                             float (*sh)[8][33], float& s, float& q) {
+                                             float (*sh)[32][33], float& s, float& q) {
   s = q = 0.f;
   if (c < C) {
-    for (int b = threadIdx.y; b < nblocks; b += 8) {
+#pragma unroll 4
+    for (int b = threadIdx.y; b < nblocks; b += 32) {
       s += partial[((int64_t)b * 2) * C + c];
       q += partial[((int64_t)b * 2 + 1) * C + c];
     }
@@ -148,7 +150,7 @@ __device__ __forceinline__ void sum_partials(const float* __restrict__ partial, 
   if (threadIdx.y == 0) {
     s = q = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 32; ++j) {
       s += sh[0][j][threadIdx.x];
       q += sh[1][j][threadIdx.x];
     }
@@ -156,11 +158,11 @@ __device__ __forceinline__ void sum_partials(const float* __restrict__ partial, 
 }
 
 // Forward: mean, invstd from the partial sums; running statistics (momentum, unbiased variance).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 bn_stats_final_kernel(const float* __restrict__ partial, int nblocks, int C, float count, float eps, float momentum,
                       float* __restrict__ mean, float* __restrict__ invstd, float* __restrict__ running_mean,
                       float* __restrict__ running_var) {
-  __shared__ float sh[2][8][33];
+  __shared__ float sh[2][32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s, q;
   sum_partials(partial, nblocks, C, c, sh, s, q);
@@ -177,10 +179,10 @@ bn_stats_final_kernel(const float* __restrict__ partial, int nblocks, int C, flo
 }
 
 // Backward: sums[0][C] = sum(g), sums[1][C] = sum(g*xhat); also the parameter gradients.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 bn_bwd_final_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ sums,
                     float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
-  __shared__ float sh[2][8][33];
+  __shared__ float sh[2][32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s, q;
   sum_partials(partial, nblocks, C, c, sh, s, q);
@@ -435,7 +437,7 @@ PD_EXPORT int pd_bn_fwd(int dtype, const void* x_pad, const void* res_pad, int N
       bn_reduce_kernel<__nv_bfloat16><<<nb, kThreads, 0, s>>>((const __nv_bfloat16*)x_pad, nullptr, nullptr, nullptr, nullptr, rows, C, 0, (float*)workspace);
   }
   PD_LAUNCH_CHECK("bn_reduce_kernel");
-  bn_stats_final_kernel<<<(C + 31) / 32, dim3(32, 8), 0, s>>>((const float*)workspace, nb, C, count, eps, momentum,
+  bn_stats_final_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)workspace, nb, C, count, eps, momentum,
                                                               mean, invstd, running_mean, running_var);
   PD_LAUNCH_CHECK("bn_stats_final_kernel");
   if (vec) {
@@ -525,7 +527,7 @@ PD_EXPORT int pd_bn_bwd(int dtype, const void* x_pad, const void* dy_pad, const 
                                                               (const __nv_bfloat16*)y_pad, mean, invstd, rows, C, 1, (float*)workspace);
   }
   PD_LAUNCH_CHECK("bn_reduce_kernel");
-  bn_bwd_final_kernel<<<(C + 31) / 32, dim3(32, 8), 0, s>>>((const float*)workspace, nb, C, sums_ws, dgamma, dbeta, accumulate);
+  bn_bwd_final_kernel<<<(C + 31) / 32, dim3(32, 32), 0, s>>>((const float*)workspace, nb, C, sums_ws, dgamma, dbeta, accumulate);
   PD_LAUNCH_CHECK("bn_bwd_final_kernel");
   if (vec) {
     const int grid = vec_grid(nvec, 2);

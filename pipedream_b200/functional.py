@@ -508,19 +508,21 @@ def col2im_pnhwc(dcol, N, C, H, W, kh, kw, stride, pad, Ho, Wo):
     return dx
 
 
-def maxpool3s2_fwd(x_pad):
+def maxpool3s2_fwd(x_pad, want_argmax=True):
+    """Returns (y_pad, argmax): argmax [N,Ho,Wo,C] uint8 = position r*3+s of each window's first maximum."""
     N, Hp, Wp, C = x_pad.shape
     H, W = Hp - 2, Wp - 2
     Ho, Wo = (H - 1) // 2 + 1, (W - 1) // 2 + 1
     y = torch.empty((N, Ho + 2, Wo + 2, C), dtype=x_pad.dtype, device=x_pad.device)
-    call("pd_maxpool3s2_fwd", _p(x_pad), N, C, H, W, _p(y), dt(x_pad), _stream())
-    return y
+    amax = torch.empty((N, Ho, Wo, C), dtype=torch.uint8, device=x_pad.device) if want_argmax else None
+    call("pd_maxpool3s2_fwd", _p(x_pad), N, C, H, W, _p(y), _p(amax), dt(x_pad), _stream())
+    return y, amax
 
 
-def maxpool3s2_bwd(x_pad, dy_pad):
-    N, Hp, Wp, C = x_pad.shape
-    dx = torch.empty_like(x_pad)
-    call("pd_maxpool3s2_bwd", _p(x_pad), _p(dy_pad), N, C, Hp - 2, Wp - 2, _p(dx), dt(x_pad), _stream())
+def maxpool3s2_bwd(amax, dy_pad, H, W):
+    N, _, _, C = dy_pad.shape
+    dx = torch.empty((N, H + 2, W + 2, C), dtype=dy_pad.dtype, device=dy_pad.device)
+    call("pd_maxpool3s2_bwd", _p(amax), _p(dy_pad), N, C, H, W, _p(dx), dt(dy_pad), _stream())
     return dx
 
 
@@ -534,4 +536,40 @@ def avgpool_fwd(x_pad):
 def avgpool_bwd(dy, N, C, H, W):
     dx = torch.empty((N, H + 2, W + 2, C), dtype=dy.dtype, device=dy.device)
     call("pd_avgpool_bwd", _p(dy), N, C, H, W, _p(dx), dt(dy), _stream())
+    return dx
+
+
+# --------------------------------------------------------------------------- #
+# layer norm, GELU (transformer stages)
+# --------------------------------------------------------------------------- #
+def layernorm_fwd(x2d, gamma, beta, eps):
+    """x2d: [rows, C] contiguous.  Returns (y, mean fp32 [rows], rstd fp32 [rows])."""
+    _cuda(x2d, gamma, beta)
+    rows, C = x2d.shape
+    y = torch.empty_like(x2d)
+    mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    call("pd_layernorm_fwd", dt(x2d), _p(x2d), rows, C, _p(gamma), _p(beta), float(eps), _p(y), _p(mean), _p(rstd), _stream())
+    return y, mean, rstd
+
+
+def layernorm_bwd(x2d, dy2d, gamma, mean, rstd, dgamma, dbeta, accumulate):
+    rows, C = x2d.shape
+    dx = torch.empty_like(x2d)
+    ws = _workspace(x2d.device, _lib.load().pd_layernorm_workspace_bytes(rows, C))
+    call("pd_layernorm_bwd", dt(x2d), _p(x2d), _p(dy2d), _p(gamma), _p(mean), _p(rstd), rows, C, _p(dx), _p(dgamma), _p(dbeta),
+         int(accumulate), _p(ws), ws.numel(), _stream())
+    return dx
+
+
+def gelu_fwd(x, tanh_form):
+    _cuda(x)
+    y = torch.empty_like(x)
+    call("pd_gelu_fwd", dt(x), _p(x), _p(y), x.numel(), int(tanh_form), _stream())
+    return y
+
+
+def gelu_bwd(x, dy, tanh_form):
+    dx = torch.empty_like(x)
+    call("pd_gelu_bwd", dt(x), _p(x), _p(dy), _p(dx), x.numel(), int(tanh_form), _stream())
     return dx

@@ -394,15 +394,15 @@ class _MaxPool3s2Fn(torch.autograd.Function):
     def forward(ctx, x, out_nchw):
         N, C, H, W = x.shape
         x_pad = pf.as_padded(x)
-        y_pad = pf.maxpool3s2_fwd(x_pad)
-        ctx.x_pad, ctx.geom = x_pad, (N, C, H, W)
+        y_pad, amax = pf.maxpool3s2_fwd(x_pad, want_argmax=ctx.needs_input_grad[0])
+        ctx.amax, ctx.geom = amax, (N, C, H, W)
         Ho, Wo = y_pad.shape[1] - 2, y_pad.shape[2] - 2
         return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, Ho, Wo)
 
     @staticmethod
     def backward(ctx, dy):
         N, C, H, W = ctx.geom
-        return pf.nchw_view(pf.maxpool3s2_bwd(ctx.x_pad, pf.as_padded(dy)), N, C, H, W), None
+        return pf.nchw_view(pf.maxpool3s2_bwd(ctx.amax, pf.as_padded(dy), H, W), N, C, H, W), None
 
 
 class NativeMaxPool3s2(nn.Module):
@@ -571,6 +571,79 @@ class NativeDropout(nn.Module):
         off = self.offset
         self.offset += x.numel()
         return _DropoutFn.apply(x, self.p, self.seed, off)
+
+
+# --------------------------------------------------------------------------- #
+# LayerNorm, GELU (transformer stages)
+# --------------------------------------------------------------------------- #
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        g, b = weight.detach(), bias.detach()
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != g.dtype:
+            x2 = pf.convert(x2.contiguous(), g.dtype)
+        elif not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y, mean, rstd = pf.layernorm_fwd(x2, g, b, eps)
+        ctx.saved = (x2, mean, rstd)
+        ctx.params = (weight, bias)
+        ctx.in_dtype = x.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, mean, rstd = ctx.saved
+        weight, bias = ctx.params
+        g = weight.detach()
+        dy2 = dy.reshape(x2.shape)
+        if dy2.dtype != g.dtype:
+            dy2 = pf.convert(dy2.contiguous(), g.dtype)
+        elif not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        acc = take_accumulate_flag(weight)
+        take_accumulate_flag(bias)
+        dx = pf.layernorm_bwd(x2, dy2, g, mean, rstd, grad_buffer(weight), grad_buffer(bias), acc)
+        dx = dx.view(dy.shape)
+        return (dx if dx.dtype == ctx.in_dtype else dx.to(ctx.in_dtype)), None, None, None
+
+
+class NativeLayerNorm(nn.Module):
+    def __init__(self, ln):
+        super().__init__()
+        self.normalized_shape, self.eps = ln.normalized_shape, ln.eps
+        self.weight, self.bias = ln.weight, ln.bias
+        _mark_native(self.weight, self.bias)
+
+    @staticmethod
+    def supports(m):
+        return (isinstance(m, nn.LayerNorm) and m.elementwise_affine and m.bias is not None
+                and len(m.normalized_shape) == 1 and m.normalized_shape[0] <= 1024)
+
+    def forward(self, x):
+        return _LayerNormFn.apply(x, self.weight, self.bias, self.eps)
+
+
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tanh_form):
+        xc = x if x.is_contiguous() else x.contiguous()
+        ctx.x, ctx.tanh_form = xc, tanh_form
+        return pf.gelu_fwd(xc, tanh_form)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        return pf.gelu_bwd(ctx.x, dyc, ctx.tanh_form), None
+
+
+class NativeGELU(nn.Module):
+    def __init__(self, approximate="none"):
+        super().__init__()
+        self.approximate = approximate
+
+    def forward(self, x):
+        return _GeluFn.apply(x, self.approximate == "tanh")
 
 
 # --------------------------------------------------------------------------- #
@@ -930,7 +1003,8 @@ _LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway, NativeBat
                  NativeMaxPool3s2, NativeGlobalAvgPool)
 _NATIVE_TYPES = _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
                                  NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention,
-                                 NativeBatchNorm2d, NativeConvGeneric, NativeMaxPool3s2, NativeGlobalAvgPool)
+                                 NativeBatchNorm2d, NativeConvGeneric, NativeMaxPool3s2, NativeGlobalAvgPool,
+                                 NativeLayerNorm, NativeGELU)
 
 
 _PADDED_PRODUCERS = (NativeConv2d, NativeReLU, NativeMaxPool2d, NativeBatchNorm2d, NativeMaxPool3s2, NativeConvGeneric)
@@ -958,6 +1032,10 @@ def _swap_leaf(m):
         return NativeMaxPool2d()
     if NativeLinear.supports(m):
         return NativeLinear(m)
+    if NativeLayerNorm.supports(m):
+        return NativeLayerNorm(m)
+    if isinstance(m, nn.GELU):
+        return NativeGELU(m.approximate)
     if NativeLSTM.supports(m):
         return NativeLSTM(m)
     if NativeEmuBidirLSTM.supports(m):

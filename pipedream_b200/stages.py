@@ -413,3 +413,61 @@ def resnet50(num_stages=1, stage_to_rank_map=None):
     n = len(chunks)
     ranks = stage_to_rank_map or {s: [s] for s in range(n)}
     return _Pkg("resnet50", None, {"module_to_stage_map": list(range(n)) + [n - 1], "stage_to_rank_map": ranks})
+
+
+def gpt2(num_stages=1, layers=24, hidden=1024, heads=16, seq_len=512, vocab=50257, dropout=0.1, stage_to_rank_map=None):
+    """GPT-style decoder cut into `num_stages` consecutive stages: embeddings with the first blocks, final
+    LayerNorm and the output projection with the last.  The vocabulary is padded to a multiple of 64 (50257 ->
+    50304) so that logits rows are 16-byte aligned; the padding classes are never targets."""
+    from . import gpt_blocks as gb
+    vpad = (vocab + 63) // 64 * 64
+    units = ["embed"] + ["block"] * layers + ["head"]
+    costs = [1] + [12 * hidden * hidden + 2 * seq_len * hidden] * layers + [hidden * vpad]
+    sizes = _balanced_cuts(costs, num_stages)
+    chunks, i = [], 0
+    for sz in sizes:
+        chunks.append(units[i:i + sz])
+        i += sz
+
+    class _Pkg(StagePackage):
+        def stages(self_inner):
+            out = []
+            for ch in chunks:
+                parts = []
+                for u in ch:
+                    if u == "embed":
+                        parts.append(gb.Embed(vpad, seq_len, hidden, dropout))
+                    elif u == "head":
+                        parts.append(gb.Head(hidden, vpad))
+                    else:
+                        parts.append(gb.Block(hidden, heads, dropout))
+                out.append(gb.GptStage(parts))
+            return out
+
+        def boundary_shapes(self_inner, batch):
+            shapes = {"input0": (batch, seq_len), "target": (batch * seq_len,)}
+            for k, ch in enumerate(chunks):
+                shapes["out%d" % k] = (batch * seq_len, vpad) if ch[-1] == "head" else (batch, seq_len, hidden)
+            return shapes
+
+    n = len(chunks)
+    ranks = stage_to_rank_map or {s: [s] for s in range(n)}
+    pkg = _Pkg("gpt2", None, {"module_to_stage_map": list(range(n)) + [n - 1], "stage_to_rank_map": ranks})
+    pkg.vocab, pkg.vocab_padded, pkg.seq_len = vocab, vpad, seq_len
+    return pkg
+
+
+class SyntheticTokens:
+    """Iterable of (tokens [B, T] int64, next-token targets [B*T] int64): ids uniform over the vocabulary."""
+
+    def __init__(self, batch, steps, seq_len=512, vocab=50257, seed=2468):
+        self.batch, self.steps, self.seq_len, self.vocab, self.seed = batch, steps, seq_len, vocab, seed
+
+    def __len__(self):
+        return self.steps
+
+    def __iter__(self):
+        for step in range(self.steps):
+            g = torch.Generator().manual_seed(self.seed + step)
+            ids = torch.randint(0, self.vocab, (self.batch, self.seq_len + 1), generator=g)
+            yield ids[:, :-1].contiguous(), ids[:, 1:].contiguous().view(-1)
