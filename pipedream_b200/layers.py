@@ -233,7 +233,8 @@ class NativeBatchNorm2d(nn.Module):
         # runtime/runtime.py:229)
         self.register_buffer("running_mean", bn.running_mean.detach().float().clone())
         self.register_buffer("running_var", bn.running_var.detach().float().clone())
-        self.register_buffer("num_batches_tracked", bn.num_batches_tracked.detach().clone())
+        # kept on the host: incrementing it every step would otherwise be one more (tiny) launch per layer
+        self.register_buffer("num_batches_tracked", bn.num_batches_tracked.detach().cpu().clone())
         _mark_native(self.weight, self.bias)
 
     @staticmethod
