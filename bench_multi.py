@@ -103,15 +103,21 @@ def run_phase(r, opt, loader, n0, warm0, read_loss):
     for _ in range(w):
         r.run_forward()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []
     for i in range(n - w):
         if i == skip:
             torch.cuda.synchronize()
             dist.barrier()
             start.record()
+        if len(marks) >= 2:
+            marks.pop(0).synchronize()      # bounded run-ahead of the host (see bench_gnmt.run)
         r.run_forward()
         if read_loss and r.is_criterion:
             r.loss.item()
         _backward(r, opt)
+        ev = torch.cuda.Event()
+        ev.record()
+        marks.append(ev)
     for _ in range(w):
         _backward(r, opt)
     end.record()

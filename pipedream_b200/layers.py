@@ -469,7 +469,7 @@ class _ReLUFn(torch.autograd.Function):
             return pf.unpack_pnhwc(y_pad) if out_nchw else pf.nchw_view(y_pad, N, C, H, W)
         xc = x if x.is_contiguous() else x.contiguous()
         y = pf.relu(xc)
-        ctx.y = y
+        ctx.y = y.detach()        # not the returned object itself (reference cycle through grad_fn)
         ctx.geom = None
         return y
 
@@ -734,7 +734,9 @@ class _LSTMFn(torch.autograd.Function):
             x2 = x2.contiguous()
         gx = pf.gemm_nt(x2, wi, bias=b_ih.detach() if b_ih is not None else None)
         y, act, c_all = pf.lstm_fwd(gx, wh, b_hh.detach() if b_hh is not None else None, T, B, H)
-        ctx.saved = (x2, y, act, c_all)
+        # an output kept on ctx must be a different tensor object than the one returned: the returned one gets
+        # this node as its grad_fn, and node -> tensor -> node is a cycle no collector can see (it leaks the step)
+        ctx.saved = (x2, y.detach(), act, c_all)
         ctx.params = (w_ih, w_hh, b_ih, b_hh)
         ctx.geom = (T, B, I, H)
         ctx.x_dtype = x.dtype
@@ -902,7 +904,7 @@ class _AttnFn(torch.autograd.Function):
         vf = v.detach().float().contiguous()
         keys_c = keys if keys.is_contiguous() else keys.contiguous()
         probs, context = pf.attn_fwd(pq.contiguous(), pk.contiguous(), keys_c, vf, nbd, ctx_len)
-        ctx.saved = (pq, pk, keys_c, vf, nbd, probs)
+        ctx.saved = (pq, pk, keys_c, vf, nbd, probs.detach())   # not the returned object (cycle through grad_fn)
         ctx.v_dtype, ctx.nb_dtype = v.dtype, nb.dtype
         ctx.mark_non_differentiable(probs)
         return context, probs
