@@ -455,3 +455,24 @@ def test_bahdanau_attention(dtype):
     for name in ("linear_q", "linear_k"):
         e = rel_err(getattr(nat, name).weight._pd_grad, getattr(ref, name).weight.grad)
         assert e <= tol, "%s: %.3e" % (name, e)
+
+
+def test_no_memory_growth_across_steps():
+    """Nothing saved for backward may keep a step alive after its backward ran (an output stored on the autograd
+    context next to being returned forms a cycle through grad_fn that no collector sees)."""
+    from pipedream_b200 import layers
+    torch.manual_seed(0)
+    lstm = layers.NativeLSTM(torch.nn.LSTM(64, 64).cuda().to(torch.bfloat16))
+    lin = layers.NativeLinear(torch.nn.Linear(64, 64).cuda().to(torch.bfloat16))
+    relu = layers.NativeReLU()
+    base = None
+    for i in range(8):
+        x = rnd(12, 16, 64, dtype=torch.bfloat16, seed=80 + i).requires_grad_(True)
+        y, _ = lstm(x)
+        z = relu(lin(y).view(-1, 64))          # 2-D ReLU path
+        z.float().sum().backward()
+        del x, y, z
+        torch.cuda.synchronize()
+        if i == 3:
+            base = torch.cuda.memory_allocated()
+    assert torch.cuda.memory_allocated() <= base, (torch.cuda.memory_allocated(), base)
