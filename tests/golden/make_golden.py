@@ -1,8 +1,9 @@
 """Generates the golden fixtures in this directory by running the *reference* implementation.
 
-Run in a container where the reference checkout is mounted (default /root/reference):
+Run where a checkout of the reference (msr-fiddle/pipedream) is available; pass its path with --ref or in
+the PIPEDREAM_REFERENCE environment variable:
 
-    python tests/golden/make_golden.py [--ref /root/reference] [--only routing|stashing|vgg16|gnmt]
+    python tests/golden/make_golden.py --ref <reference checkout> [--only routing|stashing|vgg16|gnmt]
 
 It imports the reference's runtime/ modules unmodified and records what they compute:
 
@@ -433,7 +434,7 @@ def make_gnmt(ref, steps=3, batch=8):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("PIPEDREAM_REFERENCE"), required=os.environ.get("PIPEDREAM_REFERENCE") is None)
     ap.add_argument("--only", default=None)
     ap.add_argument("--worker", type=int, default=None)
     ap.add_argument("--steps", type=int, default=20)
