@@ -22,7 +22,15 @@ def dt(t):
         raise _lib.PipedreamB200Error("unsupported dtype %s (fp32 and bf16 only)" % t.dtype)
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_CUR_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current stream of the current device as a raw handle (every entry point takes one).  The two private
+    torch accessors avoid building a torch.cuda.Stream object per call; the public path is the fallback."""
+    if _RAW_STREAM is not None and _CUR_DEVICE is not None:
+        return ctypes.c_void_p(_RAW_STREAM(_CUR_DEVICE()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -179,7 +187,7 @@ _WS = {}
 
 
 def _workspace(device, nbytes):
-    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    key = (device.index, _stream().value)
     ws = _WS.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
