@@ -243,7 +243,7 @@ def run_gpu_single(steps, warmup):
         # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the 56x56 256->256 layer
         # (profiles/gemm_tcgen05_conv_56x56_256_ncu.md), averaged over its fwd / dgrad / wgrad launches;
         # the algorithmic bytes of that launch are 221.6 MB
-        "traffic": 331.0e6, "traffic_case": "conv 64x56x56 256->256, mean of fwd/dgrad/wgrad; algorithmic 221.6e6",
+        "traffic": 332.0e6, "traffic_case": "conv 64x56x56 256->256, mean of fwd/dgrad/wgrad; algorithmic 221.6e6",
         "launches_per_step": n_launch // max(1, steps), "kernel_ms_per_step": round(tot_ms / steps, 3),
         "algorithmic_tflop_per_step": round(tot_flops / steps / 1e12, 3),
         "by_pass": {k: {"launches": v[0] // max(1, steps), "tflops": round(v[1] / (v[2] * 1e-3) / 1e12, 1),

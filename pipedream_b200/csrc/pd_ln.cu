@@ -114,6 +114,127 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
   for (int i = threadIdx.x; i < 2 * C; i += kThreads) partial[(int64_t)blockIdx.x * 2 * C + i] = sh[i];
 }
 
+// ---- bf16, C = 256 * NV (NV = 1..4): a lane owns NV 16-byte vectors of the row, everything stays in registers ----
+__device__ __forceinline__ void ln_unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 t = __bfloat1622float2(p[k]);
+    f[2 * k] = t.x;
+    f[2 * k + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 ln_pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+  return u;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kThreads)
+layernorm_fwd_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gamma, const uint4* __restrict__ beta,
+                        int64_t rows, float eps, uint4* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd) {
+  constexpr int C = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  float gm[NV * 8], bt[NV * 8];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    ln_unpack8(gamma[lane + 32 * k], gm + 8 * k);
+    ln_unpack8(beta[lane + 32 * k], bt + 8 * k);
+  }
+  for (int64_t r = warp0; r < rows; r += (int64_t)gridDim.x * kWarps) {
+    const uint4* xr = x + r * (C / 8);
+    float v[NV * 8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) ln_unpack8(xr[lane + 32 * k], v + 8 * k);
+#pragma unroll
+    for (int j = 0; j < NV * 8; ++j) s += v[j];
+    const float m = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV * 8; ++j) { const float d = v[j] - m; q += d * d; }
+    const float rs = rsqrtf(warp_sum(q) / (float)C + eps);
+    uint4* yr = y + r * (C / 8);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[8 * k + j] - m) * rs * gm[8 * k + j] + bt[8 * k + j];
+      yr[lane + 32 * k] = ln_pack8(o);
+    }
+    if (lane == 0) { mean[r] = m; rstd[r] = rs; }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kThreads)
+layernorm_bwd_v8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, const uint4* __restrict__ gamma,
+                        const float* __restrict__ mean, const float* __restrict__ rstd, int64_t rows,
+                        uint4* __restrict__ dx, float* __restrict__ partial) {
+  constexpr int C = NV * 256;
+  extern __shared__ float sh[];            // [2][C] block accumulators
+  for (int i = threadIdx.x; i < 2 * C; i += kThreads) sh[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  float gm[NV * 8], ag[NV * 8], ab[NV * 8];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) ln_unpack8(gamma[lane + 32 * k], gm + 8 * k);
+#pragma unroll
+  for (int j = 0; j < NV * 8; ++j) ag[j] = ab[j] = 0.f;
+  for (int64_t r = warp0; r < rows; r += (int64_t)gridDim.x * kWarps) {
+    const uint4* xr = x + r * (C / 8);
+    const uint4* gr = dy + r * (C / 8);
+    const float m = mean[r], rs = rstd[r];
+    float xh[NV * 8], g[NV * 8];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      ln_unpack8(xr[lane + 32 * k], xh + 8 * k);
+      ln_unpack8(gr[lane + 32 * k], g + 8 * k);
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV * 8; ++j) {
+      const float d = g[j];
+      xh[j] = (xh[j] - m) * rs;
+      ag[j] += d * xh[j];
+      ab[j] += d;
+      g[j] = d * gm[j];
+      s1 += g[j];
+      s2 += g[j] * xh[j];
+    }
+    s1 = warp_sum(s1) / (float)C;
+    s2 = warp_sum(s2) / (float)C;
+    uint4* dr = dx + r * (C / 8);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (g[8 * k + j] - s1 - xh[8 * k + j] * s2);
+      dr[lane + 32 * k] = ln_pack8(o);
+    }
+  }
+  // warps add their sums one after the other (fixed order); column of element j of vector k: (lane + 32k)*8 + j
+  for (int w = 0; w < kWarps; ++w) {
+    if ((threadIdx.x >> 5) == w) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int c = (lane + 32 * k) * 8 + j;
+          sh[c] += ag[8 * k + j];
+          sh[C + c] += ab[8 * k + j];
+        }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < 2 * C; i += kThreads) partial[(int64_t)blockIdx.x * 2 * C + i] = sh[i];
+}
+
 // second level: one block (32 x 8) per 32 columns
 __global__ void __launch_bounds__(256)
 layernorm_param_grad_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ dgamma,
@@ -209,10 +330,16 @@ gelu_bwd_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy
   }
 }
 
+// about four rows per warp (the per-block tail of the backward - partial sums of 2*C floats - must stay small
+// next to the rows), at most two blocks per SM
 int ln_blocks(int64_t rows) {
-  int64_t blocks = (rows + kWarps - 1) / kWarps;
-  int64_t cap = (int64_t)pd_num_sms() * 4;
+  int64_t blocks = (rows + kWarps * 4 - 1) / (kWarps * 4);
+  int64_t cap = (int64_t)pd_num_sms() * 2;
   return (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+bool ln_vec(int dtype, int C, const void* a, const void* b, const void* c, const void* d) {
+  return dtype == PD_BF16 && C % 256 == 0 && C <= 1024 &&
+         ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)d)) & 15) == 0;
 }
 int flat_grid(int64_t n) {
   int64_t blocks = (n + kThreads - 1) / kThreads;
@@ -240,8 +367,15 @@ PD_EXPORT int pd_layernorm_fwd(int dtype, const void* x, int64_t rows, int C, co
   PD_REQUIRE(x && gamma && beta && y && mean && rstd && rows > 0 && C > 0, "pd_layernorm_fwd: bad arguments");
   PD_REQUIRE(C <= 32 * kMaxPerLane, "pd_layernorm_fwd: at most %d columns", 32 * kMaxPerLane);
   cudaStream_t s = (cudaStream_t)stream;
-  PD_LN_T(dtype, layernorm_fwd_kernel<T><<<ln_blocks(rows), kThreads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, rows, C,
-                                                                              eps, (T*)y, mean, rstd);)
+  if (ln_vec(dtype, C, x, gamma, beta, y)) {
+    const int nb = ln_blocks(rows);
+#define PD_LN_FWD(NV) layernorm_fwd_v8_kernel<NV><<<nb, kThreads, 0, s>>>((const uint4*)x, (const uint4*)gamma, (const uint4*)beta, rows, eps, (uint4*)y, mean, rstd)
+    switch (C / 256) { case 1: PD_LN_FWD(1); break; case 2: PD_LN_FWD(2); break; case 3: PD_LN_FWD(3); break; default: PD_LN_FWD(4); break; }
+#undef PD_LN_FWD
+  } else {
+    PD_LN_T(dtype, layernorm_fwd_kernel<T><<<ln_blocks(rows), kThreads, 0, s>>>((const T*)x, (const T*)gamma, (const T*)beta, rows, C,
+                                                                                eps, (T*)y, mean, rstd);)
+  }
   PD_LAUNCH_CHECK("layernorm_fwd_kernel");
   return PD_OK;
 }
@@ -259,8 +393,14 @@ PD_EXPORT int pd_layernorm_bwd(int dtype, const void* x, const void* dy, const v
   cudaStream_t s = (cudaStream_t)stream;
   const int nb = ln_blocks(rows);
   const size_t smem = (size_t)2 * C * sizeof(float);
-  PD_LN_T(dtype, layernorm_bwd_kernel<T><<<nb, kThreads, smem, s>>>((const T*)x, (const T*)dy, (const T*)gamma, mean, rstd, rows, C,
-                                                                    (T*)dx, (float*)workspace);)
+  if (ln_vec(dtype, C, x, dy, gamma, dx)) {
+#define PD_LN_BWD(NV) layernorm_bwd_v8_kernel<NV><<<nb, kThreads, smem, s>>>((const uint4*)x, (const uint4*)dy, (const uint4*)gamma, mean, rstd, rows, (uint4*)dx, (float*)workspace)
+    switch (C / 256) { case 1: PD_LN_BWD(1); break; case 2: PD_LN_BWD(2); break; case 3: PD_LN_BWD(3); break; default: PD_LN_BWD(4); break; }
+#undef PD_LN_BWD
+  } else {
+    PD_LN_T(dtype, layernorm_bwd_kernel<T><<<nb, kThreads, smem, s>>>((const T*)x, (const T*)dy, (const T*)gamma, mean, rstd, rows, C,
+                                                                      (T*)dx, (float*)workspace);)
+  }
   PD_LAUNCH_CHECK("layernorm_bwd_kernel");
   layernorm_param_grad_kernel<<<(C + 31) / 32, dim3(32, 8), 0, s>>>((const float*)workspace, nb, C, dgamma, dbeta, accumulate);
   PD_LAUNCH_CHECK("layernorm_param_grad_kernel");
