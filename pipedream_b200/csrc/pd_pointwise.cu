@@ -478,6 +478,35 @@ relu_bwd_colsum_bf16x8_kernel(const uint4* __restrict__ dy, const uint4* __restr
   }
 }
 
+// The same for wide matrices (C8 > kThreads): blockIdx.y picks a chunk of kThreads 16-byte columns, blockIdx.x strides
+// over the rows; a thread keeps the sums of its 8 columns in registers and writes them straight to partial[x][C].
+__global__ void __launch_bounds__(kThreads)
+relu_bwd_colsum_wide_bf16x8_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ y, uint4* __restrict__ dx,
+                                   int64_t rows, int C8, float* __restrict__ partial) {
+  const int cv = blockIdx.y * kThreads + threadIdx.x;
+  if (cv >= C8) return;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t i = r * C8 + cv;
+    float g[8];
+    unpack8(dy[i], g);
+    if (y != nullptr) {
+      float yv[8];
+      unpack8(y[i], yv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (!(yv[k] > 0.f)) g[k] = 0.f;
+    }
+    if (dx != nullptr) dx[i] = pack8(g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] += g[k];
+  }
+  float4* o = reinterpret_cast<float4*>(partial + (int64_t)blockIdx.x * C8 * 8 + (int64_t)cv * 8);
+  o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
 // out[c] (+)= sum_b partial[b][c]; 32 columns per block, 8 row lanes per column.
 __global__ void __launch_bounds__(256)
 colsum_final_fast_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ out,
@@ -657,6 +686,18 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
         (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
     PD_LAUNCH_CHECK("relu_bwd_colsum_bf16x8_kernel");
     colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
+    PD_LAUNCH_CHECK("colsum_final_fast_kernel");
+    return PD_OK;
+  }
+  if (dtype == PD_BF16 && (C % 8) == 0 && C / 8 > kThreads && ((uintptr_t)dy % 16) == 0 &&
+      (y == nullptr || ((uintptr_t)y % 16) == 0) && (dx == nullptr || ((uintptr_t)dx % 16) == 0)) {
+    const int C8 = C / 8, chunks = (C8 + kThreads - 1) / kThreads;
+    int gx = grid_cap(rows, 4) / chunks;
+    if (gx < 1) gx = 1;
+    relu_bwd_colsum_wide_bf16x8_kernel<<<dim3((unsigned)gx, (unsigned)chunks), kThreads, 0, s>>>(
+        (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
+    PD_LAUNCH_CHECK("relu_bwd_colsum_wide_bf16x8_kernel");
+    colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, gx, C, colsum, accumulate);
     PD_LAUNCH_CHECK("colsum_final_fast_kernel");
     return PD_OK;
   }

@@ -95,7 +95,7 @@ def test_relu_pool(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("C", [64, 96, 512, 1000])
+@pytest.mark.parametrize("C", [64, 96, 512, 1000, 3072, 4104])
 def test_relu_bwd_colsum(dtype, C):
     rows = 777
     dy = rnd(rows, C, dtype=dtype, seed=6)
