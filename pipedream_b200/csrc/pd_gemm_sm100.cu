@@ -617,7 +617,7 @@ int pd_gemm_error_word(int** out) {
   return PD_OK;
 }
 
-// Widest N tile that still leaves about one tile per SM; K-major B allows 32-wide tiles, which is what
+// Widest N tile that still fills at least half of the SMs; K-major B allows 32-wide tiles, which is what
 // keeps a skinny Linear layer (M = batch <= 128) from running on a handful of SMs.
 int pd_gemm_pick_block_n(int M, int N, int b_major, int zs) {
   const int sms = pd_num_sms();
@@ -625,7 +625,9 @@ int pd_gemm_pick_block_n(int M, int N, int b_major, int zs) {
   const int min_bn = b_major ? 64 : 32;
   int bn = N > 128 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
   if (bn < min_bn) bn = min_bn;
-  while (bn > min_bn && (long long)m_tiles * ((N + bn - 1) / bn) * zs < sms) bn >>= 1;
+  // halve only while that at least doubles the busy SMs within one wave: a narrower tile needs more operand
+  // rows per FLOP (the TMA row rate bounds short-K tiles), so two thin waves lose against one fat partial wave
+  while (bn > min_bn && 2ll * m_tiles * ((N + bn - 1) / bn) * zs <= sms) bn >>= 1;
   return bn;
 }
 
