@@ -238,12 +238,15 @@ def run_multi(gpus, steps, warmup):
     # the untimed head of the phase (>= 6 minibatches) covers every batch shape of the pool (allocator growth)
     dev = CyclingPairs(BATCH, "cuda", seed=4321 + 1000 * rank) if first else None
     _lib.count_calls(True)
-    ms = run_phase(r, opt, dev, steps, max(warmup, 6), False)
+    # with R replicas per stage every rank's minibatch count must be a multiple of R (round-robin routing)
+    reps = len(s2r[0])
+    even = lambda w: w + (-(steps + w)) % reps
+    ms = run_phase(r, opt, dev, steps, even(max(warmup, 6)), False)
     launches = _lib.launches_counted()
     _lib.count_calls(False)
     clocks = sampler.stop() if sampler else None
     host = CyclingPairs(BATCH, "pinned", seed=4321 + 1000 * rank) if first else None
-    ms_e2e = run_phase(r, opt, host, steps, 3, True)
+    ms_e2e = run_phase(r, opt, host, steps, even(3), True)
     if pf.gemm_poll_error() != 0:
         raise RuntimeError("a tcgen05 kernel reported a bounded wait that ran out")
     t = torch.tensor([ms, ms_e2e, float(launches)], dtype=torch.float64, device="cuda")
