@@ -253,6 +253,12 @@ int pd_attn_bahdanau_bwd(int dtype, const void* pq, const void* pk, const void* 
 /* Reads and clears the error word the tcgen05 kernels set when a bounded wait runs out
  * (0 = none).  `code` is a HOST pointer; synchronises the device.                            */
 int pd_gemm_poll_error(int* code);
+/* Tiling switch of the bf16 contraction back end.  mode 1 (default): problems whose output is at least
+ * 256 x 256 with N a multiple of 256 (the 256- and 512-channel convolutions of vgg16/gpus=8/stage0.py:16-31
+ * in all three passes) run on pairs of CTAs - a cluster of two SMs sharing one 256 x 256 tile through
+ * tcgen05.mma.cta_group::2; mode 0: every problem runs on single CTAs (128-row tiles).  Both tilings add the
+ * same products in the same order.  Process-wide; meant for checking one tiling against the other.          */
+int pd_gemm_set_pair_mode(int mode);
 
 /* ---- peer channels --------------------------------------------------------------------
  * One-directional FIFO between two pipeline-adjacent GPUs; replaces the helper threads and the

@@ -41,6 +41,8 @@ struct PdGemm {
 };
 
 int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream);
+// True when the tcgen05 back end runs this problem on CTA pairs (256 x 256 tiles) rather than single CTAs.
+bool pd_gemm_use_pair(int M, int N, int num_z, int z_group, int split_k);
 // 128-byte-swizzle bf16 tensor map of a row-major [rows, cols] matrix (leading dim ld elements), cached per host
 // thread; box = box_cols x box_rows elements (box_cols * 2 bytes <= 128).
 int pd_gemm_error_word(int** out);

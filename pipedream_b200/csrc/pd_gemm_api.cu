@@ -39,14 +39,34 @@ int prepare_grad_out(PdGemm& g, int accumulate, int64_t rows, int64_t row_elems,
   return PD_OK;
 }
 
-int auto_split(int64_t tiles, int kblocks) {
-  // aim for about two waves of CTAs over the SMs
-  int sms = pd_num_sms();
-  int64_t want = (2ll * sms + tiles - 1) / tiles;
-  if (want < 1) want = 1;
-  if (want > kblocks) want = kblocks;
-  if (want > 512) want = 512;
-  return (int)want;
+// Number of K slices for a weight-gradient contraction of `tiles` output tiles and `kblocks` 64-deep K blocks
+// on `units` workers (SMs, or SM pairs): the slice count that minimises waves x (K blocks per slice + the cost of
+// one atomic epilogue, about six K blocks' worth).
+int auto_split(int64_t tiles, int kblocks, int units) {
+  if (units < 1) units = 1;
+  int best = 1;
+  double best_cost = 1e30;
+  const int smax = kblocks < 256 ? kblocks : 256;
+  for (int s = 1; s <= smax; ++s) {
+    const int per = (kblocks + s - 1) / s;
+    const int used = (kblocks + per - 1) / per;          // slices that actually get K blocks
+    const int64_t waves = (tiles * used + units - 1) / units;
+    const double cost = (double)waves * (per + (used > 1 ? 6.0 : 2.0));
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = used; }
+  }
+  return best;
+}
+
+// Split for a weight gradient with output [M, N] per z: sized for CTA pairs when the problem qualifies for them.
+int grad_split(int dtype, int M, int N, int num_z, int z_per_cta, int bm, int bn, int kblocks) {
+  const int sms = pd_num_sms();
+  if (dtype == PD_BF16 && pd_gemm_use_pair(M, N, num_z, z_per_cta, 1 << 20)) {
+    const int64_t ptiles = (int64_t)((M + 255) / 256) * (N / 256) * num_z;
+    const int sp = auto_split(ptiles, kblocks, sms / 2);
+    if (pd_gemm_use_pair(M, N, num_z, z_per_cta, sp)) return sp;
+  }
+  const int64_t tiles = (int64_t)((num_z + z_per_cta - 1) / z_per_cta) * ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+  return auto_split(tiles, kblocks, sms);
 }
 
 }  // namespace
@@ -96,8 +116,7 @@ PD_EXPORT int pd_gemm_tn(int dtype, const void* a, int64_t lda, const void* b, i
   g.out = out; g.out_dtype = PD_F32; g.ldo = ldo;
   const int bn = dtype == PD_BF16 ? (N > 128 ? 256 : (N > 64 ? 128 : 64)) : 64;
   const int bm = dtype == PD_BF16 ? 128 : 64;
-  const int64_t tiles = (int64_t)((M + bm - 1) / bm) * ((N + bn - 1) / bn);
-  g.split_k = split_k > 0 ? split_k : auto_split(tiles, (K + 63) / 64);
+  g.split_k = split_k > 0 ? split_k : grad_split(dtype, M, N, 1, 1, bm, bn, (K + 63) / 64);
   int rc = prepare_grad_out(g, accumulate, M, N, (cudaStream_t)stream);
   if (rc != PD_OK) return rc;
   return dispatch(g, (cudaStream_t)stream);
@@ -179,8 +198,7 @@ PD_EXPORT int pd_conv2d_wgrad(int dtype, const void* x_pad, const void* dy_pad, 
   const int bm = dtype == PD_BF16 ? 128 : 64;
   // bf16: up to 256 accumulator columns per CTA, i.e. several taps share one CTA (z groups)
   const int per_cta = dtype == PD_BF16 ? (256 / bn < 4 ? (256 / bn < 1 ? 1 : 256 / bn) : 4) : 1;
-  const int64_t tiles = (int64_t)((9 + per_cta - 1) / per_cta) * ((Cout + bm - 1) / bm) * ((Cin + bn - 1) / bn);
-  g.split_k = split_k > 0 ? split_k : auto_split(tiles, (int)((P + 63) / 64));
+  g.split_k = split_k > 0 ? split_k : grad_split(dtype, Cout, Cin, 9, per_cta, bm, bn, (int)((P + 63) / 64));
   int rc = prepare_grad_out(g, accumulate, Cout, 9ll * Cin, (cudaStream_t)stream);
   if (rc != PD_OK) return rc;
   return dispatch(g, (cudaStream_t)stream);

@@ -17,6 +17,11 @@
 // bound by shared-memory fill bandwidth rather than by the tensor pipe, three boxes of 136 rows, each read by
 // the three taps of one filter row through descriptors that start 0, 1 or 2 rows into the box.
 //
+// Wide problems (output tile 256 x 256) run the same roles on a pair of CTAs (cluster of two, cta_group::2): a
+// tcgen05.mma costs about 150 cycles to issue whatever its shape, so only N = 256 instructions can keep the
+// tensor pipe busy, and the pair halves the operand bytes each SM has to pull in per FLOP (each CTA loads its
+// own 128 rows of A and its half of B; the even CTA issues the MMAs for both and signals the barriers of both).
+//
 // Every mbarrier wait is bounded: when the bound is hit the role records a code
 // in an error word, stops, and the CTA still frees its tensor memory.
 #include "pd_gemm.cuh"
@@ -40,6 +45,7 @@ constexpr uint32_t kA3Bytes = kBox3Rows * kBlockK * 2; // 17 KiB (a multiple of 
 
 struct KParams {
   int M, N, block_n, m_tiles, n_tiles;
+  int cta_n;                  // B rows (columns of the output tile) one CTA loads: block_n, or half of it for a CTA pair
   int num_taps, kb_per_tap, kb_per_split, split_k, num_z;   // num_z = number of z groups
   int acc_count, num_z_total;                                // accumulators per tile, outputs in all
   int a_major, b_major;
@@ -192,6 +198,17 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t*
   }
 }
 
+template <int CG>
+__device__ __forceinline__ void umma_cg(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  if constexpr (CG == 1) umma_bf16(tmem_d, da, db, idesc, acc);
+  else umma_bf16_pair(tmem_d, da, db, idesc, acc);
+}
+template <int CG>
+__device__ __forceinline__ void commit_cg(uint32_t bar) {
+  if constexpr (CG == 1) umma_commit(bar);
+  else umma_commit_pair(bar);
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -200,6 +217,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // buffers, so the epilogues of earlier tiles (two warp sets, alternate tiles) run under the MMAs of the
 // next ones - short-K tiles are bound by the epilogue's latency chain otherwise; the shared-memory stage
 // ring runs on across tile boundaries.
+//
+// CG = 2: the CTAs of a cluster of two share one 256-row tile.  Rank 0 ("leader") owns the barriers the MMA
+// issuer waits on: both producers' TMA loads complete on the leader's full barrier, both CTAs' epilogue warps
+// arrive on the leader's tmem_empty barrier; the leader's commits arrive on the empty / tmem_full barriers of
+// both CTAs.
+template <int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const KParams p) {
@@ -213,7 +236,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t b_bytes = (uint32_t)p.block_n * kBlockK * 2;
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;   // position in the CTA pair
+  const bool leader = rank == 0u;
+  const int unit = (int)blockIdx.x / CG;                    // CTA (CG = 1) or pair (CG = 2) index
+  const int num_units = (int)gridDim.x / CG;
+  const uint32_t b_bytes = (uint32_t)p.cta_n * kBlockK * 2;
   const uint32_t stage_bytes = p.tap3 ? kA3Bytes + 3u * b_bytes : kABytes + (uint32_t)p.acc_count * b_bytes;
   const int S = p.num_stages;
   const uint32_t acc_cols = (uint32_t)(p.acc_count * p.block_n);   // TMEM columns of one buffer
@@ -232,18 +259,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
     for (int b = 0; b < kMaxAccBufs; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[b]), 4);     // one arrival per epilogue warp
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 4 * CG);     // one arrival per epilogue warp (of both CTAs of a pair)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_holder)), "r"(tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CG == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(&tmem_base_holder)), "r"(tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(&tmem_base_holder)), "r"(tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();     // the peer's barriers exist before anything is signalled on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_holder;
 
@@ -251,8 +285,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #define PD_DECODE_TILE(tile)                                                   \
   const int zs_ = (tile) / tiles_mn;                                           \
   const int rem_ = (tile) - zs_ * tiles_mn;                                    \
-  const int m0 = (rem_ / p.n_tiles) * kBlockM;                                 \
+  const int m0 = (rem_ / p.n_tiles) * (kBlockM * CG) + (int)rank * kBlockM;    \
   const int n0 = (rem_ % p.n_tiles) * p.block_n;                               \
+  const int n0l = n0 + (int)rank * p.cta_n;  /* first B row this CTA loads */  \
   const int z = zs_ / p.split_k;                                               \
   const int kb_begin = (zs_ % p.split_k) * p.kb_per_split;                     \
   const int kb_end_ = min(kb_begin + p.kb_per_split, p.kb_per_tap);            \
@@ -268,7 +303,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // Two boxes per stage (both operands K-major): one lane issues both, nothing to coordinate.
     if (p.tap3) {
       // lane 0: the shared A box; lanes 1..: the B boxes of the triple's three taps
-      const int b_boxes = p.b_major ? p.block_n / 64 : 1;
+      const int b_boxes = p.b_major ? p.cta_n / 64 : 1;
       const bool is_a = lane == 0;
       const int bl = lane - 1;
       const int s3 = is_a ? 0 : min(bl / b_boxes, 2);
@@ -276,9 +311,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const bool has_box = is_a || bl < 3 * b_boxes;
       uint32_t g = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
         PD_DECODE_TILE(tile)
-        (void)iters; (void)accn; (void)acc0; (void)z;
+        (void)iters; (void)accn; (void)acc0; (void)z; (void)n0;
         for (int r = 0; r < 3 && ok; ++r) {
           int x0, y0, xk, yk;
           uint32_t dst_off, bytes;
@@ -289,11 +324,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           } else {
             const int t = 3 * r + s3;
             if (p.b_major) {
-              x0 = p.b_col0 + p.b_tap_col[t] + n0 + j * 64; y0 = p.b_row0 + p.b_tap_row[t]; xk = 0; yk = kBlockK;
+              x0 = p.b_col0 + p.b_tap_col[t] + n0l + j * 64; y0 = p.b_row0 + p.b_tap_row[t]; xk = 0; yk = kBlockK;
               dst_off = kA3Bytes + (uint32_t)s3 * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
-              issue = issue && x0 < p.b_cols;
+              if (CG == 1) issue = issue && x0 < p.b_cols;
             } else {
-              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0 + p.b_tap_row[t]; xk = kBlockK; yk = 0;
+              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0l + p.b_tap_row[t]; xk = kBlockK; yk = 0;
               dst_off = kA3Bytes + (uint32_t)s3 * b_bytes; bytes = b_bytes;
             }
           }
@@ -308,10 +343,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) break;
             const uint32_t fb = smem_u32(&full_bar[s]);
-            if (lane == 0) mbar_expect_tx(fb, tx);
+            if (lane == 0 && leader) mbar_expect_tx(fb, tx * CG);    // the peer's boxes land on the same barrier
             __syncwarp();
-            if (issue)
-              tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+            if (issue) {
+              if constexpr (CG == 1)
+                tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+              else
+                tma_load_2d_pair(smem0 + (uint32_t)s * stage_bytes + dst_off, map, mapa_shared(fb, 0), x0 + kb * xk,
+                                 y0 + kb * yk);
+            }
           }
         }
       }
@@ -319,22 +359,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (lane == 0) {
         uint32_t g = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
           PD_DECODE_TILE(tile)
-          (void)iters; (void)accn;
+          (void)iters; (void)accn; (void)n0;
           const int zrow = p.z_b_row[min(acc0, PD_MAX_TAPS - 1)];
           for (int t = 0; t < p.num_taps && ok; ++t) {
             const int ax = p.a_col0 + p.a_tap_col[t], ay = p.a_row0 + m0 + p.a_tap_row[t];
-            const int bx = p.b_col0 + p.b_tap_col[t], by = p.b_row0 + n0 + p.b_tap_row[t] + zrow;
+            const int bx = p.b_col0 + p.b_tap_col[t], by = p.b_row0 + n0l + p.b_tap_row[t] + zrow;
             for (int kb = kb_begin; kb < kb_begin + kbn; ++kb, ++g) {
               const int s = (int)(g % (uint32_t)S);
               const uint32_t ph = (g / (uint32_t)S) & 1u;
               if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) { ok = false; break; }
               const uint32_t fb = smem_u32(&full_bar[s]);
               const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
-              mbar_expect_tx(fb, kABytes + b_bytes);
-              tma_load_2d(sa, &tma_a, fb, ax + kb * kBlockK, ay);
-              tma_load_2d(sa + kABytes, &tma_b, fb, bx + kb * kBlockK, by);
+              if (leader) mbar_expect_tx(fb, (kABytes + b_bytes) * CG);
+              if constexpr (CG == 1) {
+                tma_load_2d(sa, &tma_a, fb, ax + kb * kBlockK, ay);
+                tma_load_2d(sa + kABytes, &tma_b, fb, bx + kb * kBlockK, by);
+              } else {
+                const uint32_t fbc = mapa_shared(fb, 0);
+                tma_load_2d_pair(sa, &tma_a, fbc, ax + kb * kBlockK, ay);
+                tma_load_2d_pair(sa + kABytes, &tma_b, fbc, bx + kb * kBlockK, by);
+              }
             }
           }
         }
@@ -342,16 +388,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     } else
     {
       const int a_boxes = p.a_major ? 2 : 1;
-      const int b_boxes = p.b_major ? p.block_n / 64 : 1;
+      const int b_boxes = p.b_major ? p.cta_n / 64 : 1;
       const bool is_a = lane < a_boxes;
       const int bl = lane - a_boxes;                         // B lanes: accumulator-major
       const int acc = is_a ? 0 : bl / b_boxes;               // which accumulator's B tile
       const int j = is_a ? lane : bl % b_boxes;              // box index within its operand tile
       uint32_t g = 0;                       // stage uses so far (ring position across tiles)
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
         PD_DECODE_TILE(tile)
-        (void)iters;
+        (void)iters; (void)n0;
         const bool has_box = is_a || acc < accn;
         const int zrow = p.z_b_row[min(acc0 + acc, PD_MAX_TAPS - 1)];
         for (int t = 0; t < p.num_taps && ok; ++t) {
@@ -363,18 +409,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (p.a_major) {
               x0 = p.a_col0 + p.a_tap_col[t] + m0 + j * 64; y0 = p.a_row0 + p.a_tap_row[t]; xk = 0; yk = kBlockK;
               dst_off = (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
-              issue = issue && x0 < p.a_cols;
+              if (CG == 1) issue = issue && x0 < p.a_cols;
             } else {
               x0 = p.a_col0 + p.a_tap_col[t]; y0 = p.a_row0 + m0 + p.a_tap_row[t]; xk = kBlockK; yk = 0;
               dst_off = 0; bytes = kABytes;
             }
           } else {
             if (p.b_major) {
-              x0 = p.b_col0 + p.b_tap_col[t] + n0 + j * 64; y0 = p.b_row0 + p.b_tap_row[t] + zrow; xk = 0; yk = kBlockK;
+              x0 = p.b_col0 + p.b_tap_col[t] + n0l + j * 64; y0 = p.b_row0 + p.b_tap_row[t] + zrow; xk = 0; yk = kBlockK;
               dst_off = kABytes + (uint32_t)acc * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
-              issue = issue && x0 < p.b_cols;
+              if (CG == 1) issue = issue && x0 < p.b_cols;
             } else {
-              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0 + p.b_tap_row[t] + zrow; xk = kBlockK; yk = 0;
+              x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0l + p.b_tap_row[t] + zrow; xk = kBlockK; yk = 0;
               dst_off = kABytes + (uint32_t)acc * b_bytes; bytes = b_bytes;
             }
           }
@@ -390,25 +436,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) break;
             const uint32_t fb = smem_u32(&full_bar[s]);
-            if (lane == 0) mbar_expect_tx(fb, tx);
+            if (lane == 0 && leader) mbar_expect_tx(fb, tx * CG);    // the peer's boxes land on the same barrier
             __syncwarp();
-            if (issue)
-              tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+            if (issue) {
+              if constexpr (CG == 1)
+                tma_load_2d(smem0 + (uint32_t)s * stage_bytes + dst_off, map, fb, x0 + kb * xk, y0 + kb * yk);
+              else
+                tma_load_2d_pair(smem0 + (uint32_t)s * stage_bytes + dst_off, map, mapa_shared(fb, 0), x0 + kb * xk,
+                                 y0 + kb * yk);
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       const uint32_t adv_a = p.a_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
       const uint32_t adv_b = p.b_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
       uint32_t g = 0;
       uint32_t local = 0;                   // tiles done by this CTA
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
         PD_DECODE_TILE(tile)
-        (void)m0; (void)n0; (void)kb_begin; (void)acc0;
+        (void)m0; (void)n0; (void)n0l; (void)kb_begin; (void)acc0;
         if (iters == 0) continue;             // (cannot happen: the host never creates empty splits)
         const uint32_t buf = local % nbuf;
         const uint32_t use = local / nbuf;
@@ -432,10 +483,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               const uint64_t db3 = make_desc(sa + kA3Bytes + (uint32_t)s3 * b_bytes, p.b_major);
 #pragma unroll
               for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-                umma_bf16(tmem_d, da3 + (uint64_t)(kk * adv_a), db3 + (uint64_t)(kk * adv_b), p.idesc,
+                umma_cg<CG>(tmem_d, da3 + (uint64_t)(kk * adv_a), db3 + (uint64_t)(kk * adv_b), p.idesc,
                           (uint32_t)((it | s3 | kk) != 0));
             }
-            umma_commit(smem_u32(&empty_bar[s]));
+            commit_cg<CG>(smem_u32(&empty_bar[s]));
             continue;
           }
           const uint64_t da = make_desc(sa, p.a_major);
@@ -447,21 +498,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint32_t idesc_n = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((accn * p.block_n) >> 3) << 17);
 #pragma unroll
             for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-              umma_bf16(tmem_d, da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b), idesc_n,
+              umma_cg<CG>(tmem_d, da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b), idesc_n,
                         (uint32_t)((it | kk) != 0));
-            umma_commit(smem_u32(&empty_bar[s]));
+            commit_cg<CG>(smem_u32(&empty_bar[s]));
             continue;
           }
           for (int a = 0; a < accn; ++a) {
             const uint64_t db = make_desc(sa + kABytes + (uint32_t)a * b_bytes, p.b_major);
 #pragma unroll
             for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-              umma_bf16(tmem_d + (uint32_t)(a * p.block_n), da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b),
+              umma_cg<CG>(tmem_d + (uint32_t)(a * p.block_n), da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b),
                         p.idesc, (uint32_t)((it | kk) != 0));
           }
-          umma_commit(smem_u32(&empty_bar[s]));
+          commit_cg<CG>(smem_u32(&empty_bar[s]));
         }
-        if (ok) umma_commit(smem_u32(&tmem_full_bar[buf]));
+        if (ok) commit_cg<CG>(smem_u32(&tmem_full_bar[buf]));
         ++local;
       }
     }
@@ -471,9 +522,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t set = (uint32_t)(warp - 2) >> 2;   // which of the two epilogue sets
     uint32_t local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
       PD_DECODE_TILE(tile)
-      (void)kb_begin;
+      (void)kb_begin; (void)n0l;
       if (iters == 0) continue;
       if ((local & 1u) != set) { ++local; continue; }
       const uint32_t buf = local % nbuf;
@@ -515,7 +566,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       // this warp has read everything it needs from the accumulator: hand it back to the MMA warp
       __syncwarp();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+      if (lane == 0) {
+        if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+        else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
+      }
       ++local;
     }
   }
@@ -523,9 +577,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  // a pair stays together until both are done: the leader's MMAs read the peer's shared memory and write its
+  // tensor memory, and the peer's last arrivals land on the leader's barriers
+  if constexpr (CG == 2) cluster_sync_all();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    if constexpr (CG == 1)
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
@@ -631,6 +691,29 @@ int pd_gemm_pick_block_n(int M, int N, int b_major, int zs) {
   return bn;
 }
 
+namespace {
+int g_pair_mode = 1;     // 1 = CTA pairs where they apply, 0 = single CTAs only (kept for A/B checks of the two tilings)
+}
+
+// A pair of CTAs (256 x 256 tile) is used when the output is at least 256 wide in both directions, the
+// problem has one accumulator per tile, and there are enough tiles to give every pair of SMs one.
+bool pd_gemm_use_pair(int M, int N, int num_z, int z_group, int split_k) {
+  if (!g_pair_mode) return false;
+  const int sms = pd_num_sms();
+  if (sms < 2 || (sms & 1)) return false;
+  if (N < 256 || (N % 256) != 0 || M < 256) return false;
+  (void)z_group;
+  const long long tiles = (long long)((M + 255) / 256) * (N / 256) * (num_z > 0 ? num_z : 1) * (split_k > 0 ? split_k : 1);
+  return tiles >= sms / 2;
+}
+
+// Chooses between the two tilings of wide problems: 1 (default) lets problems that qualify run on CTA pairs,
+// 0 keeps every problem on single CTAs.  Both produce the same sums in the same order.
+PD_EXPORT int pd_gemm_set_pair_mode(int mode) {
+  g_pair_mode = mode ? 1 : 0;
+  return PD_OK;
+}
+
 int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   PD_REQUIRE(g.dtype == PD_BF16, "tcgen05 gemm: operands must be bf16");
   PD_REQUIRE(g.M > 0 && g.N > 0 && g.K > 0, "tcgen05 gemm: empty problem");
@@ -645,13 +728,17 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
     PD_REQUIRE((g.a_tap_col[t] % 8) == 0 && (g.b_tap_col[t] % 8) == 0, "tcgen05 gemm: tap column offsets must be multiples of 8");
 
   int block_n = pd_gemm_pick_block_n(g.M, g.N, g.b_major, g.num_z * g.split_k);
-  // 3x3 convolutions: 128-wide tiles with the shared tap boxes are at least as fast as 256-wide ones (an MMA of
-  // N=128 costs half of an N=256 one, the activation box is fetched once per filter row instead of once per tap)
-  // and quantise better into waves of 148 CTAs (measured: +4..9 % on the 28x28 layers, none slower)
-  if (g.share_tap_rows && block_n > 128) block_n = 128;
+  const bool pair = pd_gemm_use_pair(g.M, g.N, g.num_z, g.z_group, g.split_k);
+  if (pair) block_n = 256;
+  // 3x3 convolutions on a single CTA: 128-wide tiles with the shared tap boxes beat 256-wide ones (the 256-wide
+  // tile cannot share the activation box - its stage would not fit - and is then bound by the rate at which
+  // one SM pulls operands out of L2) and quantise better into waves of 148 CTAs
+  if (g.share_tap_rows && block_n > 128 && !pair) block_n = 128;
+  const int cg = pair ? 2 : 1;
   KParams p;
   memset(&p, 0, sizeof(p));
   p.M = g.M; p.N = g.N; p.block_n = block_n;
+  p.cta_n = block_n / cg;
   p.num_taps = g.num_taps;
   p.kb_per_tap = (g.K + kBlockK - 1) / kBlockK;
   p.split_k = g.split_k;
@@ -681,10 +768,10 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   p.relu_aux = g.relu_aux; p.ld_aux = g.ld_aux;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.a_major ? 1 : 0) << 15) |
             ((uint32_t)(g.b_major ? 1 : 0) << 16) | ((uint32_t)(block_n >> 3) << 17) |
-            ((uint32_t)(kBlockM >> 4) << 24);
+            ((uint32_t)((kBlockM * cg) >> 4) << 24);
   // shared A boxes for the three taps of a filter row: narrow output tiles only (wide ones are bound by the
   // tensor pipe and want more, smaller stages)
-  bool tap3 = g.share_tap_rows && g.num_taps == 9 && !g.a_major && block_n <= 128 && g.num_z == 1 && p.split_k == 1 &&
+  bool tap3 = g.share_tap_rows && g.num_taps == 9 && !g.a_major && p.cta_n <= 128 && g.num_z == 1 && p.split_k == 1 &&
               p.acc_count == 1;
   for (int r = 0; r < 3 && tap3; ++r) {
     int base = g.a_tap_row[3 * r];
@@ -700,8 +787,8 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   }
   p.tap3 = tap3 ? 1 : 0;
   if (tap3) p.num_taps = 3;
-  const uint32_t stage_bytes = tap3 ? kA3Bytes + 3u * (uint32_t)block_n * kBlockK * 2
-                                    : kABytes + (uint32_t)p.acc_count * (uint32_t)block_n * kBlockK * 2;
+  const uint32_t stage_bytes = tap3 ? kA3Bytes + 3u * (uint32_t)p.cta_n * kBlockK * 2
+                                    : kABytes + (uint32_t)p.acc_count * (uint32_t)p.cta_n * kBlockK * 2;
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
@@ -718,7 +805,7 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   CUtensorMap ma, mb;
   int rc = pd_make_map_2d(&ma, g.a, g.a_rows, g.a_cols, g.lda, 64, g.a_major ? kBlockK : (tap3 ? kBox3Rows : kBlockM));
   if (rc != PD_OK) return rc;
-  rc = pd_make_map_2d(&mb, g.b, g.b_rows, g.b_cols, g.ldb, 64, g.b_major ? kBlockK : block_n);
+  rc = pd_make_map_2d(&mb, g.b, g.b_rows, g.b_cols, g.ldb, 64, g.b_major ? kBlockK : p.cta_n);
   if (rc != PD_OK) return rc;
 
   const size_t smem = (size_t)stages * stage_bytes + 1024;
@@ -727,17 +814,32 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
     PD_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lk(g_attr_mu);
     if (dev >= 0 && dev < 64 && !g_attr_set[dev]) {
-      PD_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+      PD_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
+      PD_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
       g_attr_set[dev] = true;
     }
   }
-  p.m_tiles = (g.M + kBlockM - 1) / kBlockM;
+  p.m_tiles = (g.M + kBlockM * cg - 1) / (kBlockM * cg);
   p.n_tiles = (g.N + block_n - 1) / block_n;
   const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.num_z * p.split_k;
   PD_REQUIRE(total_tiles < (1ll << 31), "tcgen05 gemm: too many tiles");
   const int sms = pd_num_sms();
-  dim3 grid((unsigned)(total_tiles < sms ? total_tiles : sms), 1, 1);
-  gemm_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(ma, mb, p);
+  if (!pair) {
+    dim3 grid((unsigned)(total_tiles < sms ? total_tiles : sms), 1, 1);
+    gemm_tcgen05_kernel<1><<<grid, kThreads, smem, stream>>>(ma, mb, p);
+  } else {
+    const long long pairs = sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (total_tiles < pairs ? total_tiles : pairs)), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    PD_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<2>, ma, mb, p));
+  }
   PD_LAUNCH_CHECK("gemm_tcgen05_kernel");
   return PD_OK;
 }
