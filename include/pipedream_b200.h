@@ -268,7 +268,11 @@ int pd_gemm_set_pair_mode(int mode);
  * CUDA IPC; a push is wait-for-free-slot, NVLink copy, publish, all enqueued on `stream`.
  * create/open/close are set-up calls (they allocate and synchronise); push and wait are not.
  * timeout_ms bounds every device-side wait; when it runs out the channel's status becomes -4
- * (read with pd_chan_status) and the kernels return, so a dead peer cannot hang the GPU.
+ * and the kernels return, so a dead peer cannot hang the GPU.  A receive whose byte count differs
+ * from the message's sets status -1.  A channel with a non-zero status is dead: queued waits return
+ * at once, no payload is copied into a slot that was not freed, nothing is published or released,
+ * and a receive zero-fills its destination.  pd_chan_status synchronises `stream` and returns the
+ * status; pd_chan_poll returns it from a pinned host mirror without touching any stream.
  * blob128: 128 bytes of HOST memory carried to the producer by any host transport.
  * pd_chan_open_local makes a producer end over the same memory inside one process (tests).
  * pd_chan_peek_header blocks the host until the next message is there; out8 (HOST) receives
@@ -282,6 +286,7 @@ int pd_chan_push(void* chan, const void* src, int64_t bytes, int ndim, const int
 int pd_chan_wait(void* chan, void* dst, int64_t bytes, void* stream);
 int pd_chan_peek_header(void* chan, int64_t* out8, void* stream);
 int pd_chan_status(void* chan, void* stream);
+int pd_chan_poll(void* chan);
 int pd_chan_close(void* chan);
 
 #ifdef __cplusplus

@@ -88,6 +88,7 @@ SIGNATURES = {
     "pd_chan_wait": (I, [P, P, L, P]),
     "pd_chan_peek_header": (I, [P, POINTER(c_int64), P]),
     "pd_chan_status": (I, [P, P]),
+    "pd_chan_poll": (I, [P]),
     "pd_chan_close": (I, [P]),
 }
 

@@ -12,9 +12,12 @@ each (tensor, peer, direction) FIFO:
   "p2p" / "nccl" : one process per GPU; the producer copies the payload over
                    NVLink into a ring slot in the consumer's HBM (CUDA IPC) on a
                    side stream and publishes a sequence flag (peer_channel.py)
-  "local"        : all stages in one process (1-GPU emulation of a pipeline and
-                   tests); tensors are handed over by reference
-  "gloo"         : host-logic tests on CPU ranks (torch.distributed isend/recv)
+  "local"        : every stage of a pipeline in one process on one GPU (a way to
+                   run a multi-stage configuration on a single device); tensors
+                   are handed over by reference
+
+Other names are refused unless a transport was registered for them with
+`register_transport` (the CPU tests of the host logic register one over gloo).
 """
 import collections
 import os
@@ -129,36 +132,14 @@ class _LocalTransport:
         pass
 
 
-class _GlooTransport:
-    """CPU ranks over torch.distributed: shape message then payload, like the reference wire
-    format (runtime/communication.py:664-678,704-712), but sends are asynchronous."""
+TRANSPORTS = {}      # backend name -> factory(handler, master_addr, master_port) returning a transport
 
-    def __init__(self, rank):
-        self.rank = rank
-        self.pending = []
 
-    @staticmethod
-    def _tag(tag, backward):
-        return 2 * tag + (1 if backward else 0)
-
-    def send(self, dst_rank, name, backward, tensor, tag):
-        t = tensor.detach().cpu().contiguous()
-        shape = torch.tensor(list(t.shape), dtype=torch.int)
-        self.pending.append((dist.isend(shape, dst=dst_rank, tag=self._tag(tag, backward)), shape))
-        self.pending.append((dist.isend(t, dst=dst_rank, tag=self._tag(tag, backward)), t))
-        self.pending = [(w, keep) for (w, keep) in self.pending if not w.is_completed()]
-
-    def recv(self, src_rank, name, backward, shape, dtype, tag):
-        got_shape = torch.zeros(len(shape), dtype=torch.int)
-        dist.recv(got_shape, src=src_rank, tag=self._tag(tag, backward))
-        t = torch.zeros([int(x) for x in got_shape], dtype=dtype)
-        dist.recv(t, src=src_rank, tag=self._tag(tag, backward))
-        return t
-
-    def wait(self):
-        for w, _ in self.pending:
-            w.wait()
-        self.pending = []
+def register_transport(name, factory):
+    """Adds a backend.  factory(handler, master_addr, master_port) is called from the handler's constructor and
+    returns an object with send(dst_rank, name, backward, tensor, tag), recv(src_rank, name, backward, shape,
+    dtype, tag) and wait(); `uses_process_groups` (default True) says whether torch.distributed groups exist."""
+    TRANSPORTS[name] = factory
 
 
 def _rendezvous_env(master_addr, master_port):
@@ -191,12 +172,6 @@ class CommunicationHandler(object):
         assert num_ranks_in_server > 0
         if backend == LOCAL:
             self.transport = _LocalTransport(rank)
-        elif backend == GLOO:
-            if not dist.is_initialized():
-                _rendezvous_env(master_addr, master_port)
-                dist.init_process_group(backend, rank=rank, world_size=world_size)
-            assert dist.get_world_size() == self.world_size
-            self.transport = _GlooTransport(rank)
         elif backend in (NCCL, P2P):
             from . import peer_channel
             if not dist.is_initialized():
@@ -205,8 +180,15 @@ class CommunicationHandler(object):
                                         device_id=torch.device("cuda", local_rank))
             assert dist.get_world_size() == self.world_size
             self.transport = peer_channel.PeerTransport(rank, world_size, local_rank)
+        elif backend in TRANSPORTS:
+            self.transport = TRANSPORTS[backend](self, master_addr, master_port)
         else:
-            raise ValueError("unknown distributed backend %r" % (backend,))
+            raise ValueError("distributed backend %r is not available: boundary tensors move over NVLink peer "
+                             "channels (\"p2p\" or \"nccl\") or inside one process (\"local\")" % (backend,))
+        self.gradient_tensor_names = None
+
+    def uses_process_groups(self):
+        return self.backend != LOCAL and getattr(self.transport, "uses_process_groups", True)
 
     def initialize(self, receive_ranks, send_ranks, tensor_tags, target_tensor_names,
                    training_tensor_dtypes, rank_in_stage, num_ranks_in_stage,
@@ -281,11 +263,17 @@ class CommunicationHandler(object):
 
     # ------------------------------------------------------------------ data path
     def _dtype(self, name):
+        """Element type of a boundary tensor on the wire.  The driver scripts record the dtypes from a dry run
+        of the fp32 CPU model (main_with_runtime.py:139-155), so with `fp16` every floating tensor is really
+        the 16-bit compute type - the reference makes the same substitution (runtime/communication.py:273)."""
         if name == "ack":
             return torch.int64
-        if name in self.training_tensor_dtypes:
-            return self.training_tensor_dtypes[name]
-        return torch.int64          # targets without a recorded dtype (runtime/communication.py:320)
+        dtype = self.training_tensor_dtypes.get(name)
+        if dtype is None:
+            return torch.int64          # targets without a recorded dtype (runtime/communication.py:320)
+        if self.fp16 and dtype.is_floating_point:
+            return torch.bfloat16
+        return dtype
 
     def recv(self, tensor_name, forward_minibatch_id, backward_minibatch_id, backward=False):
         if backward:
@@ -323,6 +311,8 @@ class CommunicationHandler(object):
     def backward_ready(self, backward_minibatch_id):
         for name, peers in self.send_ranks.items():
             if name in self.target_tensor_names or name == "ack":
+                continue
+            if self.gradient_tensor_names is not None and name not in self.gradient_tensor_names:
                 continue
             idx = backward_recv_index(backward_minibatch_id, self.rank_in_stage, len(peers))
             if not self.transport.ready(peers[idx], name, True):

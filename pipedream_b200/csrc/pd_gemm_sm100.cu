@@ -238,8 +238,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;   // position in the CTA pair
   const bool leader = rank == 0u;
-  const int unit = (int)blockIdx.x / CG;                    // CTA (CG = 1) or pair (CG = 2) index
-  const int num_units = (int)gridDim.x / CG;
+  // Each CTA (CG = 1) or pair (CG = 2) walks the tile list with a stride of the number of CTAs / pairs.  The loop is
+  // written on blockIdx / gridDim directly: routed through local copies the same loop compiled into a kernel whose
+  // MMA issue interval was a fifth longer (measured on every layer shape).
+#define PD_FIRST_TILE (CG == 1 ? blockIdx.x : (blockIdx.x >> 1))
+#define PD_TILE_STEP (CG == 1 ? gridDim.x : (gridDim.x >> 1))
   const uint32_t b_bytes = (uint32_t)p.cta_n * kBlockK * 2;
   const uint32_t stage_bytes = p.tap3 ? kA3Bytes + 3u * b_bytes : kABytes + (uint32_t)p.acc_count * b_bytes;
   const int S = p.num_stages;
@@ -288,8 +291,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int m0 = (rem_ / p.n_tiles) * (kBlockM * CG) + (int)rank * kBlockM;    \
   const int n0 = (rem_ % p.n_tiles) * p.block_n;                               \
   const int n0l = n0 + (int)rank * p.cta_n;  /* first B row this CTA loads */  \
-  const int z = zs_ / p.split_k;                                               \
-  const int kb_begin = (zs_ % p.split_k) * p.kb_per_split;                     \
+  /* z varies faster than the K slice: the z outputs of a weight gradient (filter taps) read the same      \
+     activation rows shifted by a pixel or a row, so running them side by side fetches those rows from   \
+     HBM once and serves the other taps from L2 */                                                         \
+  const int z = zs_ % p.num_z;                                                 \
+  const int kb_begin = (zs_ / p.num_z) * p.kb_per_split;                       \
   const int kb_end_ = min(kb_begin + p.kb_per_split, p.kb_per_tap);            \
   const int kbn = kb_end_ - kb_begin;                                          \
   const int iters = kbn > 0 ? kbn * p.num_taps : 0;                             \
@@ -311,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const bool has_box = is_a || bl < 3 * b_boxes;
       uint32_t g = 0;
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
+      for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
         PD_DECODE_TILE(tile)
         (void)iters; (void)accn; (void)acc0; (void)z; (void)n0;
         for (int r = 0; r < 3 && ok; ++r) {
@@ -359,7 +365,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (lane == 0) {
         uint32_t g = 0;
         bool ok = true;
-        for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
+        for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
           PD_DECODE_TILE(tile)
           (void)iters; (void)accn; (void)n0;
           const int zrow = p.z_b_row[min(acc0, PD_MAX_TAPS - 1)];
@@ -395,7 +401,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int j = is_a ? lane : bl % b_boxes;              // box index within its operand tile
       uint32_t g = 0;                       // stage uses so far (ring position across tiles)
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
+      for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
         PD_DECODE_TILE(tile)
         (void)iters; (void)n0;
         const bool has_box = is_a || acc < accn;
@@ -457,7 +463,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t g = 0;
       uint32_t local = 0;                   // tiles done by this CTA
       bool ok = true;
-      for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
+      for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
         PD_DECODE_TILE(tile)
         (void)m0; (void)n0; (void)n0l; (void)kb_begin; (void)acc0;
         if (iters == 0) continue;             // (cannot happen: the host never creates empty splits)
@@ -522,7 +528,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t set = (uint32_t)(warp - 2) >> 2;   // which of the two epilogue sets
     uint32_t local = 0;
     bool ok = true;
-    for (int tile = unit; tile < total_tiles && ok; tile += num_units) {
+    for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
       PD_DECODE_TILE(tile)
       (void)kb_begin; (void)n0l;
       if (iters == 0) continue;
@@ -574,6 +580,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   }
 #undef PD_DECODE_TILE
+#undef PD_FIRST_TILE
+#undef PD_TILE_STEP
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -668,6 +676,7 @@ int pd_gemm_error_word(int** out) {
   int dev_now = 0;
   PD_CUDA(cudaGetDevice(&dev_now));
   PD_REQUIRE(dev_now >= 0 && dev_now < 64, "tcgen05 gemm: device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_attr_mu);
   if (err_addr[dev_now] == nullptr) {
     int* e = nullptr;
     PD_CUDA(cudaGetSymbolAddress((void**)&e, g_gemm_error));

@@ -124,6 +124,11 @@ class OptimizerWithWeightStashing:
                 self._grad_sync = sync
         self._build_arena()
         self.initialize_queue()
+        for m in modules:
+            rt = getattr(m, "_pd_runtime", None)
+            rt = rt() if rt is not None else None
+            if rt is not None:
+                rt.attach_optimizer(self)      # StageRuntime.load_state_dict re-seeds the ring through this
 
     def __getattr__(self, key):
         """Relay unknown attributes to the torch optimizer (param_groups, state_dict, ...)."""
@@ -353,8 +358,50 @@ class OptimizerWithWeightStashing:
         self._steps_taken = steps
 
     def resync_from_modules(self):
-        """Re-seed every slot's current version (and the master copy) from the values the
-        parameters hold now, e.g. after StageRuntime.load_state_dict."""
-        for p, (off, _) in zip(self.master_parameters, self._offsets):
-            if self.master is not None:
+        """The parameters were overwritten in place (a checkpoint was loaded into the modules after this
+        optimizer took them into its arena): make every stashed version, and the fp32 master copy, equal to
+        the values the parameters hold now - the state the reference is in when the checkpoint is loaded before
+        the optimizer is built (all queue entries are clones of the loaded weights, runtime/optimizer.py:58-62).
+        Version numbers and optimizer state are left alone."""
+        cur = self._current_slot
+        for s in range(self.num_versions):
+            if s != cur:
+                self.arena[s].copy_(self.arena[cur])
+        self._valid_slots = set(range(self.num_versions))
+        if self.master is not None:
+            for p, (off, _) in zip(self.master_parameters, self._offsets):
                 self.master.as_strided(p.data.shape, p.data.stride(), off).copy_(p.data)
+
+    # ------------------------------------------------------------------ full-fidelity checkpoints
+    def ring_state_dict(self):
+        """Everything a bit-exact resume in the middle of a pipelined epoch needs beyond torch.optim's
+        state: every stashed weight version with its number, the fp32 master copy, and the step counters.
+        The reference checkpoints between epochs only, where all versions coincide
+        (main_with_runtime.py:322-330); this is the in-flight complement."""
+        return {
+            "num_versions": self.num_versions,
+            "latest_version": self.latest_version.version,
+            "current_version": self.current_version.version,
+            "batch_counter": self.batch_counter,
+            "steps_taken": self._steps_taken,
+            "arena": self.arena.detach().clone(),
+            "master": self.master.detach().clone() if self.master is not None else None,
+            "valid_slots": sorted(self._valid_slots),
+            "current_slot": self._current_slot,
+        }
+
+    def load_ring_state_dict(self, sd):
+        if sd["num_versions"] != self.num_versions or sd["arena"].shape != self.arena.shape:
+            raise ValueError("version ring of the checkpoint (%d versions, %s) does not match this stage (%d, %s)" % (
+                sd["num_versions"], tuple(sd["arena"].shape), self.num_versions, tuple(self.arena.shape)))
+        self.arena.copy_(sd["arena"])
+        if self.master is not None:
+            self.master.copy_(sd["master"])
+        self.latest_version = Version(sd["latest_version"])
+        self.current_version = Version(sd["current_version"])
+        self.batch_counter = sd["batch_counter"]
+        self._steps_taken = sd["steps_taken"]
+        self.ring = VersionRing(self.num_versions)
+        self.ring.latest = self.latest_version.version
+        self._valid_slots = set(sd["valid_slots"])
+        self._point_params(sd["current_slot"])

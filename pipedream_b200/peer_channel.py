@@ -105,6 +105,7 @@ class PeerTransport:
             from . import functional as pf
             pad = pf.padded_of(t)
             t = pf.unpack_pnhwc(pad) if pad is not None else t.contiguous()
+        self._poll(key, ch)
         cur = torch.cuda.current_stream(self.device)
         side = self._stream("send_bwd" if backward else "send_fwd")
         ev = torch.cuda.Event()
@@ -120,6 +121,7 @@ class PeerTransport:
         ch = self.consumers.get(key)
         if ch is None:
             raise _lib.PipedreamB200Error("no peer channel for %r (tensor shapes were not set?)" % (key,))
+        self._poll(key, ch)
         cur = torch.cuda.current_stream(self.device)
         side = self._stream("recv_bwd" if backward else "recv_fwd")
         if self.variable_shapes:
@@ -138,6 +140,12 @@ class PeerTransport:
         cur.wait_event(done)
         out.record_stream(side)
         return out
+
+    def _poll(self, key, ch):
+        """Raises as soon as an earlier operation on this channel has failed on the device (a wait that ran
+        out, a message of the wrong size).  Reads a pinned host word: no stream is synchronised."""
+        if _lib.load().pd_chan_poll(ch) != 0:
+            raise _lib.PipedreamB200Error("peer channel %r: %s" % (key, _lib.last_error()))
 
     def wait(self):
         """End of an epoch: drain the side streams and surface any wait that ran out."""

@@ -2,7 +2,78 @@
 (runtime/image_classification/main_with_runtime.py:129-229)."""
 import torch
 
+import torch.distributed as dist
+
 from pipedream_b200 import runtime, sgd, adam, stages, schedule, communication
+
+
+# --------------------------------------------------------------------------- #
+# test-only variants of the runtime: the product runs native modules on CUDA over peer channels
+# --------------------------------------------------------------------------- #
+class TorchModuleRuntime(runtime.StageRuntime):
+    """StageRuntime whose stage modules stay the user's torch.nn modules (cuDNN / cuBLAS or CPU kernels).
+    `device` chooses where they run.  Used as a same-GPU control and for the CPU tests of the host logic."""
+
+    device_override = None
+
+    def _pick_device(self, local_rank):
+        if self.device_override is not None:
+            return torch.device(self.device_override)
+        return torch.device("cuda", local_rank if local_rank is not None else 0)
+
+    def _adopt_module(self, module):
+        module = module.to(self.device)
+        return module.to(self.compute_dtype) if self.fp16 else module
+
+    def _input_convert(self):
+        if self.fp16:
+            return lambda x: x.to(self.compute_dtype)      # runtime/runtime.py:397-398
+        return None
+
+
+class CpuRuntime(TorchModuleRuntime):
+    device_override = "cpu"
+
+
+class GlooTransport:
+    """CPU ranks over torch.distributed: shape message then payload, like the reference's wire format
+    (runtime/communication.py:664-678,704-712), but sends are asynchronous."""
+
+    uses_process_groups = True
+
+    def __init__(self, handler, master_addr, master_port):
+        if not dist.is_initialized():
+            communication._rendezvous_env(master_addr, master_port)
+            dist.init_process_group("gloo", rank=handler.rank, world_size=handler.world_size)
+        self.rank = handler.rank
+        self.pending = []
+
+    @staticmethod
+    def _tag(tag, backward):
+        return 2 * tag + (1 if backward else 0)
+
+    def send(self, dst_rank, name, backward, tensor, tag):
+        t = tensor.detach().cpu().contiguous()
+        shape = torch.tensor(list(t.shape), dtype=torch.int)
+        self.pending.append((dist.isend(shape, dst=dst_rank, tag=self._tag(tag, backward)), shape))
+        self.pending.append((dist.isend(t, dst=dst_rank, tag=self._tag(tag, backward)), t))
+        self.pending = [(w, keep) for (w, keep) in self.pending if not w.is_completed()]
+
+    def recv(self, src_rank, name, backward, shape, dtype, tag):
+        got_shape = torch.zeros(len(shape), dtype=torch.int)
+        dist.recv(got_shape, src=src_rank, tag=self._tag(tag, backward))
+        t = torch.zeros([int(x) for x in got_shape], dtype=dtype)
+        dist.recv(t, src=src_rank, tag=self._tag(tag, backward))
+        return t
+
+    def wait(self):
+        for w, _ in self.pending:
+            w.wait()
+        self.pending = []
+
+
+def register_gloo():
+    communication.register_transport("gloo", GlooTransport)
 
 
 def tensor_shapes(model, batch):
@@ -38,14 +109,15 @@ def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, mome
     tshapes, dtypes = shapes
     if fp16:
         dtypes = {k: (torch.bfloat16 if v == torch.float32 else v) for k, v in dtypes.items()}
-    r = runtime.StageRuntime(
+    cls = runtime.StageRuntime if native else TorchModuleRuntime
+    r = cls(
         model=model, distributed_backend=backend, fp16=fp16, loss_scale=1,
         training_tensor_shapes=dict(tshapes), eval_tensor_shapes=dict(tshapes), training_tensor_dtypes=dtypes,
         inputs_module_destinations={"input": 0}, target_tensor_names={"target"},
         configuration_maps=conf if conf is not None else {"module_to_stage_map": None, "stage_to_rank_map": None,
                                                           "stage_to_depth_map": None},
         master_addr="127.0.0.1", rank=rank, local_rank=local_rank, num_ranks_in_server=1, verbose_freq=0,
-        model_type=runtime.IMAGE_CLASSIFICATION, native=native)
+        model_type=runtime.IMAGE_CLASSIFICATION)
     nv = r.num_warmup_minibatches + 1
     if optimizer == "sgd":
         opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=nv,

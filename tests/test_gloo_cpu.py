@@ -46,8 +46,11 @@ def worker(rank, world, conf_name, port, out_dir):
     model = make_model()
     shapes = {"input0": (6, 12), "target": (6,), "out0": (6, 16), "out1": (6, 5)}
     dtypes = {"input0": torch.float32, "target": torch.int64, "out0": torch.float32, "out1": torch.float32}
-    r = runtime.StageRuntime(model, "gloo", False, 1, shapes, dict(shapes), dtypes, {"input": 0}, {"target"}, conf,
-                             "127.0.0.1", rank, 0, 1, 0, runtime.IMAGE_CLASSIFICATION, device="cpu", native=False)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import pipeline_util as pu
+    pu.register_gloo()
+    r = pu.CpuRuntime(model, "gloo", False, 1, shapes, dict(shapes), dtypes, {"input": 0}, {"target"}, conf,
+                      "127.0.0.1", rank, 0, 1, 0, runtime.IMAGE_CLASSIFICATION)
     trainable = [m for m in r.modules() if any(True for _ in m.parameters())]
     opt = oracle.StashingOracle("SGD", trainable, r.num_warmup_minibatches + 1, lr=0.1, momentum=0.9)
     sync = getattr(r.modules()[0], "_pd_grad_sync", None)

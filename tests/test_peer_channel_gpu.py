@@ -59,24 +59,51 @@ def test_channel_fifo_and_header():
 
 def test_channel_wait_is_bounded():
     """A receive with nothing published gives up after the bound, reports a status, and leaves the
-    context usable (this is how a stalled or dead peer shows up)."""
+    context usable (this is how a stalled or dead peer shows up).  After that the channel is dead: a second
+    queued receive returns at once, `consumed` does not advance, the destination is zero-filled."""
+    import time
     cons, prod = _pair(1024, 2, 50)
-    o = torch.zeros(256, device="cuda")
+    o = torch.full((256,), 7.0, device="cuda")
     call("pd_chan_wait", cons, ctypes.c_void_p(o.data_ptr()), 1024, _s())
     rc = _lib.load().pd_chan_status(cons, _s())
     assert rc == -4 and "wait ran out" in _lib.last_error()
-    assert _lib.load().pd_chan_status(cons, _s()) == 0          # status is cleared once read
+    assert _lib.load().pd_chan_poll(cons) == -4                  # host mirror, no synchronisation
+    assert (o == 0).all()                                        # not stale slot contents
+    t0 = time.time()
+    call("pd_chan_wait", cons, ctypes.c_void_p(o.data_ptr()), 1024, _s())
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 0.04                               # no second 50 ms spin
+    assert _lib.load().pd_chan_status(cons, _s()) == -4          # a failed channel stays failed
+    # the producer end sees `consumed` still at 0: three pushes into a 2-slot ring must run out as well
+    m = torch.ones(256, device="cuda")
+    dims = (ctypes.c_int64 * 1)(256)
+    for _ in range(3):
+        call("pd_chan_push", prod, ctypes.c_void_p(m.data_ptr()), 1024, 1, dims, _s())
+    assert _lib.load().pd_chan_status(prod, _s()) == -4
     assert torch.ones(4, device="cuda").sum().item() == 4.0      # the context still works
     # producer side: a full ring that nobody drains
     cons2, prod2 = _pair(1024, 1, 50)
-    m = torch.ones(256, device="cuda")
-    dims = (ctypes.c_int64 * 1)(256)
     call("pd_chan_push", prod2, ctypes.c_void_p(m.data_ptr()), 1024, 1, dims, _s())
     call("pd_chan_push", prod2, ctypes.c_void_p(m.data_ptr()), 1024, 1, dims, _s())
     assert _lib.load().pd_chan_status(prod2, _s()) == -4
     with pytest.raises(_lib.PipedreamB200Error):
         call("pd_chan_push", prod2, ctypes.c_void_p(m.data_ptr()), 4096, 1, dims, _s())   # over capacity
     for ch in (prod, cons, prod2, cons2):
+        call("pd_chan_close", ch)
+
+
+def test_channel_size_mismatch_is_an_error():
+    """A receive that asks for another byte count than the message carries (the two stages disagree about a
+    tensor's shape or element type) fails the channel instead of reinterpreting the payload."""
+    cons, prod = _pair(4096, 2, 2000)
+    m = torch.ones(512, device="cuda", dtype=torch.bfloat16)          # 1024 bytes
+    dims = (ctypes.c_int64 * 1)(512)
+    call("pd_chan_push", prod, ctypes.c_void_p(m.data_ptr()), 1024, 1, dims, _s())
+    o = torch.full((512,), 3.0, device="cuda")                        # 2048 bytes asked for
+    call("pd_chan_wait", cons, ctypes.c_void_p(o.data_ptr()), 2048, _s())
+    assert _lib.load().pd_chan_status(cons, _s()) == -1 and "byte count" in _lib.last_error()
+    assert (o == 0).all()
+    for ch in (prod, cons):
         call("pd_chan_close", ch)
 
 
