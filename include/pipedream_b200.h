@@ -256,9 +256,16 @@ int pd_gemm_poll_error(int* code);
 /* Tiling switch of the bf16 contraction back end.  mode 1 (default): problems whose output is at least
  * 256 x 256 with N a multiple of 256 (the 256- and 512-channel convolutions of vgg16/gpus=8/stage0.py:16-31
  * in all three passes) run on pairs of CTAs - a cluster of two SMs sharing one 256 x 256 tile through
- * tcgen05.mma.cta_group::2; mode 0: every problem runs on single CTAs (128-row tiles).  Both tilings add the
- * same products in the same order.  Process-wide; meant for checking one tiling against the other.          */
+ * tcgen05.mma.cta_group::2 - and the 64- and 128-channel convolutions run two 128-row groups per tile, each with
+ * its own MMA-issuing warp (the 128-channel ones on CTA pairs as well); mode 0: every problem runs on single CTAs
+ * with one group (128-row tiles); mode 3: pairs, but one group.  All tilings add the same products in the same
+ * order.  Process-wide; meant for checking one tiling against the other.                                      */
 int pd_gemm_set_pair_mode(int mode);
+/* Diagnostic for the bf16 contraction kernel (no counterpart in the reference): with `device_buffer` pointing at
+ * 4 x (SM count) int64 in device memory, the MMA-issuing warp of every CTA adds, per launch, {cycles waiting for
+ * operand tiles to land in shared memory, cycles waiting for the epilogue to free an accumulator, total cycles,
+ * tiles} to its four slots.  NULL (the default) switches the counters off.  Process-wide.                    */
+int pd_gemm_set_stall_counters(void* device_buffer);
 
 /* ---- peer channels --------------------------------------------------------------------
  * One-directional FIFO between two pipeline-adjacent GPUs; replaces the helper threads and the

@@ -80,6 +80,7 @@ SIGNATURES = {
     "pd_attn_bahdanau_bwd": (I, [I, P, P, P, L, L, P, P, P, P, L, L, I, I, I, I, I, P, P, P, L, L, P, P, P, P]),
     "pd_gemm_poll_error": (I, [POINTER(c_int)]),
     "pd_gemm_set_pair_mode": (I, [I]),
+    "pd_gemm_set_stall_counters": (I, [P]),
     "pd_chan_create": (I, [L, I, I, POINTER(c_void_p)]),
     "pd_chan_export_handle": (I, [P, P]),
     "pd_chan_open": (I, [P, I, POINTER(c_void_p)]),

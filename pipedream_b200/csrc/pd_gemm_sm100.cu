@@ -1,13 +1,14 @@
 // bf16 contraction back end for Blackwell: TMA-fed tcgen05.mma with the fp32
 // accumulator in tensor memory.  One CTA computes one 128 x BLOCK_N output tile.
 //
-//   warp 0   : TMA producer (one elected lane) - fills a ring of shared-memory
-//              stages with 128B-swizzled operand boxes
-//   warp 1   : allocates tensor memory, issues tcgen05.mma (one elected lane),
-//              releases stages through tcgen05.commit
-//   warps 2-9: epilogue, two sets of four warps that take alternate tiles - tcgen05.ld the
-//              accumulator, apply bias / ReLU / border mask, store (or fp32 atomic-add for
-//              split-K weight gradients)
+//   warp 0    : TMA producer (one elected lane) - fills a ring of shared-memory
+//               stages with 128B-swizzled operand boxes
+//   warp 1    : allocates tensor memory, issues tcgen05.mma (one elected lane),
+//               releases stages through tcgen05.commit
+//   warp 2    : second MMA issuer, used by narrow tiles (two 128-row groups per tile)
+//   warps 3-10: epilogue, two sets of four warps - tcgen05.ld the accumulator, apply
+//               bias / ReLU / border mask, store (or fp32 atomic-add for split-K weight
+//               gradients); the sets take alternate tiles, or one group each
 //
 // Both operands may be K-major (contraction index contiguous in memory) or
 // MN-major (output index contiguous); the latter is what lets the data- and
@@ -36,7 +37,8 @@ using namespace pd_sm100;
 
 constexpr int kBlockM = 128;
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 320;                     // producer, MMA issuer, 2 x 4 epilogue warps
+constexpr int kThreads = 352;                     // producer, 2 MMA issuers, 2 x 4 epilogue warps
+constexpr int kEpiWarp0 = 3;                      // first epilogue warp
 constexpr int kMaxAccBufs = 4;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;   // 16 KiB
@@ -45,6 +47,7 @@ constexpr uint32_t kA3Bytes = kBox3Rows * kBlockK * 2; // 17 KiB (a multiple of 
 
 struct KParams {
   int M, N, block_n, m_tiles, n_tiles;
+  int groups;                 // 128-row sub-tiles of a tile, each with its own MMA issuer warp, accumulators and epilogue set
   int cta_n;                  // B rows (columns of the output tile) one CTA loads: block_n, or half of it for a CTA pair
   int num_taps, kb_per_tap, kb_per_split, split_k, num_z;   // num_z = number of z groups
   int acc_count, num_z_total;                                // accumulators per tile, outputs in all
@@ -67,6 +70,7 @@ struct KParams {
   int tap3;
   int t3_base[3], t3_off[PD_MAX_TAPS];
   int* err;
+  long long* stall;           // diagnostic (may be null): per CTA {cycles waiting for operands, for a free accumulator, total, tiles}
 };
 
 __device__ int g_gemm_error = 0;
@@ -229,11 +233,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-  __shared__ __align__(8) uint64_t tmem_full_bar[kMaxAccBufs];
-  __shared__ __align__(8) uint64_t tmem_empty_bar[kMaxAccBufs];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2 * kMaxAccBufs];     // [group][buffer]
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2 * kMaxAccBufs];
   __shared__ uint32_t tmem_base_holder;
 
-  const int warp = threadIdx.x >> 5;
+  // broadcast from lane 0 so that the compiler knows the warp index is the same in every lane of a warp: the role
+  // branches below are then warp-uniform and the code inside them can use the uniform datapath
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;   // position in the CTA pair
@@ -244,7 +250,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #define PD_FIRST_TILE (CG == 1 ? blockIdx.x : (blockIdx.x >> 1))
 #define PD_TILE_STEP (CG == 1 ? gridDim.x : (gridDim.x >> 1))
   const uint32_t b_bytes = (uint32_t)p.cta_n * kBlockK * 2;
-  const uint32_t stage_bytes = p.tap3 ? kA3Bytes + 3u * b_bytes : kABytes + (uint32_t)p.acc_count * b_bytes;
+  const int G = p.groups;
+  const uint32_t a_bytes = p.tap3 ? kA3Bytes : kABytes;      // one group's A box
+  const uint32_t a_total = (uint32_t)G * a_bytes;            // B tiles follow the groups' A boxes in a stage
+  const uint32_t stage_bytes = a_total + (p.tap3 ? 3u : (uint32_t)p.acc_count) * b_bytes;
+  const int group_rows = kBlockM * CG;                       // rows between the groups of a tile
   const int S = p.num_stages;
   const uint32_t acc_cols = (uint32_t)(p.acc_count * p.block_n);   // TMEM columns of one buffer
   const int tiles_mn = p.m_tiles * p.n_tiles;
@@ -253,14 +263,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   // TMEM columns: power of two >= 32 covering all accumulator buffers
   const uint32_t nbuf = (uint32_t)p.acc_bufs;
   uint32_t tmem_cols = 32;
-  while (tmem_cols < nbuf * acc_cols) tmem_cols <<= 1;
+  while (tmem_cols < (uint32_t)G * nbuf * acc_cols) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), (uint32_t)G);    // one commit per issuer
     }
-    for (int b = 0; b < kMaxAccBufs; ++b) {
+    for (int b = 0; b < 2 * kMaxAccBufs; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[b]), 4 * CG);     // one arrival per epilogue warp (of both CTAs of a pair)
     }
@@ -288,7 +298,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #define PD_DECODE_TILE(tile)                                                   \
   const int zs_ = (tile) / tiles_mn;                                           \
   const int rem_ = (tile) - zs_ * tiles_mn;                                    \
-  const int m0 = (rem_ / p.n_tiles) * (kBlockM * CG) + (int)rank * kBlockM;    \
+  const int m0 = (rem_ / p.n_tiles) * (kBlockM * CG * G) + (int)rank * kBlockM; \
   const int n0 = (rem_ % p.n_tiles) * p.block_n;                               \
   const int n0l = n0 + (int)rank * p.cta_n;  /* first B row this CTA loads */  \
   /* z varies faster than the K slice: the z outputs of a weight gradient (filter taps) read the same      \
@@ -308,10 +318,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // so the (up to six) box loads of a stage go out in one instruction slot.
     // Two boxes per stage (both operands K-major): one lane issues both, nothing to coordinate.
     if (p.tap3) {
-      // lane 0: the shared A box; lanes 1..: the B boxes of the triple's three taps
+      // lanes 0..G-1: the shared A box of each group; the lanes after them: the B boxes of the triple's three taps
       const int b_boxes = p.b_major ? p.cta_n / 64 : 1;
-      const bool is_a = lane == 0;
-      const int bl = lane - 1;
+      const bool is_a = lane < G;
+      const int bl = lane - G;
       const int s3 = is_a ? 0 : min(bl / b_boxes, 2);
       const int j = is_a ? 0 : bl % b_boxes;
       const bool has_box = is_a || bl < 3 * b_boxes;
@@ -325,17 +335,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           uint32_t dst_off, bytes;
           bool issue = has_box;
           if (is_a) {
-            x0 = p.a_col0; y0 = p.a_row0 + m0 + p.t3_base[r]; xk = kBlockK; yk = 0;
-            dst_off = 0; bytes = kA3Bytes;
+            x0 = p.a_col0; y0 = p.a_row0 + m0 + lane * group_rows + p.t3_base[r]; xk = kBlockK; yk = 0;
+            dst_off = (uint32_t)lane * kA3Bytes; bytes = kA3Bytes;
           } else {
             const int t = 3 * r + s3;
             if (p.b_major) {
               x0 = p.b_col0 + p.b_tap_col[t] + n0l + j * 64; y0 = p.b_row0 + p.b_tap_row[t]; xk = 0; yk = kBlockK;
-              dst_off = kA3Bytes + (uint32_t)s3 * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              dst_off = a_total + (uint32_t)s3 * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
               if (CG == 1) issue = issue && x0 < p.b_cols;
             } else {
               x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0l + p.b_tap_row[t]; xk = kBlockK; yk = 0;
-              dst_off = kA3Bytes + (uint32_t)s3 * b_bytes; bytes = b_bytes;
+              dst_off = a_total + (uint32_t)s3 * b_bytes; bytes = b_bytes;
             }
           }
           uint32_t tx = issue ? bytes : 0u;
@@ -378,14 +388,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) { ok = false; break; }
               const uint32_t fb = smem_u32(&full_bar[s]);
               const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
-              if (leader) mbar_expect_tx(fb, (kABytes + b_bytes) * CG);
+              if (leader) mbar_expect_tx(fb, (a_total + b_bytes) * CG);
               if constexpr (CG == 1) {
-                tma_load_2d(sa, &tma_a, fb, ax + kb * kBlockK, ay);
-                tma_load_2d(sa + kABytes, &tma_b, fb, bx + kb * kBlockK, by);
+                for (int g = 0; g < G; ++g)
+                  tma_load_2d(sa + (uint32_t)g * kABytes, &tma_a, fb, ax + kb * kBlockK, ay + g * group_rows);
+                tma_load_2d(sa + a_total, &tma_b, fb, bx + kb * kBlockK, by);
               } else {
                 const uint32_t fbc = mapa_shared(fb, 0);
-                tma_load_2d_pair(sa, &tma_a, fbc, ax + kb * kBlockK, ay);
-                tma_load_2d_pair(sa + kABytes, &tma_b, fbc, bx + kb * kBlockK, by);
+                for (int g = 0; g < G; ++g)
+                  tma_load_2d_pair(sa + (uint32_t)g * kABytes, &tma_a, fbc, ax + kb * kBlockK, ay + g * group_rows);
+                tma_load_2d_pair(sa + a_total, &tma_b, fbc, bx + kb * kBlockK, by);
               }
             }
           }
@@ -393,12 +405,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
     } else
     {
-      const int a_boxes = p.a_major ? 2 : 1;
+      const int a_boxes = p.a_major ? 2 : 1;                 // per group
       const int b_boxes = p.b_major ? p.cta_n / 64 : 1;
-      const bool is_a = lane < a_boxes;
-      const int bl = lane - a_boxes;                         // B lanes: accumulator-major
+      const bool is_a = lane < a_boxes * G;
+      const int ag = is_a ? lane / a_boxes : 0;              // A lanes: which group's tile
+      const int bl = lane - a_boxes * G;                     // B lanes: accumulator-major
       const int acc = is_a ? 0 : bl / b_boxes;               // which accumulator's B tile
-      const int j = is_a ? lane : bl % b_boxes;              // box index within its operand tile
+      const int j = is_a ? lane % a_boxes : bl % b_boxes;    // box index within its operand tile
       uint32_t g = 0;                       // stage uses so far (ring position across tiles)
       bool ok = true;
       for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
@@ -413,21 +426,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           bool issue = has_box;
           if (is_a) {
             if (p.a_major) {
-              x0 = p.a_col0 + p.a_tap_col[t] + m0 + j * 64; y0 = p.a_row0 + p.a_tap_row[t]; xk = 0; yk = kBlockK;
-              dst_off = (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              x0 = p.a_col0 + p.a_tap_col[t] + m0 + ag * group_rows + j * 64; y0 = p.a_row0 + p.a_tap_row[t]; xk = 0; yk = kBlockK;
+              dst_off = (uint32_t)ag * kABytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
               if (CG == 1) issue = issue && x0 < p.a_cols;
             } else {
-              x0 = p.a_col0 + p.a_tap_col[t]; y0 = p.a_row0 + m0 + p.a_tap_row[t]; xk = kBlockK; yk = 0;
-              dst_off = 0; bytes = kABytes;
+              x0 = p.a_col0 + p.a_tap_col[t]; y0 = p.a_row0 + m0 + ag * group_rows + p.a_tap_row[t]; xk = kBlockK; yk = 0;
+              dst_off = (uint32_t)ag * kABytes; bytes = kABytes;
             }
           } else {
             if (p.b_major) {
               x0 = p.b_col0 + p.b_tap_col[t] + n0l + j * 64; y0 = p.b_row0 + p.b_tap_row[t] + zrow; xk = 0; yk = kBlockK;
-              dst_off = kABytes + (uint32_t)acc * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
+              dst_off = a_total + (uint32_t)acc * b_bytes + (uint32_t)j * kAtomBytes; bytes = kAtomBytes;
               if (CG == 1) issue = issue && x0 < p.b_cols;
             } else {
               x0 = p.b_col0 + p.b_tap_col[t]; y0 = p.b_row0 + n0l + p.b_tap_row[t] + zrow; xk = kBlockK; yk = 0;
-              dst_off = kABytes + (uint32_t)acc * b_bytes; bytes = b_bytes;
+              dst_off = a_total + (uint32_t)acc * b_bytes; bytes = b_bytes;
             }
           }
           // bytes that will land in a stage = sum over the issuing lanes
@@ -455,14 +468,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0 && leader) {
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------- MMA issuers ------------------------------
+    // One warp per group; one lane issues.  The issuing thread runs every instruction between two MMAs itself, and a
+    // tcgen05.mma is only 32 (N = 64) to 128 (N = 256) cycles of tensor-pipe work, so the loops below are kept to a
+    // handful of instructions per MMA: descriptors are advanced by 32-bit adds on their low words, the ring position
+    // and its barrier addresses are carried along instead of being derived by division, and nothing is decided per
+    // MMA that can be decided per tile.  Narrow tiles (N <= 128) still need two issuers to fill the pipe - each
+    // with its own accumulators and A rows, sharing the stage's B tiles.
+    const int grp = warp - 1;
+    if (lane == 0 && leader && grp < G) {
+      const uint32_t bar0 = (uint32_t)grp * kMaxAccBufs;           // this group's tmem barriers
+      const uint32_t tmem_g = tmem_base + (uint32_t)grp * nbuf * acc_cols;
       const uint32_t adv_a = p.a_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
       const uint32_t adv_b = p.b_major ? (uint32_t)(kUmmaK * 128) >> 4 : (uint32_t)(kUmmaK * 2) >> 4;
-      uint32_t g = 0;
+      constexpr int kSteps = kBlockK / kUmmaK;
+      // descriptor words of stage 0; a stage further on adds stage_lo to the low words
+      const uint64_t da0 = make_desc(smem0 + (uint32_t)grp * a_bytes, p.a_major);
+      const uint64_t db0 = make_desc(smem0 + a_total, p.b_major);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t stage_lo = stage_bytes >> 4;
+      const uint32_t b_tile_lo = b_bytes >> 4;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t idesc = p.idesc;
+      // ring position, carried across tiles
+      int s = 0;
+      uint32_t ph = 0, a_lo = a_lo0, b_lo = b_lo0, fb = full0, eb = empty0;
+#define PD_NEXT_STAGE                                                         \
+      ++s; a_lo += stage_lo; b_lo += stage_lo; fb += 8; eb += 8;                \
+      if (s == S) { s = 0; ph ^= 1u; a_lo = a_lo0; b_lo = b_lo0; fb = full0; eb = empty0; }
       uint32_t local = 0;                   // tiles done by this CTA
       bool ok = true;
+      const bool timing = p.stall != nullptr;
+      long long t_ops = 0, t_acc = 0;
+      const long long t_begin = timing ? clock64() : 0;
       for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
         PD_DECODE_TILE(tile)
         (void)m0; (void)n0; (void)n0l; (void)kb_begin; (void)acc0;
@@ -470,77 +510,110 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const uint32_t buf = local % nbuf;
         const uint32_t use = local / nbuf;
         // the epilogue must have drained this accumulator (passes at once on its first use)
-        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), (use & 1u) ^ 1u, p.err, 4)) { ok = false; break; }
+        const long long ta = timing ? clock64() : 0;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[bar0 + buf]), (use & 1u) ^ 1u, p.err, 4);
+        if (timing) t_acc += clock64() - ta;
+        if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + buf * acc_cols;
-        for (int it = 0; it < iters; ++it, ++g) {
-          const int s = (int)(g % (uint32_t)S);
-          const uint32_t ph = (g / (uint32_t)S) & 1u;
-          if (!mbar_wait(smem_u32(&full_bar[s]), ph, p.err, 2)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = smem0 + (uint32_t)s * stage_bytes;
-          if (p.tap3) {
-            const int r = it / kbn;
+        const uint32_t tmem_d = tmem_g + buf * acc_cols;
+        uint32_t acc = 0;                     // the tile's first MMA overwrites the accumulator
+        if (p.tap3) {
+          for (int r = 0; r < 3 && ok; ++r) {
+            // the taps' rows start t3_off (0..2) rows into the shared box; the swizzle is a function of the
+            // shared-memory address, so a descriptor may start on any 128-byte row of the box
+            const uint32_t o0 = (uint32_t)p.t3_off[3 * r] * 8u, o1 = (uint32_t)p.t3_off[3 * r + 1] * 8u,
+                           o2 = (uint32_t)p.t3_off[3 * r + 2] * 8u;
+            for (int kb = 0; kb < kbn; ++kb) {
+              const long long tw = timing ? clock64() : 0;
+              ok = mbar_wait(fb, ph, p.err, 2);
+              if (timing) t_ops += clock64() - tw;
+              if (!ok) break;
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+              umma_lo<CG, 2>(tmem_d, a_lo + o0, a_hi, b_lo, b_hi, idesc, acc);
 #pragma unroll
-            for (int s3 = 0; s3 < 3; ++s3) {
-              // the tap's rows start t3_off (0..2) rows into the shared box; the swizzle is a function of
-              // the shared-memory address, so a descriptor may start on any 128-byte row of the box
-              const uint64_t da3 = make_desc(sa + (uint32_t)p.t3_off[3 * r + s3] * 128u, 0);
-              const uint64_t db3 = make_desc(sa + kA3Bytes + (uint32_t)s3 * b_bytes, p.b_major);
+              for (int kk = 1; kk < kSteps; ++kk)
+                umma_lo<CG, 1>(tmem_d, a_lo + o0 + kk * adv_a, a_hi, b_lo + kk * adv_b, b_hi, idesc, 1u);
 #pragma unroll
-              for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-                umma_cg<CG>(tmem_d, da3 + (uint64_t)(kk * adv_a), db3 + (uint64_t)(kk * adv_b), p.idesc,
-                          (uint32_t)((it | s3 | kk) != 0));
+              for (int kk = 0; kk < kSteps; ++kk)
+                umma_lo<CG, 1>(tmem_d, a_lo + o1 + kk * adv_a, a_hi, b_lo + b_tile_lo + kk * adv_b, b_hi, idesc, 1u);
+#pragma unroll
+              for (int kk = 0; kk < kSteps; ++kk)
+                umma_lo<CG, 1>(tmem_d, a_lo + o2 + kk * adv_a, a_hi, b_lo + 2u * b_tile_lo + kk * adv_b, b_hi, idesc, 1u);
+              commit_cg<CG>(eb);
+              acc = 1u;
+              PD_NEXT_STAGE
             }
-            commit_cg<CG>(smem_u32(&empty_bar[s]));
-            continue;
           }
-          const uint64_t da = make_desc(sa, p.a_major);
-          if (p.b_major && accn > 1 && accn * p.block_n <= 256) {
-            // MN-major B tiles of the accumulators of a z group lie back to back, 64-column atom after atom,
-            // and so do their accumulators in tensor memory: one MMA of N = accn * block_n does the work of
-            // accn narrow ones (an MMA costs about the same up to N = 128, so narrow ones waste the pipe)
-            const uint64_t db = make_desc(sa + kABytes, 1);
-            const uint32_t idesc_n = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((accn * p.block_n) >> 3) << 17);
+        } else if (p.b_major && accn > 1 && accn * p.block_n <= 256) {
+          // MN-major B tiles of the accumulators of a z group lie back to back, 64-column atom after atom,
+          // and so do their accumulators in tensor memory: one MMA of N = accn * block_n does the work of
+          // accn narrow ones
+          const uint32_t idesc_n = (idesc & ~(0x3Fu << 17)) | ((uint32_t)((accn * p.block_n) >> 3) << 17);
+          for (int it = 0; it < iters; ++it) {
+            const long long tw = timing ? clock64() : 0;
+            ok = mbar_wait(fb, ph, p.err, 2);
+            if (timing) t_ops += clock64() - tw;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            umma_lo<CG, 2>(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc_n, acc);
 #pragma unroll
-            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-              umma_cg<CG>(tmem_d, da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b), idesc_n,
-                        (uint32_t)((it | kk) != 0));
-            commit_cg<CG>(smem_u32(&empty_bar[s]));
-            continue;
+            for (int kk = 1; kk < kSteps; ++kk)
+              umma_lo<CG, 1>(tmem_d, a_lo + kk * adv_a, a_hi, b_lo + kk * adv_b, b_hi, idesc_n, 1u);
+            commit_cg<CG>(eb);
+            acc = 1u;
+            PD_NEXT_STAGE
           }
-          for (int a = 0; a < accn; ++a) {
-            const uint64_t db = make_desc(sa + kABytes + (uint32_t)a * b_bytes, p.b_major);
+        } else {
+          for (int it = 0; it < iters; ++it) {
+            const long long tw = timing ? clock64() : 0;
+            ok = mbar_wait(fb, ph, p.err, 2);
+            if (timing) t_ops += clock64() - tw;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int a = 0; a < accn; ++a) {
+              const uint32_t tmem_a = tmem_d + (uint32_t)(a * p.block_n);
+              const uint32_t b_lo_a = b_lo + (uint32_t)a * b_tile_lo;
+              umma_lo<CG, 2>(tmem_a, a_lo, a_hi, b_lo_a, b_hi, idesc, acc);
 #pragma unroll
-            for (int kk = 0; kk < kBlockK / kUmmaK; ++kk)
-              umma_cg<CG>(tmem_d + (uint32_t)(a * p.block_n), da + (uint64_t)(kk * adv_a), db + (uint64_t)(kk * adv_b),
-                        p.idesc, (uint32_t)((it | kk) != 0));
+              for (int kk = 1; kk < kSteps; ++kk)
+                umma_lo<CG, 1>(tmem_a, a_lo + kk * adv_a, a_hi, b_lo_a + kk * adv_b, b_hi, idesc, 1u);
+            }
+            commit_cg<CG>(eb);
+            acc = 1u;
+            PD_NEXT_STAGE
           }
-          commit_cg<CG>(smem_u32(&empty_bar[s]));
         }
-        if (ok) commit_cg<CG>(smem_u32(&tmem_full_bar[buf]));
+        if (ok) commit_cg<CG>(smem_u32(&tmem_full_bar[bar0 + buf]));
         ++local;
+      }
+#undef PD_NEXT_STAGE
+      if (timing && grp == 0) {
+        long long* o = p.stall + 4ll * blockIdx.x;
+        o[0] += t_ops; o[1] += t_acc; o[2] += clock64() - t_begin; o[3] += local;
       }
     }
   } else {
     // -------------------------------- epilogue --------------------------------
     const int lg = warp & 3;                 // TMEM lane group this warp may read
-    const uint32_t set = (uint32_t)(warp - 2) >> 2;   // which of the two epilogue sets
+    const uint32_t set = (uint32_t)(warp - kEpiWarp0) >> 2;   // which of the two epilogue sets
+    // one group: the sets take alternate tiles; two groups: each set drains its own group's accumulators
+    const uint32_t grp = G == 2 ? set : 0u;
+    const uint32_t bar0 = grp * kMaxAccBufs;
     uint32_t local = 0;
     bool ok = true;
     for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
       PD_DECODE_TILE(tile)
       (void)kb_begin; (void)n0l;
       if (iters == 0) continue;
-      if ((local & 1u) != set) { ++local; continue; }
+      if (G == 1 && (local & 1u) != set) { ++local; continue; }
       const uint32_t buf = local % nbuf;
       const uint32_t use = local / nbuf;
-      ok = mbar_wait(smem_u32(&tmem_full_bar[buf]), use & 1u, p.err, 3);
+      ok = mbar_wait(smem_u32(&tmem_full_bar[bar0 + buf]), use & 1u, p.err, 3);
       // the wait result can differ between lanes only when the bound ran out; make it uniform
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m = m0 + lg * 32 + lane;
+      const int m = m0 + (int)grp * group_rows + lg * 32 + lane;
       bool border = false;
       if (p.pad_wp > 0) {
         const int wp = m % p.pad_wp;
@@ -548,7 +621,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         border = (wp == 0) | (wp == p.pad_wp - 1) | (hp == 0) | (hp == p.pad_hp - 1);
       }
       const bool row_ok = m < p.M;
-      const uint32_t tmem_acc = tmem_base + buf * acc_cols + ((uint32_t)(lg * 32) << 16);
+      const uint32_t tmem_acc = tmem_base + (grp * nbuf + buf) * acc_cols + ((uint32_t)(lg * 32) << 16);
       const int total_cols = accn * p.block_n;
       for (int cc = 0; cc < total_cols; cc += 64) {
         // two chunks in flight per wait
@@ -573,8 +646,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       __syncwarp();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       if (lane == 0) {
-        if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
-        else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
+        if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[bar0 + buf]));
+        else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[bar0 + buf]), 0));
       }
       ++local;
     }
@@ -702,6 +775,8 @@ int pd_gemm_pick_block_n(int M, int N, int b_major, int zs) {
 
 namespace {
 int g_pair_mode = 1;     // 1 = CTA pairs where they apply, 0 = single CTAs only (kept for A/B checks of the two tilings)
+int g_group_mode = 1;    // 1 = two issuer groups per tile for narrow convolutions, 0 = one
+long long* g_stall = nullptr;
 }
 
 // A pair of CTAs (256 x 256 tile) is used when the output is at least 256 wide in both directions, the
@@ -713,13 +788,22 @@ bool pd_gemm_use_pair(int M, int N, int num_z, int z_group, int split_k) {
   if (N < 256 || (N % 256) != 0 || M < 256) return false;
   (void)z_group;
   const long long tiles = (long long)((M + 255) / 256) * (N / 256) * (num_z > 0 ? num_z : 1) * (split_k > 0 ? split_k : 1);
-  return tiles >= sms / 2;
+  return tiles >= sms / 2 - sms / 16;     // enough to keep nearly every pair of SMs busy
 }
 
 // Chooses between the two tilings of wide problems: 1 (default) lets problems that qualify run on CTA pairs,
 // 0 keeps every problem on single CTAs.  Both produce the same sums in the same order.
 PD_EXPORT int pd_gemm_set_pair_mode(int mode) {
-  g_pair_mode = mode ? 1 : 0;
+  g_pair_mode = (mode & 1) ? 1 : 0;
+  g_group_mode = (mode & 1) && !(mode & 2) ? 1 : 0;
+  return PD_OK;
+}
+
+// Diagnostic: with a device buffer of 4 x (number of SMs) int64 the MMA issuer of every CTA adds up, per launch,
+// the cycles it waited for operands to land in shared memory, the cycles it waited for a free accumulator, its
+// total cycles and its tile count.  NULL switches the counters off (the default).
+PD_EXPORT int pd_gemm_set_stall_counters(void* device_buffer) {
+  g_stall = (long long*)device_buffer;
   return PD_OK;
 }
 
@@ -737,17 +821,32 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
     PD_REQUIRE((g.a_tap_col[t] % 8) == 0 && (g.b_tap_col[t] % 8) == 0, "tcgen05 gemm: tap column offsets must be multiples of 8");
 
   int block_n = pd_gemm_pick_block_n(g.M, g.N, g.b_major, g.num_z * g.split_k);
-  const bool pair = pd_gemm_use_pair(g.M, g.N, g.num_z, g.z_group, g.split_k);
+  bool pair = pd_gemm_use_pair(g.M, g.N, g.num_z, g.z_group, g.split_k);
   if (pair) block_n = 256;
   // 3x3 convolutions on a single CTA: 128-wide tiles with the shared tap boxes beat 256-wide ones (the 256-wide
   // tile cannot share the activation box - its stage would not fit - and is then bound by the rate at which
   // one SM pulls operands out of L2) and quantise better into waves of 148 CTAs
   if (g.share_tap_rows && block_n > 128 && !pair) block_n = 128;
+  // Narrow convolutions (N = 64 or 128): two 128-row groups per tile, each with its own issuer warp, because one
+  // thread cannot issue N <= 128 instructions fast enough to fill the tensor pipe.  N = 64 keeps single CTAs
+  // (stage: two activation boxes + three 8 KiB weight tiles, three stages); N = 128 runs on CTA pairs so that each
+  // CTA only holds half of the weight tiles and three stages still fit.
+  int groups = 1;
+  const bool conv9 = g.share_tap_rows && g.num_taps == 9 && !g.a_major && g.num_z == 1 && g.split_k == 1;
+  if (g_group_mode && conv9 && !pair) {
+    const int sms = pd_num_sms();
+    if (g.N == 64 && (long long)((g.M + 255) / 256) >= sms) {
+      groups = 2; block_n = 64;
+    } else if (g.N == 128 && g_pair_mode && sms >= 2 && !(sms & 1) && (long long)((g.M + 511) / 512) >= sms / 2) {
+      groups = 2; block_n = 128; pair = true;
+    }
+  }
   const int cg = pair ? 2 : 1;
   KParams p;
   memset(&p, 0, sizeof(p));
   p.M = g.M; p.N = g.N; p.block_n = block_n;
   p.cta_n = block_n / cg;
+  p.groups = groups;
   p.num_taps = g.num_taps;
   p.kb_per_tap = (g.K + kBlockK - 1) / kBlockK;
   p.split_k = g.split_k;
@@ -796,16 +895,21 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   }
   p.tap3 = tap3 ? 1 : 0;
   if (tap3) p.num_taps = 3;
-  const uint32_t stage_bytes = tap3 ? kA3Bytes + 3u * (uint32_t)p.cta_n * kBlockK * 2
+  if (!tap3 && groups > 1) {
+    pd_set_error("tcgen05 gemm: internal error, grouped tiles need the shared-tap path");
+    return PD_ERR_INVALID;
+  }
+  const uint32_t stage_bytes = tap3 ? (uint32_t)groups * kA3Bytes + 3u * (uint32_t)p.cta_n * kBlockK * 2
                                     : kABytes + (uint32_t)p.acc_count * (uint32_t)p.cta_n * kBlockK * 2;
   int stages = (int)((200u * 1024u) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   p.num_stages = stages;
   {
     const int acc_cols = p.acc_count * block_n;
-    int bufs = 512 / acc_cols;
+    int bufs = 512 / (acc_cols * groups);
     p.acc_bufs = bufs > kMaxAccBufs ? kMaxAccBufs : (bufs < 2 ? 2 : bufs);
   }
+  p.stall = g_stall;
   {
     int erc = pd_gemm_error_word(&p.err);
     if (erc != PD_OK) return erc;
@@ -828,7 +932,7 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
       g_attr_set[dev] = true;
     }
   }
-  p.m_tiles = (g.M + kBlockM * cg - 1) / (kBlockM * cg);
+  p.m_tiles = (g.M + kBlockM * cg * groups - 1) / (kBlockM * cg * groups);
   p.n_tiles = (g.N + block_n - 1) / block_n;
   const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.num_z * p.split_k;
   PD_REQUIRE(total_tiles < (1ll << 31), "tcgen05 gemm: too many tiles");

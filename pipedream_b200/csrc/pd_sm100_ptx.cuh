@@ -48,6 +48,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// True in exactly one lane of a converged warp.  The MMA issuer runs its loops with the whole warp and only
+// predicates the tcgen05 instructions themselves on this: descriptors and addresses computed in warp-uniform code
+// can stay in uniform registers, which is where tcgen05.mma takes its operands from.  (Computed by a single
+// diverged lane they have to be moved over for every instruction, and that - not the tensor pipe - then sets
+// the pace: about 150 cycles per MMA against 32..128 cycles of work.)
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n.reg .pred P1;\n"
+      "elect.sync _|P1, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P1;\n}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -57,6 +71,39 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// The same MMA with each descriptor given as its low word plus a high word that never changes inside a kernel
+// (stride, version and swizzle fields): advancing a descriptor along K, to another tap or to the next pipeline
+// stage is then one 32-bit add.  The issuing thread executes every instruction between two MMAs by itself, and
+// at 30 to 130 cycles of tensor-pipe work per MMA those instructions - not the pipe - easily set the pace.
+// ACC: 0 = overwrite the accumulator, 1 = accumulate, 2 = decided by `acc` at run time.
+template <int CG, int ACC>
+__device__ __forceinline__ void umma_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                        uint32_t idesc, uint32_t acc) {
+  if constexpr (CG == 1) {
+    if constexpr (ACC == 2)
+      asm volatile(
+          "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+          ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc) : "memory");
+    else
+      asm volatile(
+          "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+          "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+          ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC) : "memory");
+  } else {
+    if constexpr (ACC == 2)
+      asm volatile(
+          "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+          "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+          ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc) : "memory");
+    else
+      asm volatile(
+          "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+          "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}"
+          ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC) : "memory");
+  }
+}
+
 // ---- cta_group::2 (a pair of CTAs in one cluster working on one 256-row tile) ------------------------------
 // The pair's MMA is issued by the even-ranked CTA; each CTA supplies its own 128 rows of A and its half of B
 // from its own shared memory and receives its 128 accumulator rows in its own tensor memory.
