@@ -99,7 +99,8 @@ def disable_dropout(model):
 
 
 def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, momentum=0.9, weight_decay=5e-4,
-                dropout=False, optimizer="sgd", macrobatch=False, shapes=None, native=True, local_rank=0):
+                dropout=False, optimizer="sgd", macrobatch=False, shapes=None, native=True, local_rank=0,
+                num_ranks_in_server=1, enable_recompute=False, reference_dtypes=False):
     torch.manual_seed(seed)
     model = package.model(torch.nn.CrossEntropyLoss())
     if not dropout:
@@ -107,7 +108,9 @@ def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, mome
     if shapes is None:
         shapes = tensor_shapes(model, batch)
     tshapes, dtypes = shapes
-    if fp16:
+    if fp16 and not reference_dtypes:
+        # (the reference's driver scripts leave float32 in this table even with --fp16; reference_dtypes=True
+        # keeps it that way to check that the runtime substitutes the 16-bit type itself)
         dtypes = {k: (torch.bfloat16 if v == torch.float32 else v) for k, v in dtypes.items()}
     cls = runtime.StageRuntime if native else TorchModuleRuntime
     r = cls(
@@ -116,8 +119,8 @@ def make_worker(package, conf, rank, batch, fp16, backend, seed=0, lr=0.01, mome
         inputs_module_destinations={"input": 0}, target_tensor_names={"target"},
         configuration_maps=conf if conf is not None else {"module_to_stage_map": None, "stage_to_rank_map": None,
                                                           "stage_to_depth_map": None},
-        master_addr="127.0.0.1", rank=rank, local_rank=local_rank, num_ranks_in_server=1, verbose_freq=0,
-        model_type=runtime.IMAGE_CLASSIFICATION)
+        master_addr="127.0.0.1", rank=rank, local_rank=local_rank, num_ranks_in_server=num_ranks_in_server,
+        verbose_freq=0, model_type=runtime.IMAGE_CLASSIFICATION, enable_recompute=enable_recompute)
     nv = r.num_warmup_minibatches + 1
     if optimizer == "sgd":
         opt = sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1, num_versions=nv,
