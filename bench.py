@@ -43,6 +43,30 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def measured_traffic():
+    """DRAM traffic per launch of the contraction kernel as ncu measured it, read from the committed profile
+    summary.  The summary names the sha256 of the kernel source it was taken on; if the source has changed since,
+    the figure is stale and None is reported instead."""
+    import hashlib
+    import re
+    path = os.path.join(ROOT, "profiles", "gemm_tcgen05_conv_56x56_256_ncu.md")
+    src = os.path.join(ROOT, "pipedream_b200", "csrc", "pd_gemm_sm100.cu")
+    try:
+        text = open(path).read()
+        sha = hashlib.sha256(open(src, "rb").read()).hexdigest()
+    except OSError:
+        return None, "no profile summary"
+    m = re.search(r"kernel_source_sha256:\s*([0-9a-f]{64})", text)
+    t = re.search(r"dram_bytes_per_launch_mean:\s*([0-9.eE+]+)", text)
+    c = re.search(r"captured_at_commit:\s*([0-9a-f]+)", text)
+    if not (m and t):
+        return None, "profile summary carries no machine-readable traffic line"
+    if m.group(1) != sha:
+        return None, "kernel source changed since the capture (commit %s)" % (c.group(1) if c else "?")
+    return float(t.group(1)), "ncu capture at commit %s: conv 64x56x56 256->256, mean of fwd/dgrad/wgrad; algorithmic 221.6e6" % (
+        c.group(1) if c else "?")
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -168,11 +192,12 @@ def timed_loop(r, opt, steps, warmup, read_loss):
     return start.elapsed_time(end)
 
 
-def cpu_baseline(sample_steps=2, batch=8):
+def cpu_baseline(sample_steps=3, batch=8):
     """The CPU oracle (port of the reference's PyTorch path) on the host cores, fp32, on a bounded
     sample of the workload: `sample_steps` minibatches of `batch` images after one untimed one."""
     from oracle import pipedream_oracle as oracle
     from pipedream_b200.stages import SyntheticImages
+    torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     st = oracle.vgg16_stages(None)
     model = [(st[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
@@ -232,6 +257,7 @@ def run_gpu_single(steps, warmup):
         raise RuntimeError("a tcgen05 kernel reported a bounded wait that ran out (code %d)" % err)
 
     pk = peaks()
+    traffic, traffic_note = measured_traffic()
     tot_flops = sum(v[1] for v in tl.values())
     tot_ms = sum(v[2] for v in tl.values())
     n_launch = sum(v[0] for v in tl.values())
@@ -240,10 +266,7 @@ def run_gpu_single(steps, warmup):
         "bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": round(achieved, 1),
         "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(achieved / pk["bf16_tflops_sustained"], 4),
         "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
-        # dram__bytes_read + dram__bytes_write per launch from the ncu capture of the 56x56 256->256 layer
-        # (profiles/gemm_tcgen05_conv_56x56_256_ncu.md), averaged over its fwd / dgrad / wgrad launches;
-        # the algorithmic bytes of that launch are 221.6 MB
-        "traffic": 332.0e6, "traffic_case": "conv 64x56x56 256->256, mean of fwd/dgrad/wgrad; algorithmic 221.6e6",
+        "traffic": traffic, "traffic_case": traffic_note,
         "launches_per_step": n_launch // max(1, steps), "kernel_ms_per_step": round(tot_ms / steps, 3),
         "algorithmic_tflop_per_step": round(tot_flops / steps / 1e12, 3),
         "by_pass": {k: {"launches": v[0] // max(1, steps), "tflops": round(v[1] / (v[2] * 1e-3) / 1e12, 1),
@@ -267,35 +290,78 @@ def run_gpu_single(steps, warmup):
     }
 
 
+def reference_partition(n_gpus):
+    """The stage / replica layout the GPU arm uses at this GPU count, for the CPU arm to follow."""
+    if n_gpus <= 1:
+        return None, [0, 0], {0: [0]}, "1 stage x 1 replica"
+    if n_gpus == 2:
+        return None, [0, 0], {0: [0, 1]}, "1 stage x 2 replicas (data parallel)"
+    return "flatten", [0, 1, 1], {0: list(range(n_gpus - 1)), 1: [n_gpus - 1]}, "hybrid %d:1" % (n_gpus - 1)
+
+
 def run_reference(steps, warmup, n_gpus):
-    """--impl reference: the reference's CPU path (oracle port) on the host cores, same metric and
-    network; each step is a bounded sample (batch 8 instead of 64 per replica, fp32)."""
+    """--impl reference: the reference's CPU path on the host cores - the oracle port, because the reference is
+    Python source that cannot travel to the benchmark machine - for the same metric, network and stage / replica
+    layout as the GPU arm at this GPU count.  All ranks of the layout are stepped inside one process (the oracle's
+    pipeline simulation: 1F1B with weight stashing, replica gradient averaging) with every host thread given to
+    torch's intra-op pool; each step is a bounded sample: one minibatch of 8 images (instead of 64) per stage-0
+    replica, fp32.  Under torch.distributed.run rank 0 alone runs it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
     from oracle import pipedream_oracle as oracle
     from pipedream_b200.stages import SyntheticImages
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)          # the launcher exports OMP_NUM_THREADS=1 for its workers
     batch = 8
+    cut, m2s, s2r, label = reference_partition(n_gpus)
     torch.manual_seed(0)
-    st = oracle.vgg16_stages(None)
-    model = [(st[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
-    pipe = oracle.PipelineOracle(model, [0, 0], {0: [0]}, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=5e-4))
-    if warmup > 0:
-        pipe.run({0: SyntheticImages(batch, warmup)}, warmup)
+    st = oracle.vgg16_stages(cut)
+    if len(st) == 1:
+        model = [(st[0], ["input0"], ["out0"]), (torch.nn.CrossEntropyLoss(), ["out0"], ["loss"])]
+    else:
+        model = [(st[0], ["input0"], ["out0"]), (st[1], ["out0"], ["out1"]), (torch.nn.CrossEntropyLoss(), ["out1"], ["loss"])]
+    r0 = len(s2r[0])
+    # a multi-rank CPU step costs r0 minibatches: keep the whole run within a few minutes
+    steps_run = max(2, min(steps, max(2, 24 // r0)))
+    warm_run = min(warmup, 1 if r0 > 1 else 2)
+    pipe = oracle.PipelineOracle(model, m2s, s2r, None, "SGD", dict(lr=0.01, momentum=0.9, weight_decay=5e-4, scale_lr=True))
+    if warm_run > 0:
+        pipe.run({k: SyntheticImages(batch, warm_run, seed=7 + k) for k in s2r[0]}, warm_run)
     t0 = time.time()
-    pipe.run({0: SyntheticImages(batch, steps, seed=99)}, steps)
+    pipe.run({k: SyntheticImages(batch, steps_run, seed=99 + k) for k in s2r[0]}, steps_run)
     dt = time.time() - t0
-    v = round(batch * steps / dt, 3)
-    sample = "each step = one minibatch of %d images (instead of 64), fp32, whole VGG-16 in one stage" % batch
+    v = round(batch * r0 * steps_run / dt, 3)
+    sample = ("%d timed steps (of the %d asked for) after %d untimed; each step = one minibatch of %d images (instead of 64) "
+              "per stage-0 replica, fp32, layout %s simulated rank by rank in one process, %d intra-op threads"
+              % (steps_run, steps, warm_run, batch, label, cores))
     return {
-        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": n_gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": round(dt / steps * 1e3, 1), "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": n_gpus, "steps": steps_run,
+        "warmup": warm_run, "ms_per_step": round(dt / steps_run * 1e3, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "VGG-16 training step on host cores (CPU restatement of the reference's PyTorch path)",
-                   "global_batch": batch, "parallelism": "1 process"},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+                   "global_batch": batch * r0, "parallelism": label},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+
+
+def secondary_gnmt_single(steps, warmup):
+    """The other network of the headline metric on the same GPU right after VGG-16: GNMT 8+8 layers, batch 128,
+    the four stages in one process.  A trimmed copy of `python bench.py --model gnmt`."""
+    import gc
+    import bench_gnmt
+    gc.collect()
+    torch.cuda.empty_cache()
+    try:
+        g = bench_gnmt.run(steps, warmup, False)
+    except Exception as e:      # the headline line must not be lost to the secondary run
+        return {"error": "%s: %s" % (type(e).__name__, e)}
+    keep = ("metric", "value", "unit", "steps", "warmup", "ms_per_step", "dtype", "e2e", "gpu_launches")
+    out = {k: g[k] for k in keep if k in g}
+    out["config"] = {k: g["config"][k] for k in ("workload", "global_batch", "tokens_per_sec", "parallelism")}
+    out["roofline"] = {k: g["roofline"][k] for k in ("bound", "kernel", "achieved", "peak", "unit", "frac", "kernel_ms_per_step")}
+    return out
 
 
 def run_profile_case(name):
@@ -346,10 +412,13 @@ def run_profile_case(name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default: 200 for the GPU arm, 20 for --impl reference)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the GNMT run that the default line carries under \"secondary\"")
     ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50", "gpt"],
                     help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT), resnet50 or gpt (24-layer 2BW decoder)")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd"],
@@ -358,6 +427,8 @@ def main():
     if a.profile_case:
         run_profile_case(a.profile_case)
         return
+    if a.steps is None:
+        a.steps = 20 if a.impl == "reference" else 200
     if a.impl == "reference":
         out = run_reference(a.steps, a.warmup, a.gpus)
         if out is not None:
@@ -399,6 +470,8 @@ def main():
         out = run_gpu_single(a.steps, a.warmup)
         if not a.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline()
+        if not a.no_secondary:
+            out["secondary"] = {"gnmt": secondary_gnmt_single(min(a.steps, 40), a.warmup)}
         print(json.dumps(out))
         return
     from bench_multi import run_gpu_multi     # pipeline / hybrid partitions over NVLink peer channels

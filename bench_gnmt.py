@@ -232,6 +232,15 @@ def run_multi(gpus, steps, warmup):
     opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
                                       num_versions=r.num_warmup_minibatches + 1, lr=2e-3, weight_decay=1e-4)
     first = r.stage == 0
+    # this stage's share of the work per minibatch, for the stage roofline: every weight matrix (embedding tables
+    # aside, which are gathered, not multiplied) is used once per token forward and twice backward; Adam with an
+    # fp32 master copy moves 30 bytes per parameter, the three passes read the bf16 weights once each; an LSTM
+    # layer keeps gate activations and cell states per token for its backward pass (about 30 H bytes in all)
+    mat = sum(p.numel() for m in r.modules() for n_, p in m.named_parameters() if p.dim() >= 2 and "embed" not in n_)
+    allp = sum(p.numel() for p in r.parameters())
+    tokens = BATCH * 35.0
+    work = {"stage": r.stage, "rank": rank, "tflop": 6.0 * mat * tokens / 1e12,
+            "hbm_gb": (allp * 36.0 + mat / (8.0 * H) * tokens * 30.0 * 2) / 1e9}
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -254,8 +263,23 @@ def run_multi(gpus, steps, warmup):
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     r0 = len(s2r[0])
+    work["ms_own"] = ms / steps * len(s2r[r.stage]) / r0          # measured period per minibatch of this replica
+    sent = [n for n in r.send_ranks if n in dtypes and dtypes[n].is_floating_point]
+    work["nvlink_mb"] = 2 * sum(35.0 * BATCH * shapes[n][-1] * 2 for n in sent) / 1e6     # activations + gradients
+    works = [None] * world
+    dist.all_gather_object(works, work)
     if rank != 0:
         return None
+    pk = peaks()
+    stage_roofline = []
+    for w in sorted(works, key=lambda w: (w["stage"], w["rank"])):
+        if w["rank"] != s2r[w["stage"]][0]:
+            continue
+        t = max(w["tflop"] / pk["bf16_tflops_sustained"], w["hbm_gb"] / pk["hbm_gbs"]) + w["nvlink_mb"] / 1e3 / 770.0
+        stage_roofline.append({"stage": w["stage"], "replicas": len(s2r[w["stage"]]), "tflop_per_minibatch": round(w["tflop"], 3),
+                               "hbm_gb_per_minibatch": round(w["hbm_gb"], 3), "nvlink_mb_per_minibatch": round(w["nvlink_mb"], 1),
+                               "roofline_ms": round(t * 1e3, 3), "measured_ms": round(w["ms_own"], 3),
+                               "frac": round(t * 1e3 / w["ms_own"], 4)})
     samples = BATCH * r0 * steps
     return {
         "metric": METRIC, "value": round(samples / (tmax[0].item() * 1e-3), 2), "unit": "samples/s", "n_gpus": world,
@@ -270,6 +294,7 @@ def run_multi(gpus, steps, warmup):
                 "h2d_bytes_per_step": (dev.bytes_per_step if dev else 0) * r0, "d2h_bytes_per_step": 8 * len(s2r[max(s2r)]),
                 "ms_per_step": round(tmax[1].item() / steps, 3)},
         "gpu_launches": int(t[2].item()),
+        "stage_roofline": stage_roofline,
         "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": None, "peak": peaks()["bf16_tflops_sustained"],
                      "unit": "TFLOP/s", "frac": None, "traffic": None,
                      "note": "per-kernel figures are reported by the 1-GPU run (python bench.py --model gnmt)"},
