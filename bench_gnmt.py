@@ -275,11 +275,11 @@ def run_multi(gpus, steps, warmup):
     for w in sorted(works, key=lambda w: (w["stage"], w["rank"])):
         if w["rank"] != s2r[w["stage"]][0]:
             continue
-        t = max(w["tflop"] / pk["bf16_tflops_sustained"], w["hbm_gb"] / pk["hbm_gbs"]) + w["nvlink_mb"] / 1e3 / 770.0
+        t_s = max(w["tflop"] / pk["bf16_tflops_sustained"], w["hbm_gb"] / pk["hbm_gbs"]) + w["nvlink_mb"] / 1e3 / 770.0
         stage_roofline.append({"stage": w["stage"], "replicas": len(s2r[w["stage"]]), "tflop_per_minibatch": round(w["tflop"], 3),
                                "hbm_gb_per_minibatch": round(w["hbm_gb"], 3), "nvlink_mb_per_minibatch": round(w["nvlink_mb"], 1),
-                               "roofline_ms": round(t * 1e3, 3), "measured_ms": round(w["ms_own"], 3),
-                               "frac": round(t * 1e3 / w["ms_own"], 4)})
+                               "roofline_ms": round(t_s * 1e3, 3), "measured_ms": round(w["ms_own"], 3),
+                               "frac": round(t_s * 1e3 / w["ms_own"], 4)})
     samples = BATCH * r0 * steps
     return {
         "metric": METRIC, "value": round(samples / (tmax[0].item() * 1e-3), 2), "unit": "samples/s", "n_gpus": world,

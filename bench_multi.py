@@ -155,9 +155,9 @@ def parity_probe(r, opt, loader):
     return out
 
 
-def nvlink_peer_copy_gbs(nbytes=256 << 20):
+def nvlink_peer_copy_gbs(nbytes=1 << 30):
     """Measured once on rank 0: device-to-device copy cuda:0 -> cuda:1 with the copy engine (GB/s)."""
-    if torch.cuda.device_count() < 2:
+    if torch.cuda.device_count() < 2 or not torch.cuda.can_device_access_peer(0, 1):
         return None
     a = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0")
     b = torch.empty(nbytes, dtype=torch.uint8, device="cuda:1")
