@@ -212,18 +212,23 @@ class OptimizerWithWeightStashing:
             return [v.clone() for v in views], self.latest_version
         return views, self.latest_version
 
-    def set_params(self, version):
+    def set_params(self, state_dicts, version):
+        """Makes `version` the one the modules compute with (runtime/optimizer.py:96-108).  The reference copies
+        `state_dicts` into the modules; here the version number alone selects a slot of the ring and the
+        parameters are re-pointed at it, so `state_dicts` (what `get_params` or `queue` handed out) is not read."""
         self._point_params(self.ring.slot(version.version))
         self.current_version = version
 
     def load_old_params(self):
         if self.num_versions > 1:
-            self.set_params(Version(self.ring.oldest()))
+            v = Version(self.ring.oldest())
+            self.set_params(self._views[self.ring.slot(v.version)], v)
         self.trace.append(("load_old", self.current_version.version))
 
     def load_new_params(self):
         if self.num_versions > 1:
-            self.set_params(Version(self.ring.newest()))
+            v = Version(self.ring.newest())
+            self.set_params(self._views[self.ring.slot(v.version)], v)
         self.trace.append(("load_new", self.current_version.version))
 
     # ------------------------------------------------------------------ step

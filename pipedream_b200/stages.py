@@ -471,3 +471,71 @@ class SyntheticTokens:
             g = torch.Generator().manual_seed(self.seed + step)
             ids = torch.randint(0, self.vocab, (self.batch, self.seq_len + 1), generator=g)
             yield ids[:, :-1].contiguous(), ids[:, 1:].contiguous().view(-1)
+
+
+# --------------------------------------------------------------------------- #
+# stages from a declarative description (the form a stage generator emits)
+# --------------------------------------------------------------------------- #
+class SpecStage(nn.Module):
+    """A pipeline stage built from a description instead of a source file: the declarations
+    `[name, type, kwargs]` in order, and the dataflow `[result, op, operands...]` with op one of a declared
+    module's name, "input", "clone", "add", "size0", "flatten" - the statement kinds the reference's stage
+    generator emits (optimizer/convert_graph_to_model.py:89-356 writes them as Python source, e.g.
+    runtime/image_classification/models/resnet50/gpus=4/stage1.py:7-120).  Modules are created in declaration
+    order and initialised as the generated files do (`kaiming_normal_(fan_out)` convolutions, unit BatchNorm),
+    so under the same seed the parameters equal those of the generated stage, name for name."""
+
+    TYPES = {"Conv2d": nn.Conv2d, "BatchNorm2d": nn.BatchNorm2d, "ReLU": nn.ReLU, "MaxPool2d": nn.MaxPool2d,
+             "AvgPool2d": nn.AvgPool2d, "Linear": nn.Linear, "Dropout": nn.Dropout}
+
+    def __init__(self, spec):
+        super().__init__()
+        for name, kind, kwargs in spec["modules"]:
+            kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in kwargs.items()}
+            setattr(self, name, self.TYPES[kind](**kw))
+        self._flow = [tuple(st) for st in spec["flow"]]
+        self._returns = list(spec["returns"])
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+
+    def forward(self, *inputs):
+        v = {}
+        for st in self._flow:
+            res, op = st[0], st[1]
+            if op == "input":
+                v[res] = inputs[st[2]]
+            elif op == "clone":
+                v[res] = v[st[2]].clone()
+            elif op == "add":
+                v[res] = v[st[2]] + v[st[3]]
+            elif op == "size0":
+                v[res] = v[st[2]].size(0)
+            elif op == "flatten":
+                v[res] = v[st[2]].view(v[st[3]], -1)
+            else:
+                v[res] = getattr(self, op)(v[st[2]])
+        out = tuple(v[n] for n in self._returns)
+        return out[0] if len(out) == 1 else out
+
+
+class SpecPackage:
+    """Stage package (`arch`, `model(criterion)`, `conf`) over SpecStage descriptions:
+    {"arch": ..., "stages": [{"modules", "flow", "returns", "inputs", "outputs"}, ...]}."""
+
+    def __init__(self, description):
+        self.description = description
+        n = len(description["stages"])
+        self.conf = {"module_to_stage_map": list(range(n)) + [n - 1],
+                     "stage_to_rank_map": {s: [s] for s in range(n)}, "stage_to_depth_map": None}
+
+    def arch(self):
+        return self.description["arch"]
+
+    def model(self, criterion):
+        out = [(SpecStage(st), list(st["inputs"]), list(st["outputs"])) for st in self.description["stages"]]
+        out.append((criterion, [self.description["stages"][-1]["outputs"][0]], ["loss"]))
+        return out

@@ -7,16 +7,25 @@ the PIPEDREAM_REFERENCE environment variable:
 
 It imports the reference's runtime/ modules unmodified and records what they compute:
 
+  signatures_golden.json  constructor / method signatures of the runtime and optimizer classes the driver scripts use
   routing_golden.json   stage/rank/warm-up assignment (runtime/runtime.py:129-222) and the
                         replica routing sequences (runtime/communication.py:456-521,583-608)
                         for the stage/rank maps of the benchmark configurations
   stashing_golden.json  the weight-stashing truth table (runtime/tests/backprop/
                         sgd_with_stashing.py:57-70), per-stage version traces of the 1F1B loop
                         (runtime/optimizer.py), and a small SGD/Adam parameter trajectory
+  gnmt_pipeline_golden.json  20 minibatches of the same stage modules as the reference's real 4-stage pipeline: the
+                        reference runtime in translation mode on four gloo CPU ranks, sorted variable-length
+                        batches, AdamWithWeightStashing with 4..1 weight versions: losses, version traces, parameters
   gnmt_large_golden.json  3 minibatches of the 8+8-layer GNMT stage modules with LabelSmoothing and
                         AdamWithWeightStashing on CPU: losses, boundary-tensor and parameter checksums
   vgg16_cfg1_golden.json  20 minibatches of the 2-stage VGG-16 pipeline (cut after conv4_3) on two
                         gloo CPU ranks: per-minibatch loss, parameter checksums, version trace
+  vgg16_cfg1_f64_golden.json  the same run with the reference modules in float64 (arbitrates fp32 deviations)
+  resnet50_gpus4_golden.json  the reference's 3-stage ResNet-50 package (models.resnet50.gpus=4; two tensors
+                        cross each boundary): a description of every stage recorded from the live modules
+                        (declarations from named_children, dataflow from a torch.fx trace) and 6 minibatches
+                        of the pipeline on three gloo CPU ranks with BatchNorm in training mode
 
 Shims (monkey patches only; no reference file is modified or copied): `.cuda()` is the
 identity, `torch.cuda.set_device` is a no-op, and the optimizer wrapper's in-place weight
@@ -40,6 +49,51 @@ def _shim_cpu():
     torch.Tensor.cuda = lambda self, *a, **k: self
     torch.nn.Module.cuda = lambda self, *a, **k: self
     torch.cuda.set_device = lambda *a, **k: None
+    _shim_batchnorm()
+
+
+def _shim_batchnorm():
+    """In a pipelined stage the forward pass of minibatch i+1 runs before the backward pass of minibatch i and
+    moves BatchNorm's running statistics in place.  Current PyTorch saves those buffers with the autograd graph
+    and refuses the delayed backward ("modified by an inplace operation"); the PyTorch 1.1 the reference was
+    written for did not.  The stand-in computes the same function - normalisation by the batch statistics - with
+    the running statistics kept out of the graph and updated by the same formula (momentum, unbiased variance)."""
+    import torch.nn.functional as F
+
+    def forward(self, x):
+        if not self.training or not self.track_running_stats:
+            return F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias, self.training, 0.0, self.eps)
+        y = F.batch_norm(x, None, None, self.weight, self.bias, True, 0.0, self.eps)
+        with torch.no_grad():
+            dims = [0] + list(range(2, x.dim()))
+            m = self.momentum
+            self.running_mean.mul_(1 - m).add_(x.mean(dims), alpha=m)
+            self.running_var.mul_(1 - m).add_(x.var(dims, unbiased=True), alpha=m)
+            self.num_batches_tracked += 1
+        return y
+    torch.nn.BatchNorm2d.forward = forward
+
+
+def _shim_transport(ref_comm, float64=False):
+    """gloo in current PyTorch refuses non-contiguous tensors (the GNMT stages send transposed views); and the
+    reference marks a received activation as requiring a gradient only when it is float32
+    (runtime/communication.py:595-596), so a float64 run needs the same mark for float64."""
+    import torch.distributed as dist
+    orig_send = dist.send
+
+    def send(tensor, dst=None, group=None, tag=0, **kw):
+        return orig_send(tensor.contiguous(), dst=dst, group=group, tag=tag, **kw)
+    dist.send = send
+    ref_comm.dist.send = send
+    if float64:
+        orig_recv = ref_comm.CommunicationHandler.recv
+
+        def recv(self, tensor_name, forward_minibatch_id, backward_minibatch_id, backward=False):
+            t = orig_recv(self, tensor_name, forward_minibatch_id, backward_minibatch_id, backward=backward)
+            if not backward and t.dtype == torch.float64:
+                t = t.requires_grad_()
+            return t
+        ref_comm.CommunicationHandler.recv = recv
 
 
 def _import_reference(ref, domain="image_classification"):
@@ -49,6 +103,9 @@ def _import_reference(ref, domain="image_classification"):
     import optimizer as ref_optimizer
 
     def wrap(fn):
+        import functools
+
+        @functools.wraps(fn)
         def inner(self, *a, **k):
             params = tuple(p for m in self.modules for p in m.parameters())
             with torch.autograd._unsafe_preserve_version_counter(params):
@@ -152,6 +209,45 @@ def make_routing(ref):
     with open(os.path.join(HERE, "routing_golden.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)
     print("wrote routing_golden.json")
+
+
+# ----------------------------------------------------------------------------- interface
+def make_signatures(ref):
+    """Constructor and method signatures of the classes main_with_runtime.py uses, read off the imported reference."""
+    import inspect
+    _shim_cpu()
+    _import_reference(ref)
+    import runtime as ref_runtime
+    import sgd as ref_sgd
+    import adam as ref_adam
+    import optimizer as ref_optimizer
+
+    def sig(fn):
+        out = []
+        for name, p in inspect.signature(fn).parameters.items():
+            if name == "self":
+                continue
+            out.append([name, None if p.default is inspect.Parameter.empty else repr(p.default)])
+        return out
+
+    def methods(cls, names):
+        return {n: sig(getattr(cls, n)) for n in names}
+    out = {
+        "runtime.StageRuntime": methods(ref_runtime.StageRuntime, [
+            "__init__", "train", "eval", "set_loader", "run_forward", "run_backward", "run_ack", "wait", "num_iterations",
+            "get_adjusted_learning_rate", "state_dict", "load_state_dict", "modules", "parameters", "zero_grad", "cuda",
+            "num_tokens", "initialize", "receive_tensors_forward", "send_tensors_forward", "receive_tensors_backward",
+            "send_tensors_backward"]),
+        "runtime.constants": {k: getattr(ref_runtime, k) for k in ("IMAGE_CLASSIFICATION", "TRANSLATION", "SPEECH_TO_TEXT")},
+        "sgd.SGDWithWeightStashing": methods(ref_sgd.SGDWithWeightStashing, ["__init__"]),
+        "adam.AdamWithWeightStashing": methods(ref_adam.AdamWithWeightStashing, ["__init__"]),
+        "optimizer.OptimizerWithWeightStashing": methods(ref_optimizer.OptimizerWithWeightStashing, [
+            "__init__", "initialize_queue", "get_params", "set_params", "load_old_params", "load_new_params", "zero_grad",
+            "step"]),
+    }
+    with open(os.path.join(HERE, "signatures_golden.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+    print("wrote signatures_golden.json")
 
 
 # ----------------------------------------------------------------------------- stashing
@@ -264,15 +360,28 @@ def tensor_checksum(t):
             "samples": t[idx].tolist()}
 
 
-def vgg16_worker(ref, rank, steps, batch, out_path):
+PIPELINES = {
+    # name: (module, module_to_stage_map, ranks, lr, momentum, weight_decay)
+    "vgg16": ("models.vgg16.gpus=8", [0, 1, 1], 2, 0.01, 0.9, 5e-4),
+    "resnet50": ("models.resnet50.gpus=4", [0, 1, 2, 2], 3, 0.01, 0.9, 1e-4),
+}
+
+
+def vgg16_worker(ref, rank, steps, batch, out_path, which="vgg16", f64=False):
     _shim_cpu()
     _import_reference(ref)
     import runtime as ref_runtime
     import sgd as ref_sgd
+    import communication as ref_comm
+    _shim_transport(ref_comm, float64=f64)
     torch.manual_seed(0)
-    module = importlib.import_module("models.vgg16.gpus=8")
+    mod_name, m2s, world, lr, momentum, wd = PIPELINES[which]
+    module = importlib.import_module(mod_name)
     criterion = torch.nn.CrossEntropyLoss()
     model = module.model(criterion)
+    if f64:
+        model = [(m.double() if i < len(model) - 1 else m, a, b) for i, (m, a, b) in enumerate(model)]
+    fdt = torch.float64 if f64 else torch.float32
     for (m, _, _) in model[:-1]:
         for sub in m.modules():
             if isinstance(sub, torch.nn.Dropout):
@@ -280,13 +389,18 @@ def vgg16_worker(ref, rank, steps, batch, out_path):
     shapes = {"input0": [batch, 3, 224, 224], "target": [batch]}
     dtypes = {"input0": torch.int64, "target": torch.int64}
     for (stage, inputs, outputs) in model[:-1]:
-        ins = [torch.zeros(tuple(shapes[i]), dtype=torch.float32) for i in inputs]
+        ins = [torch.zeros(tuple(shapes[i]), dtype=fdt) for i in inputs]
+        was_training = stage.training
+        stage.eval()                       # the dry run must not move BatchNorm's running statistics
         with torch.no_grad():
             o = stage(*ins)
-        shapes[outputs[0]] = list(o.size())
-        dtypes[outputs[0]] = o.dtype
+        stage.train(was_training)
+        o = o if isinstance(o, tuple) else (o,)
+        for name, t in zip(outputs, o):
+            shapes[name] = list(t.size())
+            dtypes[name] = t.dtype
     shapes = {k: tuple(v) for k, v in shapes.items()}
-    conf = {"module_to_stage_map": [0, 1, 1], "stage_to_rank_map": {0: [0], 1: [1]}, "stage_to_depth_map": None}
+    conf = {"module_to_stage_map": m2s, "stage_to_rank_map": {s: [s] for s in range(world)}, "stage_to_depth_map": None}
     r = ref_runtime.StageRuntime(
         model=model, distributed_backend="gloo", fp16=False, loss_scale=1,
         training_tensor_shapes=shapes, eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dtypes,
@@ -294,13 +408,16 @@ def vgg16_worker(ref, rank, steps, batch, out_path):
         master_addr="127.0.0.1", rank=rank, local_rank=rank, num_ranks_in_server=1, verbose_freq=0,
         model_type=ref_runtime.IMAGE_CLASSIFICATION)
     opt = ref_sgd.SGDWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
-                                        num_versions=r.num_warmup_minibatches + 1, lr=0.01, momentum=0.9,
-                                        weight_decay=5e-4)
+                                        num_versions=r.num_warmup_minibatches + 1, lr=lr, momentum=momentum,
+                                        weight_decay=wd)
     sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
     from pipedream_b200.stages import SyntheticImages
     n = steps
     r.train(n)
-    r.set_loader(SyntheticImages(batch, n) if r.stage == 0 else None)
+    data = SyntheticImages(batch, n)
+    if f64:
+        data = [(x.double(), y) for (x, y) in data]
+    r.set_loader(data if r.stage == 0 else None)
     losses, trace = [], []
     import time
     t0 = time.time()
@@ -338,19 +455,40 @@ def vgg16_worker(ref, rank, steps, batch, out_path):
                    "seconds": elapsed, "threads": torch.get_num_threads()}, f)
 
 
-def make_vgg16(ref, steps=20, batch=8):
+def _wait_all(procs, limit_s):
+    """Waits for every worker; as soon as one fails (or the limit passes) the others are killed - a rank that
+    died leaves its peers blocked in a receive for ever."""
+    import time
+    t0 = time.time()
+    while True:
+        codes = [p.poll() for p in procs]
+        if all(c == 0 for c in codes):
+            return
+        if any(c not in (None, 0) for c in codes) or time.time() - t0 > limit_s:
+            for p in procs:
+                if p.poll() is None:
+                    p.kill()
+            raise RuntimeError("reference worker failed or timed out (exit codes %s)" % codes)
+        time.sleep(1.0)
+
+
+def run_pipeline(ref, which, steps, batch, f64=False):
+    """The reference runtime on one gloo CPU rank per stage; returns the per-rank records."""
+    world = PIPELINES[which][2]
     procs, outs = [], []
-    for rank in range(2):
-        out_path = "/tmp/vgg16_cfg1_rank%d.json" % rank
+    for rank in range(world):
+        out_path = "/tmp/%s_rank%d.json" % (which, rank)
         outs.append(out_path)
-        env = dict(os.environ, OMP_NUM_THREADS=str(max(1, (os.cpu_count() or 2) // 2)), PYTHONDONTWRITEBYTECODE="1")
-        procs.append(subprocess.Popen([sys.executable, "-O", os.path.abspath(__file__), "--ref", ref, "--worker",
-                                       str(rank), "--steps", str(steps), "--batch", str(batch), "--out", out_path],
-                                      env=env))
-    for p in procs:
-        if p.wait() != 0:
-            raise RuntimeError("reference worker failed")
-    ranks = [json.load(open(o)) for o in outs]
+        env = dict(os.environ, OMP_NUM_THREADS=str(max(1, (os.cpu_count() or 2) // world)), PYTHONDONTWRITEBYTECODE="1")
+        cmd = [sys.executable, "-O", os.path.abspath(__file__), "--ref", ref, "--worker", str(rank), "--steps", str(steps),
+               "--batch", str(batch), "--out", out_path, "--pipeline", which]
+        procs.append(subprocess.Popen(cmd + (["--f64"] if f64 else []), env=env))
+    _wait_all(procs, 1500)
+    return [json.load(open(o)) for o in outs]
+
+
+def make_vgg16(ref, steps=20, batch=8, f64=False):
+    ranks = run_pipeline(ref, "vgg16", steps, batch, f64)
     gold = {
         "config": {"module": "models.vgg16.gpus=8", "batch": batch, "steps": steps, "lr": 0.01, "momentum": 0.9,
                    "weight_decay": 5e-4, "seed": 0, "data_seed": 1234, "dropout": "disabled (p=0) on both sides"},
@@ -360,23 +498,109 @@ def make_vgg16(ref, steps=20, batch=8):
         "reference_cpu_seconds": max(r["seconds"] for r in ranks),
         "reference_cpu_threads_per_rank": ranks[0]["threads"],
     }
-    with open(os.path.join(HERE, "vgg16_cfg1_golden.json"), "w") as f:
+    name = "vgg16_cfg1_f64_golden.json" if f64 else "vgg16_cfg1_golden.json"
+    if f64:
+        gold["config"]["dtype"] = "float64"
+    with open(os.path.join(HERE, name), "w") as f:
         json.dump(gold, f, indent=1, sort_keys=True)
-    print("wrote vgg16_cfg1_golden.json; reference took %.1f s" % gold["reference_cpu_seconds"])
+    print("wrote %s; reference took %.1f s" % (name, gold["reference_cpu_seconds"]))
+
+
+# ----------------------------------------------------------------------------- ResNet-50, 3 stages
+def describe_stage(stage):
+    """Declarations and dataflow of a live stage module, in the form pipedream_b200.stages.SpecStage takes."""
+    import torch.fx
+    import operator
+    mods = []
+    for name, m in stage.named_children():
+        kind = type(m).__name__
+        if kind == "Conv2d":
+            kw = {"in_channels": m.in_channels, "out_channels": m.out_channels, "kernel_size": list(m.kernel_size),
+                  "stride": list(m.stride), "padding": list(m.padding), "bias": m.bias is not None}
+        elif kind == "BatchNorm2d":
+            kw = {"num_features": m.num_features, "eps": m.eps, "momentum": m.momentum, "affine": m.affine,
+                  "track_running_stats": m.track_running_stats}
+        elif kind == "ReLU":
+            kw = {"inplace": m.inplace}
+        elif kind == "MaxPool2d":
+            kw = {"kernel_size": m.kernel_size, "stride": m.stride, "padding": m.padding, "dilation": m.dilation,
+                  "ceil_mode": m.ceil_mode}
+        elif kind == "AvgPool2d":
+            kw = {"kernel_size": m.kernel_size, "stride": m.stride, "padding": m.padding}
+        elif kind == "Linear":
+            kw = {"in_features": m.in_features, "out_features": m.out_features, "bias": m.bias is not None}
+        else:
+            raise ValueError("unexpected module type %s" % kind)
+        mods.append([name, kind, kw])
+    g = torch.fx.symbolic_trace(stage).graph
+    flow, returns, n_in = [], [], 0
+    for node in g.nodes:
+        if node.op == "placeholder":
+            flow.append([node.name, "input", n_in])
+            n_in += 1
+        elif node.op == "call_module":
+            flow.append([node.name, node.target, node.args[0].name])
+        elif node.op == "call_method" and node.target == "clone":
+            flow.append([node.name, "clone", node.args[0].name])
+        elif node.op == "call_method" and node.target == "size":
+            assert node.args[1] == 0
+            flow.append([node.name, "size0", node.args[0].name])
+        elif node.op == "call_method" and node.target == "view":
+            assert node.args[2] == -1
+            flow.append([node.name, "flatten", node.args[0].name, node.args[1].name])
+        elif node.op == "call_function" and node.target in (operator.add, torch.add):
+            flow.append([node.name, "add", node.args[0].name, node.args[1].name])
+        elif node.op == "output":
+            res = node.args[0]
+            returns = [r.name for r in (res if isinstance(res, (tuple, list)) else (res,))]
+        else:
+            raise ValueError("unexpected node %s %s" % (node.op, node.target))
+    return {"modules": mods, "flow": flow, "returns": returns}
+
+
+def make_resnet50(ref, steps=6, batch=8):
+    _shim_cpu()
+    _import_reference(ref)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from pipedream_b200 import stages as pd_stages
+    torch.manual_seed(0)
+    module = importlib.import_module("models.resnet50.gpus=4")
+    model = module.model(torch.nn.CrossEntropyLoss())
+    desc = {"arch": module.arch(), "stages": []}
+    for (m, ins, outs) in model[:-1]:
+        d = describe_stage(m)
+        d["inputs"], d["outputs"] = list(ins), list(outs)
+        desc["stages"].append(d)
+    # the description rebuilds the package bit for bit under the same seed
+    torch.manual_seed(0)
+    mine = pd_stages.SpecPackage(desc).model(torch.nn.CrossEntropyLoss())
+    for (a, _, _), (b, _, _) in zip(model[:-1], mine[:-1]):
+        sa, sb = a.state_dict(), b.state_dict()
+        assert list(sa) == list(sb)
+        for k in sa:
+            assert torch.equal(sa[k], sb[k]), k
+    ranks = run_pipeline(ref, "resnet50", steps, batch)
+    gold = {
+        "config": {"module": "models.resnet50.gpus=4", "batch": batch, "steps": steps, "lr": 0.01, "momentum": 0.9,
+                   "weight_decay": 1e-4, "seed": 0, "data_seed": 1234, "batchnorm": "training mode"},
+        "description": desc,
+        "losses": ranks[-1]["losses"],
+        "trace": {"stage%d" % i: r["trace"] for i, r in enumerate(ranks)},
+        "params": {"stage%d" % i: r["params"] for i, r in enumerate(ranks)},
+        "reference_cpu_seconds": max(r["seconds"] for r in ranks),
+    }
+    with open(os.path.join(HERE, "resnet50_gpus4_golden.json"), "w") as f:
+        json.dump(gold, f, indent=1, sort_keys=True)
+    print("wrote resnet50_gpus4_golden.json; losses", gold["losses"], "in %.1f s" % gold["reference_cpu_seconds"])
 
 
 # ----------------------------------------------------------------------------- GNMT (8+8 layers)
-def make_gnmt(ref, steps=3, batch=8):
-    """The reference's gnmt_large stage modules (4 stages run back to back in one process), its
-    LabelSmoothing criterion and AdamWithWeightStashing, on CPU.  The reference's pack_utils CUDA
-    extension does not build against current PyTorch; a pure-torch stand-in with the semantics of
-    csrc/pack_utils_kernel.cu:24-63 and pack_utils.cpp:13-31 is injected in its place."""
+def _inject_pack_utils():
+    """Pure-torch stand-in for the reference's pack_utils CUDA extension (csrc/pack_utils_kernel.cu:24-63,
+    pack_utils.cpp:13-31), which does not build against current PyTorch."""
     import types
-    _shim_cpu()
-    _import_reference(ref, "translation")
     sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
     from pipedream_b200.gnmt_blocks import _revert_varlen_torch
-    from pipedream_b200.stages import SyntheticTranslation
     stub, c = types.ModuleType("pack_utils"), types.ModuleType("pack_utils._C")
     c.revert_varlen_tensor = lambda x, lengths: _revert_varlen_torch(x, lengths)
 
@@ -386,6 +610,130 @@ def make_gnmt(ref, steps=3, batch=8):
     c.set_mask_cpp = set_mask_cpp
     stub._C = c
     sys.modules["pack_utils"], sys.modules["pack_utils._C"] = stub, c
+
+
+GNMT_PIPE = {"batch": 8, "min_len": 6, "max_len": 14, "lr": 2e-3, "weight_decay": 1e-4, "data_seed": 4321}
+
+
+def gnmt_worker(ref, rank, steps, out_path):
+    """One rank of the reference's 4-stage GNMT pipeline (models.gnmt_large.gpus=4, one stage per rank) through the
+    reference runtime in its translation mode: variable-length batches sorted by source length, LabelSmoothing,
+    AdamWithWeightStashing with 4, 3, 2, 1 weight versions from the first to the last stage."""
+    _shim_cpu()
+    _import_reference(ref, "translation")
+    _inject_pack_utils()
+    import runtime as ref_runtime
+    import adam as ref_adam
+    import communication as ref_comm
+    _shim_transport(ref_comm)
+    from seq2seq.train.smoothing import LabelSmoothing
+    from pipedream_b200.stages import SyntheticTranslation
+    cfg = GNMT_PIPE
+    torch.manual_seed(0)
+    module = importlib.import_module("models.gnmt_large.gpus=4")
+    model = module.model(LabelSmoothing(0, 0.1))
+    for (m, _, _) in model[:-1]:
+        for sub in m.modules():
+            if isinstance(sub, torch.nn.Dropout):
+                sub.p = 0.0
+    B, T = cfg["batch"], cfg["max_len"]
+    shapes = {"input0": [T, B], "input1": [B], "input2": [T, B], "target": [T * B], "target_length": [B]}
+    dtypes = {"input0": torch.int64, "input1": torch.int64, "input2": torch.int64, "target": torch.int64,
+              "target_length": torch.int32}
+    dests = {"input0": 0, "input1": 0, "input2": 0}
+    for module_id, (stage, inputs, outputs) in enumerate(model[:-1]):        # translation/main_with_runtime.py:161-184
+        ins = []
+        for name in inputs:
+            if name in dests:
+                dests[name] = module_id
+            ins.append(torch.ones(tuple(shapes[name]), dtype=dtypes[name]))
+        with torch.no_grad():
+            o = stage(*ins)
+        o = o if isinstance(o, tuple) else (o,)
+        for name, t in zip(outputs, o):
+            shapes[name] = list(t.size())
+            dtypes[name] = t.dtype
+    shapes = {k: tuple(v) for k, v in shapes.items()}
+    conf = {"module_to_stage_map": [0, 1, 2, 3, 3], "stage_to_rank_map": {s: [s] for s in range(4)}, "stage_to_depth_map": None}
+    r = ref_runtime.StageRuntime(
+        model=model, distributed_backend="gloo", fp16=False, loss_scale=1, training_tensor_shapes=shapes,
+        eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dtypes, inputs_module_destinations=dests,
+        target_tensor_names={"target", "target_length"}, configuration_maps=conf, master_addr="127.0.0.1",
+        rank=rank, local_rank=rank, num_ranks_in_server=1, verbose_freq=0, model_type=ref_runtime.TRANSLATION)
+    opt = ref_adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
+                                          num_versions=r.num_warmup_minibatches + 1, lr=cfg["lr"],
+                                          weight_decay=cfg["weight_decay"])
+    n = steps
+    r.train(n)
+    r.set_loader(SyntheticTranslation(B, n, seed=cfg["data_seed"], min_len=cfg["min_len"], max_len=cfg["max_len"])
+                 if r.stage == 0 else None)
+    losses, trace = [], []
+
+    def bwd(i):
+        opt.zero_grad()
+        opt.load_old_params()
+        trace.append(["B", i, opt.current_version.version if opt.num_versions > 1 else opt.latest_version.version])
+        r.run_backward()
+        opt.load_new_params()
+        opt.step()
+
+    w = r.num_warmup_minibatches
+    for i in range(w):
+        trace.append(["F", i, opt.latest_version.version])
+        r.run_forward()
+    for i in range(n - w):
+        trace.append(["F", w + i, opt.latest_version.version])
+        r.run_forward()
+        if r.stage == r.num_stages - 1:
+            losses.append([float(r.tensors[-1]["loss"]), float(r.loss)])
+        bwd(i)
+    for i in range(w):
+        bwd(n - w + i)
+    r.wait()
+    params = {}
+    for mi, m in enumerate(r.modules()):
+        for k, v in m.state_dict().items():
+            if v is not None:
+                params["module%d.%s" % (mi, k)] = tensor_checksum(v)
+    with open(out_path, "w") as f:
+        json.dump({"rank": rank, "stage": r.stage, "num_versions": opt.num_versions, "losses": losses, "trace": trace,
+                   "params": params, "shapes": {k: list(v) for k, v in shapes.items()},
+                   "dtypes": {k: str(v) for k, v in dtypes.items()}, "inputs_module_destinations": dests}, f)
+
+
+def make_gnmt_pipeline(ref, steps=20):
+    import time
+    t0 = time.time()
+    procs, outs = [], []
+    for rank in range(4):
+        out_path = "/tmp/gnmt_pipe_rank%d.json" % rank
+        outs.append(out_path)
+        env = dict(os.environ, OMP_NUM_THREADS=str(max(1, (os.cpu_count() or 4) // 4)), PYTHONDONTWRITEBYTECODE="1")
+        procs.append(subprocess.Popen([sys.executable, "-O", os.path.abspath(__file__), "--ref", ref, "--worker", str(rank),
+                                       "--steps", str(steps), "--out", out_path, "--pipeline", "gnmt"], env=env))
+    _wait_all(procs, 1500)
+    ranks = [json.load(open(o)) for o in outs]
+    gold = {"config": dict(GNMT_PIPE, module="models.gnmt_large.gpus=4", steps=steps, seed=0, smoothing=0.1,
+                           optimizer="Adam", dropout="disabled (p=0)", num_versions=[r["num_versions"] for r in ranks],
+                           inputs_module_destinations=ranks[0]["inputs_module_destinations"]),
+            "losses": [x[0] for x in ranks[3]["losses"]], "losses_per_token": [x[1] for x in ranks[3]["losses"]],
+            "trace": {"stage%d" % i: r["trace"] for i, r in enumerate(ranks)},
+            "params": {"stage%d" % i: r["params"] for i, r in enumerate(ranks)},
+            "shapes": ranks[0]["shapes"], "dtypes": ranks[0]["dtypes"], "reference_cpu_seconds": time.time() - t0}
+    with open(os.path.join(HERE, "gnmt_pipeline_golden.json"), "w") as f:
+        json.dump(gold, f, indent=1, sort_keys=True)
+    print("wrote gnmt_pipeline_golden.json; losses", [round(x, 3) for x in gold["losses"]], "in %.1f s" % gold["reference_cpu_seconds"])
+
+
+def make_gnmt(ref, steps=3, batch=8):
+    """The reference's gnmt_large stage modules (4 stages run back to back in one process), its
+    LabelSmoothing criterion and AdamWithWeightStashing, on CPU.  The reference's pack_utils CUDA
+    extension does not build against current PyTorch; a pure-torch stand-in with the semantics of
+    csrc/pack_utils_kernel.cu:24-63 and pack_utils.cpp:13-31 is injected in its place."""
+    _shim_cpu()
+    _import_reference(ref, "translation")
+    _inject_pack_utils()
+    from pipedream_b200.stages import SyntheticTranslation
     import adam as ref_adam
     from seq2seq.train.smoothing import LabelSmoothing
     torch.manual_seed(0)
@@ -440,18 +788,32 @@ if __name__ == "__main__":
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--pipeline", default="vgg16")
+    ap.add_argument("--f64", action="store_true")
     a = ap.parse_args()
-    if a.worker is not None:
-        vgg16_worker(a.ref, a.worker, a.steps, a.batch, a.out)
+    if a.worker is not None and a.pipeline == "gnmt":
+        gnmt_worker(a.ref, a.worker, a.steps, a.out)
+    elif a.worker is not None:
+        vgg16_worker(a.ref, a.worker, a.steps, a.batch, a.out, a.pipeline, a.f64)
     else:
         if a.only in (None, "routing"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_routing(%r)" % (HERE, a.ref)])
+        if a.only in (None, "signatures"):
+            subprocess.check_call([sys.executable, "-O", "-c",
+                                   "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_signatures(%r)" % (HERE, a.ref)])
         if a.only in (None, "stashing"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_stashing(%r)" % (HERE, a.ref)])
         if a.only in (None, "vgg16"):
             make_vgg16(a.ref, a.steps, a.batch)
+        if a.only in (None, "vgg16_f64"):
+            make_vgg16(a.ref, a.steps, a.batch, f64=True)
+        if a.only in (None, "resnet50"):
+            subprocess.check_call([sys.executable, "-O", "-c",
+                                   "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_resnet50(%r)" % (HERE, a.ref)])
+        if a.only in (None, "gnmt_pipeline"):
+            make_gnmt_pipeline(a.ref, a.steps)
         if a.only in (None, "gnmt"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_gnmt(%r)" % (HERE, a.ref)])

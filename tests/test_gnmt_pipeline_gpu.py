@@ -1,0 +1,90 @@
+"""GNMT (8+8 layers) as the reference's real 4-stage pipeline: tests/golden/gnmt_pipeline_golden.json holds 20
+minibatches of models.gnmt_large.gpus=4 through the reference runtime in translation mode on four gloo CPU ranks -
+sorted variable-length batches, LabelSmoothing(0.1), AdamWithWeightStashing with 4, 3, 2, 1 weight versions from the
+first stage to the last (runtime/translation/main_with_runtime.py:146-230, runtime/optimizer.py:19-164).
+
+Here the same four stages run natively as a 4-stage pipeline on one GPU, with the boundary tensors of the reference
+(two activations plus the forwarded lengths and decoder inputs between the encoder stages, three between the decoder
+stages).  Bars: weight-version traces exact; losses within 1e-3 relative in fp32 and 2e-2 in bf16 for the first
+minibatches, and within 5e-3 / 4e-2 over all 20 (Adam turns last-bit gradient differences into lr-sized steps, so the
+runs drift apart slowly); parameters' absolute sums within 1e-3 / 2e-2."""
+import json
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from pipedream_b200 import adam, communication, gnmt_blocks, runtime, schedule, stages  # noqa: E402
+from pipedream_b200 import functional as pf                                            # noqa: E402
+import pipeline_util as pu                                                             # noqa: E402
+
+GOLD = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gnmt_pipeline_golden.json")))
+_DT = {"torch.int64": torch.int64, "torch.int32": torch.int32, "torch.float32": torch.float32}
+
+
+def build(fp16):
+    cfg = GOLD["config"]
+    schedule.reset_local()
+    shapes = {k: tuple(v) for k, v in GOLD["shapes"].items()}
+    dtypes = {k: _DT[v] for k, v in GOLD["dtypes"].items()}          # float32 throughout, as the driver records them
+    conf = {"module_to_stage_map": [0, 1, 2, 3, 3], "stage_to_rank_map": {s: [s] for s in range(4)}, "stage_to_depth_map": None}
+    workers = []
+    for rank in range(4):
+        torch.manual_seed(cfg["seed"])
+        model = stages.gnmt_large().model(gnmt_blocks.LabelSmoothing(0, cfg["smoothing"]))
+        pu.disable_dropout(model)
+        r = runtime.StageRuntime(
+            model=model, distributed_backend=communication.LOCAL, fp16=fp16, loss_scale=1, training_tensor_shapes=dict(shapes),
+            eval_tensor_shapes=dict(shapes), training_tensor_dtypes=dict(dtypes),
+            inputs_module_destinations=dict(cfg["inputs_module_destinations"]),
+            target_tensor_names={"target", "target_length"}, configuration_maps=conf, master_addr="127.0.0.1", rank=rank,
+            local_rank=0, num_ranks_in_server=1, verbose_freq=0, model_type=runtime.TRANSLATION)
+        opt = adam.AdamWithWeightStashing(r.modules(), r.master_parameters, r.model_parameters, 1,
+                                          num_versions=r.num_warmup_minibatches + 1, lr=cfg["lr"],
+                                          weight_decay=cfg["weight_decay"])
+        workers.append((r, opt))
+    return schedule.LocalPipeline(workers), cfg
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_gnmt_four_stage_pipeline_matches_reference_run(fp16):
+    pipe, cfg = build(fp16)
+    assert [o.num_versions for (_, o) in pipe.workers] == cfg["num_versions"] == [4, 3, 2, 1]
+    n = cfg["steps"]
+    pipe.workers[0][0].set_loader(stages.SyntheticTranslation(cfg["batch"], n, seed=cfg["data_seed"], min_len=cfg["min_len"],
+                                                              max_len=cfg["max_len"]))
+    for (r, _) in pipe.workers[1:]:
+        r.set_loader(None)
+    raw, per_token = [], []
+
+    def on_loss(k, i, r):
+        raw.append(float(r.tensors[-1]["loss"]))
+        per_token.append(float(r.loss))
+    pipe.run([n] * 4, on_loss=on_loss)
+    torch.cuda.synchronize()
+    assert pf.gemm_poll_error() == 0
+    early, late = (2e-2, 4e-2) if fp16 else (1e-3, 5e-3)
+    rel = [abs(a - b) / abs(b) for a, b in zip(raw, GOLD["losses"])]
+    relt = [abs(a - b) / abs(b) for a, b in zip(per_token, GOLD["losses_per_token"])]
+    print("relative loss differences:", ["%.1e" % x for x in rel])
+    assert len(raw) == n
+    assert max(rel[:5]) <= early and max(relt[:5]) <= early, rel
+    assert max(rel) <= late and max(relt) <= late, rel
+    for s, (_, opt) in enumerate(pipe.workers):
+        ref = [e for e in GOLD["trace"]["stage%d" % s] if e[0] == "B"]
+        got = [["B", i, v] for i, (_, v) in enumerate([e for e in opt.trace if e[0] == "load_old"])]
+        assert got == ref, s
+    ptol = 2e-2 if fp16 else 1e-3
+    worst, worst_name = 0.0, None
+    for s, (r, _) in enumerate(pipe.workers):
+        got = pu.param_checksums(r)
+        for name, ref in GOLD["params"]["stage%d" % s].items():
+            if name not in got or (fp16 and name.endswith("normalize_bias")):
+                continue        # (zero-initialised and moved by +-lr steps of Adam: not comparable in bf16)
+            e = abs(got[name]["abs_sum"] - ref["abs_sum"]) / max(ref["abs_sum"], 1e-9)
+            if e > worst:
+                worst, worst_name = e, name
+    print("largest relative difference of a parameter's absolute sum: %.2e (%s)" % (worst, worst_name))
+    assert worst <= ptol, worst_name

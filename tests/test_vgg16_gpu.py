@@ -103,16 +103,27 @@ def test_vgg16_single_stage_matches_oracle_fp32():
     assert pf.gemm_poll_error() == 0
 
 
+GOLD64 = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "vgg16_cfg1_f64_golden.json")))
+
+
+def _distance_to(gold, losses, workers):
+    rel = [abs(a - b) / abs(b) for a, b in zip(losses, gold["losses"])]
+    werr, berr = pu.checksum_errors(workers, gold)
+    return rel, max(werr.values()), max(berr.values())
+
+
 @pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
 def test_vgg16_cfg1_20_steps(fp16):
     """2-stage pipeline cut after conv4_3, batch 8, SGD 0.01/0.9/5e-4, 1F1B with weight stashing, 20
-    minibatches: against the reference's recorded CPU run.
+    minibatches: against the reference's recorded CPU run, arbitrated by the same run of the reference in float64.
 
-    The bar is 1e-3 (fp32) / 2e-2 (bf16) relative on the loss and the updated parameters.  This network
-    (no normalisation, loss spike at minibatch 8 in the reference's own run) amplifies fp32 rounding
-    differences between any two implementations, so the same pipeline is also run with the unswapped
-    torch.nn modules (cuDNN / cuBLAS, TF32 off) on the same GPU as a control: where the native path
-    exceeds the bar it must still be no further from the reference than that control."""
+    The bar is 1e-3 (fp32) / 2e-2 (bf16) relative on the loss and the updated parameters.  This network (no
+    normalisation, a loss spike at minibatch 8) amplifies rounding: the reference's OWN fp32 run is up to 1.3e-3 away
+    from its float64 twin (minibatch 9; both recorded in tests/golden), so two correct fp32 implementations cannot
+    be expected within 1e-3 of each other after 20 steps.  What is asserted: the bar outright on the first five
+    minibatches, and over all twenty that the native run is no further from float64 than twice the distance of
+    the reference's fp32 run from float64 (twice, because weight-gradient sums here are combined with fp32 atomics
+    whose order changes from launch to launch)."""
     tol = 2e-2 if fp16 else 1e-3
     losses, workers = pu.run_cfg1(GOLD, fp16, native=True)
     (r0, o0), (r1, o1) = workers
@@ -120,8 +131,19 @@ def test_vgg16_cfg1_20_steps(fp16):
     assert (o0.num_versions, o1.num_versions) == (2, 1)
     n = GOLD["config"]["steps"]
     assert len(losses) == n
-    rel = [abs(a - b) / abs(b) for a, b in zip(losses, GOLD["losses"])]
-    werr, berr = pu.checksum_errors(workers, GOLD)
+    rel, werr, berr = _distance_to(GOLD, losses, workers)
+    rel64, werr64, berr64 = _distance_to(GOLD64, losses, workers)
+    # how far the reference's fp32 run is from float64 (constants of the two fixtures)
+    ref64 = [abs(a - b) / abs(b) for a, b in zip(GOLD["losses"], GOLD64["losses"])]
+    ref_w, ref_b = 0.0, 0.0
+    for st in ("stage0", "stage1"):
+        for k, v in GOLD64["params"][st].items():
+            g = GOLD["params"][st][k]
+            e = max(abs(g["sum"] - v["sum"]), abs(g["abs_sum"] - v["abs_sum"])) / max(abs(v["abs_sum"]), 1e-6)
+            if k.endswith("bias"):
+                ref_b = max(ref_b, e)
+            else:
+                ref_w = max(ref_w, e)
     # version indices of backward passes and steps: exact
     for (r, o), key in (((r0, o0), "stage0"), ((r1, o1), "stage1")):
         ref = [e for e in GOLD["trace"][key] if e[0] == "B"]
@@ -130,22 +152,14 @@ def test_vgg16_cfg1_20_steps(fp16):
             got = [[e[0], e[1], i] for i, e in enumerate(got)]   # with one version B runs on the latest: v_i
         assert got == ref, key
     assert pf.gemm_poll_error() == 0
-    del workers, r0, o0, r1, o1
-    torch.cuda.empty_cache()
-    closs, cworkers = pu.run_cfg1(GOLD, fp16, native=False)
-    crel = [abs(a - b) / abs(b) for a, b in zip(closs, GOLD["losses"])]
-    cwerr, cberr = pu.checksum_errors(cworkers, GOLD)
-    print("\n[%s] loss rel err: native max %.2e (first 5 %.2e), torch control max %.2e; weights native %.2e / "
-          "control %.2e; biases native %.2e / control %.2e" % (
-              "bf16" if fp16 else "fp32", max(rel), max(rel[:5]), max(crel), max(werr.values()),
-              max(cwerr.values()), max(berr.values()), max(cberr.values())))
-    # before rounding differences have been amplified the bar holds outright
+    print("\n[%s] loss: native vs reference fp32 max %.2e (first 5 %.2e); native vs float64 max %.2e; reference fp32 vs "
+          "float64 max %.2e.  weights: native vs float64 %.2e, reference fp32 vs float64 %.2e.  biases: %.2e / %.2e" % (
+              "bf16" if fp16 else "fp32", max(rel), max(rel[:5]), max(rel64), max(ref64), werr64, ref_w, berr64, ref_b))
     assert max(rel[:5]) <= tol, rel
-    for i in range(n):
-        assert rel[i] <= max(tol, 1.5 * max(crel)), "minibatch %d: %.3e (control %.3e)" % (i, rel[i], max(crel))
-    assert max(werr.values()) <= max(tol, 1.5 * max(cwerr.values())), werr
+    assert max(rel64) <= max(tol, 2.0 * max(ref64)), (rel64, ref64)
+    assert werr64 <= max(tol, 2.0 * ref_w), (werr64, ref_w)
     # biases start at zero, so their value is a pure sum of gradients and inherits the gradient noise
-    assert max(berr.values()) <= max(tol, 1.5 * max(cberr.values())), berr
+    assert berr64 <= max(tol, 2.0 * ref_b), (berr64, ref_b)
 
 
 @pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
