@@ -364,6 +364,99 @@ def secondary_gnmt_single(steps, warmup):
     return out
 
 
+def run_profile_case_other(name):
+    """A few launches of one of the memory-bound kernels on a case that exceeds L2 but stays under 1 GB, for `ncu`
+    captures; prints the kernel's algorithmic bytes per launch (what its roofline fraction is measured against):
+    sgd / adam : the fused optimizer over a 2-version ring, 64 M bf16 parameters with fp32 master copy;
+    softmax_ce : criterion forward + backward on [6400, 32320] bf16 logits (GNMT: 50 steps x 128 pairs);
+    bn         : BatchNorm2d training forward + backward on a padded-NHWC [64, 58, 58, 256] bf16 tensor;
+    layernorm  : LayerNorm forward + backward on [65536, 1024] bf16 rows;
+    lstm       : one LSTM layer's recurrence, T = 50, B = 128, H = 1024, forward + backward;
+    attn       : normalised additive attention forward + backward, B = 128, Tq = Tk = 50, 1024 channels."""
+    import ctypes
+    from pipedream_b200 import functional as pf
+    from pipedream_b200._lib import call
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(0)
+    bf = torch.bfloat16
+    info = {"case": name}
+    if name in ("sgd", "adam"):
+        n, V = 64 * 1024 * 1024, 2
+        arena = torch.zeros(V, n, device="cuda", dtype=bf)
+        master = torch.randn(n, device="cuda") * 0.01
+        grad = torch.randn(n, device="cuda") * 0.01
+        sa, sb = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+        for i in range(4):
+            if name == "sgd":
+                call("pd_opt_sgd_multi_tensor", p(arena), n, i % 2, (i + 1) % 2, 1, p(master), p(grad), p(sa), n, 0.01, 0.9, 0.0,
+                     5e-4, 0, int(i == 0), 1.0, st)
+            else:
+                call("pd_opt_adam_multi_tensor", p(arena), n, i % 2, (i + 1) % 2, 1, p(master), p(grad), p(sa), p(sb), n, 2e-3,
+                     0.9, 0.999, 1e-8, 1e-4, i + 1, 1.0, st)
+        # read gradient, master (and the moments); write master, moments and the bf16 weights of the new version
+        info["algorithmic_bytes_per_launch"] = n * (4 + 4 + 4 + 4 + 4 + 2) if name == "sgd" else n * (4 + 4 + 4 + 4 + 4 + 4 + 4 + 2)
+    elif name == "softmax_ce":
+        rows, C = 6400, 32320
+        logits = (torch.randn(rows, C, generator=g) * 2).cuda().to(bf)
+        target = torch.randint(1, C, (rows,), generator=g).cuda()
+        up = torch.ones((), device="cuda")
+        for _ in range(3):
+            loss, lse, _ = pf.softmax_ce_fwd(logits, target, 0.1, 0, 1.0)
+            pf.softmax_ce_bwd(logits, target, lse, 0.1, 0, up, 1.0)
+        info["algorithmic_bytes_per_launch"] = {"forward (read logits)": rows * C * 2, "backward (read logits, write gradient)": rows * C * 4}
+    elif name == "bn":
+        N, H, C = 64, 56, 256
+        x = pf.pack_pnhwc(torch.randn(N, C, H, H, generator=g).cuda().to(bf))
+        dy = pf.pack_pnhwc(torch.randn(N, C, H, H, generator=g).cuda().to(bf))
+        gamma, beta = torch.ones(C, device="cuda", dtype=bf), torch.zeros(C, device="cuda", dtype=bf)
+        rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+        dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+        for _ in range(3):
+            y, mean, invstd = pf.bn_fwd(x, gamma, beta, 1e-5, 0.1, True, rm, rv)
+            pf.bn_bwd(x, dy, y, gamma, mean, invstd, dg, db, False)
+        info["algorithmic_bytes_per_launch"] = {"tensor": x.numel() * 2, "forward": "read x twice, write y", "backward": "read x, dy, y twice, write dx"}
+    elif name == "layernorm":
+        rows, C = 65536, 1024
+        x = torch.randn(rows, C, generator=g).cuda().to(bf)
+        dy = torch.randn(rows, C, generator=g).cuda().to(bf)
+        gamma, beta = torch.ones(C, device="cuda", dtype=bf), torch.zeros(C, device="cuda", dtype=bf)
+        dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+        for _ in range(3):
+            y, mean, rstd = pf.layernorm_fwd(x, gamma, beta, 1e-5)
+            pf.layernorm_bwd(x, dy, gamma, mean, rstd, dg, db, False)
+        info["algorithmic_bytes_per_launch"] = {"forward": rows * C * 4, "backward": rows * C * 6}
+    elif name == "lstm":
+        T, B, H = 50, 128, 1024
+        gx = (torch.randn(T, B, 4 * H, generator=g) * 0.1).cuda().to(bf)
+        w = (torch.randn(4 * H, H, generator=g) * 0.03).cuda().to(bf)
+        b = torch.zeros(4 * H, device="cuda", dtype=bf)
+        dyy = (torch.randn(T, B, H, generator=g) * 0.1).cuda().to(bf)
+        for _ in range(2):
+            y, act, c_all = pf.lstm_fwd(gx, w, b, T, B, H)
+            pf.lstm_bwd(dyy, w, act, c_all)
+        info["algorithmic_flop_per_launch"] = 2.0 * (T - 1) * B * 4 * H * H
+        info["steps"] = T
+    elif name == "attn":
+        B, T, n = 128, 50, 1024
+        pq = (torch.randn(B, T, n, generator=g) * 0.3).cuda().to(bf)
+        pk = (torch.randn(B, T, n, generator=g) * 0.3).cuda().to(bf)
+        keys = (torch.randn(T, B, n, generator=g) * 0.3).cuda().to(bf)
+        v = (torch.randn(n, generator=g) * 0.05).cuda()
+        nb = torch.zeros(n, device="cuda", dtype=bf)
+        lens = torch.full((B,), T, dtype=torch.int64, device="cuda")
+        dctx = (torch.randn(T, B, n, generator=g) * 0.1).cuda().to(bf)
+        for _ in range(2):
+            probs, ctx = pf.attn_fwd(pq, pk, keys, v, nb, lens)
+            pf.attn_bwd(pq, pk, keys, v, nb, probs, dctx)
+        info["tanh_per_pass"] = B * T * T * n
+    else:
+        raise ValueError(name)
+    torch.cuda.synchronize()
+    print(json.dumps(info))
+
+
 def run_profile_case(name):
     """A few launches of one contraction at one layer shape, for `ncu` captures of the tensor-core kernel on
     a case that is larger than L2 but well under 1 GB:
@@ -421,9 +514,14 @@ def main():
                     help="skip the GNMT run that the default line carries under \"secondary\"")
     ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50", "gpt"],
                     help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT), resnet50 or gpt (24-layer 2BW decoder)")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd"],
-                    help="run a few launches of one convolution pass (for ncu) and exit")
+    ap.add_argument("--profile-case", default=None,
+                    choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd", "sgd", "adam", "softmax_ce", "bn",
+                             "layernorm", "lstm", "attn"],
+                    help="run a few launches of one kernel family on a small case (for ncu) and exit")
     a = ap.parse_args()
+    if a.profile_case in ("sgd", "adam", "softmax_ce", "bn", "layernorm", "lstm", "attn"):
+        run_profile_case_other(a.profile_case)
+        return
     if a.profile_case:
         run_profile_case(a.profile_case)
         return

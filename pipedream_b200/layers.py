@@ -51,9 +51,14 @@ def _mark_native(*params):
 
 
 def take_accumulate_flag(param):
-    """False on the first gradient write after zero_grad (store), True afterwards (accumulate)."""
+    """False on the first gradient write after zero_grad (store), True afterwards (accumulate).  Called right
+    before the kernel that writes the gradient is enqueued; a replicated stage listens here to learn how far the
+    backward pass has come (StageRuntime's GradientAverager)."""
     acc = getattr(param, "_pd_acc", False)
     param._pd_acc = True
+    hook = getattr(param, "_pd_grad_hook", None)
+    if hook is not None:
+        hook(param)
     return acc
 
 

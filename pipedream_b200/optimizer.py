@@ -124,6 +124,8 @@ class OptimizerWithWeightStashing:
                 self._grad_sync = sync
         self._build_arena()
         self.initialize_queue()
+        if self._grad_sync is not None and hasattr(self._grad_sync, "bind"):
+            self._grad_sync.bind(self)         # bucketed, backward-overlapped reduction needs the arena layout
         for m in modules:
             rt = getattr(m, "_pd_runtime", None)
             rt = rt() if rt is not None else None

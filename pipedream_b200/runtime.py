@@ -714,13 +714,113 @@ class StageRuntime:
 class GradientAverager:
     """Sums a stage's flat fp32 gradient arena over its replicas; returns the factor that turns the sum into
     the mean (the optimizer folds it into the gradient scale of its fused kernel).  Stands where the
-    reference wraps the stage in DistributedDataParallel (runtime/runtime.py:232-262)."""
+    reference wraps the stage in DistributedDataParallel (runtime/runtime.py:232-262) and, like it, reduces in
+    buckets while the backward pass is still running:
 
-    def __init__(self, group, world):
+    * the arena is cut into contiguous buckets of about `bucket_bytes`; parameters are laid out in forward order,
+      so the backward pass finishes the buckets from the last to the first;
+    * every native layer announces a gradient write just before it enqueues the writing kernel; when a bucket's last
+      parameter has been announced and the NEXT announcement arrives (so the writing kernel is in the stream), an
+      event is recorded and the bucket's all-reduce is issued on a side stream behind that event;
+    * `__call__` (from the optimizer's step) issues whatever is left and makes the compute stream wait for the
+      side stream - only the last bucket's reduction is exposed.
+
+    The first minibatch runs as one blocking all-reduce while the announcements are counted: a parameter that is
+    written more than once per backward pass (shared between two layers of the stage) would be reduced too early,
+    so a stage with such a parameter keeps the blocking form.  Gradient accumulation over several minibatches
+    (`update_interval` > 1) keeps it as well."""
+
+    def __init__(self, group, world, bucket_bytes=32 << 20):
         self.group, self.world = group, world
+        self.bucket_bytes = bucket_bytes
+        self.opt = None
+        self.mode = "learn"            # learn -> overlap | blocking
+        self.counts = {}
+        self.stream = None
 
+    # -- set-up ------------------------------------------------------------------------------------------
+    def bind(self, optimizer):
+        """Called by the optimizer once its arena exists."""
+        self.opt = optimizer
+        if self.group is None or optimizer.update_interval != 1 or optimizer.grad_arena.device.type != "cuda":
+            self.mode = "blocking"
+            return
+        for p in optimizer.master_parameters:
+            p._pd_grad_hook = self._announce
+
+    def _plan(self):
+        opt = self.opt
+        self.bucket_of, self.buckets = {}, []
+        lo, members = None, []
+        for p, (off, span) in zip(opt.master_parameters, opt._offsets):
+            if lo is None:
+                lo = off
+            members.append(p)
+            end = (off + span + 63) // 64 * 64
+            if (end - lo) * 4 >= self.bucket_bytes:
+                self.buckets.append({"lo": lo, "hi": end, "members": members})
+                lo, members = None, []
+        if members:
+            end = (opt._offsets[-1][0] + opt._offsets[-1][1] + 63) // 64 * 64
+            self.buckets.append({"lo": lo, "hi": end, "members": members})
+        for b in self.buckets:
+            for p in b["members"]:
+                self.bucket_of[id(p)] = b
+        self.stream = torch.cuda.Stream(device=opt.grad_arena.device)
+        self._reset()
+
+    def _reset(self):
+        for b in self.buckets:
+            b["left"] = len(b["members"])
+            b["sent"] = False
+        self.previous = None
+
+    # -- backward pass -----------------------------------------------------------------------------------
+    def _announce(self, param):
+        if self.mode == "learn":
+            self.counts[id(param)] = self.counts.get(id(param), 0) + 1
+            return
+        if self.mode != "overlap":
+            return
+        prev, self.previous = self.previous, param
+        if prev is not None:
+            b = self.bucket_of[id(prev)]
+            b["left"] -= 1
+            if b["left"] == 0:
+                self._send(b)
+
+    def _send(self, b):
+        if b["sent"]:
+            return
+        b["sent"] = True
+        arena = self.opt.grad_arena
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(arena.device))
+        self.stream.wait_event(ev)
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(arena[b["lo"]:b["hi"]], op=dist.ReduceOp.SUM, group=self.group)
+
+    # -- optimizer step ----------------------------------------------------------------------------------
     def __call__(self, grad_arena):
         if self.group is None:
             return 1.0
+        if self.mode == "overlap":
+            for b in self.buckets:
+                self._send(b)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+            torch.cuda.current_stream(grad_arena.device).wait_event(done)
+            self._reset()
+            return 1.0 / self.world
         dist.all_reduce(grad_arena, op=dist.ReduceOp.SUM, group=self.group)
+        if self.mode == "learn" and self.opt is None:
+            self.mode = "blocking"         # used without an arena (no optimizer bound): nothing to bucket
+        if self.mode == "learn":
+            once = all(c == 1 for c in self.counts.values())
+            # every replica must take the same decision: they all run the same stage code, but be explicit
+            flag = torch.tensor([1 if once else 0], device=grad_arena.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            self.mode = "overlap" if int(flag.item()) == 1 else "blocking"
+            if self.mode == "overlap":
+                self._plan()
         return 1.0 / self.world
