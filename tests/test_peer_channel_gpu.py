@@ -107,7 +107,7 @@ def test_channel_size_mismatch_is_an_error():
         call("pd_chan_close", ch)
 
 
-def _pipeline_worker(rank, world, port, out_dir, fp16):
+def _pipeline_worker(rank, world, port, out_dir, fp16, reference_dtypes=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["PIPEDREAM_MASTER_PORT"] = str(port)
@@ -122,7 +122,8 @@ def _pipeline_worker(rank, world, port, out_dir, fp16):
     conf = dict(pkg.conf)
     conf["stage_to_depth_map"] = None
     r, opt = pu.make_worker(pkg, conf, rank, cfg["batch"], fp16, "p2p", lr=cfg["lr"], momentum=cfg["momentum"],
-                            weight_decay=cfg["weight_decay"], seed=cfg["seed"], local_rank=rank)
+                            weight_decay=cfg["weight_decay"], seed=cfg["seed"], local_rank=rank,
+                            reference_dtypes=reference_dtypes)
     n = cfg["steps"]
     r.train(n)
     r.set_loader(stages.SyntheticImages(cfg["batch"], n, seed=cfg["data_seed"]) if r.stage == 0 else None)
@@ -153,6 +154,20 @@ def test_two_stage_pipeline_over_peer_channels(fp16, tmp_path):
     for rank in (0, 1):
         g = json.load(open(os.path.join(str(tmp_path), "rank%d.json" % rank)))
         assert g["werr"] <= max(tol, 5e-3), g
+
+
+def test_sixteen_bit_pipeline_with_the_drivers_float32_dtype_table(tmp_path):
+    """The reference's driver scripts record float32 for every boundary tensor even when they run with --fp16
+    (main_with_runtime.py:139-155).  The stages then push bf16; the receiver must allocate and copy bf16 too (a
+    float32 receive of twice the bytes would reinterpret the payload - and now fails the channel on the byte count)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_pipeline_worker, args=(2, 24510, str(tmp_path), True, True), nprocs=2, join=True)
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "vgg16_cfg1_golden.json")))
+    got = json.load(open(os.path.join(str(tmp_path), "rank1.json")))
+    rel = [abs(a - b) / abs(b) for a, b in zip(got["losses"], gold["losses"])]
+    assert len(rel) == 20 and max(rel) <= 2e-2, rel
 
 
 def _gnmt_worker(rank, world, port, out_dir):
