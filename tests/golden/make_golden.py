@@ -7,6 +7,8 @@ the PIPEDREAM_REFERENCE environment variable:
 
 It imports the reference's runtime/ modules unmodified and records what they compute:
 
+  partition_golden.json  stage cuts and replication factors the reference's partitioner (optimizer/
+                        optimizer_graph_hierarchical.py) computes for eight synthetic chain profiles
   signatures_golden.json  constructor / method signatures of the runtime and optimizer classes the driver scripts use
   routing_golden.json   stage/rank/warm-up assignment (runtime/runtime.py:129-222) and the
                         replica routing sequences (runtime/communication.py:456-521,583-608)
@@ -248,6 +250,70 @@ def make_signatures(ref):
     with open(os.path.join(HERE, "signatures_golden.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)
     print("wrote signatures_golden.json")
+
+
+# ----------------------------------------------------------------------------- partitioner
+def make_partition(ref):
+    """The reference's own `compute_partitioning` + `analyze_partitioning` on synthetic chain profiles."""
+    import random
+    import types
+    sys.modules.setdefault("graphviz", types.ModuleType("graphviz"))
+    sys.path.insert(0, ref)
+    sys.path.insert(0, os.path.join(ref, "optimizer"))
+    import optimizer_graph_hierarchical as ogh
+    cases = []
+    for seed, L, machines, straight, ratio in ((1, 12, 4, False, None), (2, 16, 8, False, None), (3, 10, 4, True, None),
+                                               (4, 14, 8, False, 1.0), (5, 9, 3, False, 1.0), (6, 20, 8, True, 1.0),
+                                               (7, 16, 6, False, None), (8, 13, 8, False, 2.0)):
+        rnd = random.Random(seed)
+        times = [rnd.uniform(0.5, 8.0) * (3.0 if rnd.random() < 0.2 else 1.0) for _ in range(L)]
+        params = [rnd.choice([0.0, 1e6, 5e7, 5e8, 3e9]) for _ in range(L)]
+        acts = [rnd.uniform(1e5, 5e7) for _ in range(L)]
+        outs = [rnd.uniform(1e5, 3e7) for _ in range(L)]
+        bandwidth = rnd.choice([2e8, 1e9, 5e9])
+        ogh.straight_pipeline = straight
+        ogh.use_memory_constraint = False
+        ogh.memory_size = 1e18
+        ogh.use_fewer_machines = False
+        ogh.activation_compression_ratio = ratio
+        states = []
+        ct = ps = ac = 0.0
+        for i in range(L):
+            ct += times[i]; ps += params[i]; ac += acts[i]
+            states.append(types.SimpleNamespace(compute_time=ct, parameter_size=ps, activation_size=ac,
+                                                output_activation_size=outs[i], antichain=[i]))
+        compute_times, activation_sizes, parameter_sizes = [], [], []
+        for i in range(L + 1):
+            r1, r2, r3 = [], [], []
+            for j in range(L):
+                if i == 0:
+                    r1.append(states[j].compute_time); r2.append(states[j].activation_size); r3.append(states[j].parameter_size)
+                elif j > i - 1:
+                    r1.append(states[j].compute_time - states[i - 1].compute_time)
+                    r2.append(states[j].activation_size - states[i - 1].activation_size)
+                    r3.append(states[j].parameter_size - states[i - 1].parameter_size)
+                else:
+                    r1.append(None); r2.append(None); r3.append(None)
+            compute_times.append(r1); activation_sizes.append(r2); parameter_sizes.append(r3)
+        preds = [list(range(j)) for j in range(L)]
+        A = ogh.compute_partitioning(compute_times, activation_sizes, parameter_sizes, outs, preds, machines, 1, bandwidth,
+                                     final_level=True)
+        # replication factors are not returned by analyze_partitioning: walk the table the same way
+        splits = ogh.analyze_partitioning(A, states, 0, L, bandwidth, machines, ratio, False, False)
+        meta = A[0][L - 1][machines - 1]
+        reps, nxt = [], meta[1]
+        while nxt is not None:
+            reps.append(meta[2])
+            meta = A[0][nxt[0]][nxt[1]]
+            nxt = meta[1]
+        reps.append(meta[2])
+        reps.reverse()
+        cases.append({"times": times, "param_bytes": params, "act_bytes": acts, "out_bytes": outs, "bandwidth": bandwidth,
+                      "num_machines": machines, "straight": straight, "compression_ratio": ratio,
+                      "splits": splits, "replication": reps, "pipeline_time": A[0][L - 1][machines - 1][0]})
+    with open(os.path.join(HERE, "partition_golden.json"), "w") as f:
+        json.dump(cases, f, indent=1)
+    print("wrote partition_golden.json:", [(c["splits"], c["replication"]) for c in cases])
 
 
 # ----------------------------------------------------------------------------- stashing
@@ -799,6 +865,9 @@ if __name__ == "__main__":
         if a.only in (None, "routing"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_routing(%r)" % (HERE, a.ref)])
+        if a.only in (None, "partition"):
+            subprocess.check_call([sys.executable, "-O", "-c",
+                                   "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_partition(%r)" % (HERE, a.ref)])
         if a.only in (None, "signatures"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_signatures(%r)" % (HERE, a.ref)])
