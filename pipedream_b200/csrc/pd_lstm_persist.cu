@@ -154,19 +154,30 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       bool ok = wait_bar(smem_u32(&w_bar), 0, p.err, 6);
-      uint32_t it = 0;
+      // The issuing thread runs every instruction between two MMAs itself and an N = 32 MMA is only 16 cycles of
+      // tensor-pipe work, so descriptors advance by 32-bit adds on their low words and the ring position is
+      // carried along instead of being derived by division.
+      const uint64_t da0 = make_desc(smem_a, 0), db0 = make_desc(smem_w, 0);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t idesc = p.idesc;
+      int s = 0;
+      uint32_t ph = 0, a_lo = a_lo0, fb = full0, eb = empty0;
       for (int t = 1; t < p.T && ok; ++t) {
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)S);
-          const uint32_t ph = (it / (uint32_t)S) & 1u;
-          if (!wait_bar(smem_u32(&full_bar[s]), ph, p.err, 2)) { ok = false; break; }
+        uint32_t b_lo = b_lo0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!wait_bar(fb, ph, p.err, 2)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = make_desc(smem_a + (uint32_t)s * kStageBytes, 0);
-          const uint64_t db = make_desc(smem_w + (uint32_t)kb * kWBlockBytes, 0);
+          if (kb == 0) umma_lo<1, 0>(tmem_acc, a_lo, a_hi, b_lo, b_hi, idesc, 0u);
+          else umma_lo<1, 1>(tmem_acc, a_lo, a_hi, b_lo, b_hi, idesc, 1u);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 16; ++kk)
-            umma_bf16(tmem_acc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), p.idesc, (uint32_t)((kb | kk) != 0));
-          umma_commit(smem_u32(&empty_bar[s]));
+          for (int kk = 1; kk < kBlockK / 16; ++kk)
+            umma_lo<1, 1>(tmem_acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, idesc, 1u);
+          umma_commit(eb);
+          b_lo += kWBlockBytes >> 4;
+          ++s; a_lo += kStageBytes >> 4; fb += 8; eb += 8;
+          if (s == S) { s = 0; ph ^= 1u; a_lo = a_lo0; fb = full0; eb = empty0; }
         }
         if (ok) umma_commit(smem_u32(&acc_bar));
       }
@@ -372,19 +383,28 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = wait_bar(smem_u32(&w_bar), 0, p.err, 6);
-      uint32_t it = 0;
+      // lean issue loop: see the forward kernel
+      const uint64_t da0 = make_desc(smem_a, 0), db0 = make_desc(smem_w, 1);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t idesc = p.idesc;
+      int s = 0;
+      uint32_t ph = 0, a_lo = a_lo0, fb = full0, eb = empty0;
       for (int i = 0; i + 1 < p.T && ok; ++i) {
-        for (int kb = 0; kb < kKb; ++kb, ++it) {
-          const int s = (int)(it % (uint32_t)kBwdStages);
-          const uint32_t ph = (it / (uint32_t)kBwdStages) & 1u;
-          if (!wait_bar(smem_u32(&full_bar[s]), ph, p.err, 2)) { ok = false; break; }
+        uint32_t b_lo = b_lo0;
+        for (int kb = 0; kb < kKb; ++kb) {
+          if (!wait_bar(fb, ph, p.err, 2)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = make_desc(smem_a + (uint32_t)s * kStageBytes, 0);
-          const uint64_t db = make_desc(smem_w + (uint32_t)(kb * 2) * kAtomBytes, 1);
+          if (kb == 0) umma_lo<1, 0>(tmem_acc, a_lo, a_hi, b_lo, b_hi, idesc, 0u);
+          else umma_lo<1, 1>(tmem_acc, a_lo, a_hi, b_lo, b_hi, idesc, 1u);
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 16; ++kk)
-            umma_bf16(tmem_acc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 128), p.idesc, (uint32_t)((kb | kk) != 0));
-          umma_commit(smem_u32(&empty_bar[s]));
+          for (int kk = 1; kk < kBlockK / 16; ++kk)
+            umma_lo<1, 1>(tmem_acc, a_lo + kk * 2, a_hi, b_lo + kk * 128, b_hi, idesc, 1u);
+          umma_commit(eb);
+          b_lo += (2u * kAtomBytes) >> 4;
+          ++s; a_lo += kStageBytes >> 4; fb += 8; eb += 8;
+          if (s == kBwdStages) { s = 0; ph ^= 1u; a_lo = a_lo0; fb = full0; eb = empty0; }
         }
         if (ok) umma_commit(smem_u32(&acc_bar));
       }
