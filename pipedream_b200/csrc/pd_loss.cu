@@ -76,6 +76,108 @@ softmax_ce_rows_kernel(const T* __restrict__ logits, const int64_t* __restrict__
   }
 }
 
+// bf16 rows whose length is a multiple of 8 and whose base is 16-byte aligned: one pass over the row with 16-byte
+// loads and an online log-sum-exp (running maximum m and sum of exp(x - m) per thread, merged across the block), so
+// the logits are read from HBM exactly once.  Same outputs as softmax_ce_rows_kernel.
+__global__ void __launch_bounds__(kThreads)
+softmax_ce_rows_bf16x8_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target, int C,
+                              float smoothing, int64_t padding_idx, float* __restrict__ row_loss,
+                              float* __restrict__ lse_out) {
+  __shared__ float sm[32];
+  const int64_t r = blockIdx.x;
+  const __nv_bfloat16* x = logits + r * C;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const int nv = C >> 3;
+  float m = -INFINITY, se = 0.f, sx = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 pk = __ldg(xv + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      v[2 * e] = f.x; v[2 * e + 1] = f.y;
+    }
+    float vm = v[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) vm = fmaxf(vm, v[e]);
+    const float mn = fmaxf(m, vm);
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { acc += __expf(v[e] - mn); sx += v[e]; }
+    se = se * __expf(m - mn) + acc;          // (m = -inf on the first vector: exp(-inf) = 0)
+    m = mn;
+  }
+  const float mx = block_max(m, sm);
+  se = block_sum(m == -INFINITY ? 0.f : se * __expf(m - mx), sm);
+  sx = block_sum(sx, sm);
+  if (threadIdx.x == 0) {
+    const float lse = mx + logf(se);
+    lse_out[r] = lse;
+    const int64_t t = target[r];
+    float loss = 0.f;
+    if (t >= 0 && t < C && !(padding_idx >= 0 && t == padding_idx)) {
+      const float nll = lse - __bfloat162float(x[t]);
+      const float smooth = lse - sx / (float)C;
+      loss = (1.f - smoothing) * nll + smoothing * smooth;
+    }
+    row_loss[r] = loss;
+  }
+}
+
+// The matching backward pass: 16-byte loads and stores.
+__global__ void __launch_bounds__(kThreads)
+softmax_ce_bwd_bf16x8_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target,
+                             const float* __restrict__ lse, int C, float smoothing, int64_t padding_idx,
+                             const float* __restrict__ upstream, float gscale, __nv_bfloat16* __restrict__ dlogits) {
+  const int64_t r = blockIdx.x;
+  const uint4* xv = reinterpret_cast<const uint4*>(logits + r * C);
+  uint4* dv = reinterpret_cast<uint4*>(dlogits + r * C);
+  const int64_t t = target[r];
+  const bool dead = !(t >= 0 && t < C) || (padding_idx >= 0 && t == padding_idx);
+  const float g = gscale * (upstream ? *upstream : 1.f);
+  const float l = lse[r];
+  const float conf = 1.f - smoothing, sm_c = smoothing / (float)C;
+  const int nv = C >> 3;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (!dead) {
+      const uint4 pk = __ldg(xv + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+      __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
+      const int c0 = i << 3;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        const float a = g * (__expf(f.x - l) - ((int64_t)(c0 + 2 * e) == t ? conf : 0.f) - sm_c);
+        const float b = g * (__expf(f.y - l) - ((int64_t)(c0 + 2 * e + 1) == t ? conf : 0.f) - sm_c);
+        o[e] = __floats2bfloat162_rn(a, b);
+      }
+    }
+    dv[i] = out;
+  }
+}
+
+template <typename T>
+void launch_rows(const void* logits, const int64_t* target, int64_t rows, int C, float smoothing, int64_t padding_idx,
+                 float* row_loss, float* lse, cudaStream_t s);
+template <>
+void launch_rows<float>(const void* logits, const int64_t* target, int64_t rows, int C, float smoothing,
+                        int64_t padding_idx, float* row_loss, float* lse, cudaStream_t s) {
+  softmax_ce_rows_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, C, smoothing, padding_idx,
+                                                                     row_loss, lse);
+}
+template <>
+void launch_rows<__nv_bfloat16>(const void* logits, const int64_t* target, int64_t rows, int C, float smoothing,
+                                int64_t padding_idx, float* row_loss, float* lse, cudaStream_t s) {
+  if ((C & 7) == 0 && (((uintptr_t)logits) & 15) == 0)
+    softmax_ce_rows_bf16x8_kernel<<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing,
+                                                                       padding_idx, row_loss, lse);
+  else
+    softmax_ce_rows_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing,
+                                                                               padding_idx, row_loss, lse);
+}
+
 // Deterministic single-block reduction: loss = scale * sum(row_loss).
 __global__ void __launch_bounds__(1024)
 loss_reduce_kernel(const float* __restrict__ row_loss, int64_t rows, float scale, float* __restrict__ loss) {
@@ -120,10 +222,8 @@ PD_EXPORT int pd_softmax_ce_fwd(const void* logits, int dtype, const int64_t* ta
   PD_REQUIRE(logits && target && row_loss && lse && loss && rows > 0 && C > 0,
              "pd_softmax_ce_fwd: bad arguments");
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == PD_F32)
-    softmax_ce_rows_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, C, smoothing, padding_idx, row_loss, lse);
-  else if (dtype == PD_BF16)
-    softmax_ce_rows_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  if (dtype == PD_F32) launch_rows<float>(logits, target, rows, C, smoothing, padding_idx, row_loss, lse, s);
+  else if (dtype == PD_BF16) launch_rows<__nv_bfloat16>(logits, target, rows, C, smoothing, padding_idx, row_loss, lse, s);
   else PD_REQUIRE(false, "pd_softmax_ce_fwd: bad dtype");
   PD_LAUNCH_CHECK("softmax_ce_rows_kernel");
   loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, rows, scale, loss);
@@ -141,6 +241,8 @@ PD_EXPORT int pd_softmax_ce_bwd(const void* logits, int dtype, const int64_t* ta
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == PD_F32)
     softmax_ce_bwd_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, lse, C, smoothing, padding_idx, upstream, gscale, (float*)dlogits);
+  else if (dtype == PD_BF16 && (C & 7) == 0 && ((((uintptr_t)logits) | ((uintptr_t)dlogits)) & 15) == 0)
+    softmax_ce_bwd_bf16x8_kernel<<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, lse, C, smoothing, padding_idx, upstream, gscale, (__nv_bfloat16*)dlogits);
   else if (dtype == PD_BF16)
     softmax_ce_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, lse, C, smoothing, padding_idx, upstream, gscale, (__nv_bfloat16*)dlogits);
   else PD_REQUIRE(false, "pd_softmax_ce_bwd: bad dtype");
@@ -195,10 +297,8 @@ PD_EXPORT int pd_softmax_ce_fwd_static(const void* logits, int dtype, const int6
   rc = static_row_loss_ptr(&row_loss);
   if (rc != PD_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == PD_F32)
-    softmax_ce_rows_kernel<float><<<(unsigned)rows, kThreads, 0, s>>>((const float*)logits, target, C, smoothing, padding_idx, row_loss, lse);
-  else if (dtype == PD_BF16)
-    softmax_ce_rows_kernel<__nv_bfloat16><<<(unsigned)rows, kThreads, 0, s>>>((const __nv_bfloat16*)logits, target, C, smoothing, padding_idx, row_loss, lse);
+  if (dtype == PD_F32) launch_rows<float>(logits, target, rows, C, smoothing, padding_idx, row_loss, lse, s);
+  else if (dtype == PD_BF16) launch_rows<__nv_bfloat16>(logits, target, rows, C, smoothing, padding_idx, row_loss, lse, s);
   else PD_REQUIRE(false, "pd_softmax_ce_fwd_static: bad dtype");
   PD_LAUNCH_CHECK("softmax_ce_rows_kernel");
   loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, rows, scale, loss);

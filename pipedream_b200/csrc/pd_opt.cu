@@ -76,6 +76,17 @@ sgd_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
   }
 }
 
+__device__ __forceinline__ void adam_update(float& p, float g, float& m, float& v, float beta1, float beta2, float eps,
+                                            float wd, float step_size, float bias_c2_sqrt) {
+  if (wd != 0.f) g = fmaf(wd, p, g);
+  m = m + (g - m) * (1.f - beta1);           // lerp form used by torch.optim.Adam
+  v = v * beta2 + (1.f - beta2) * g * g;
+  const float denom = sqrtf(v) / bias_c2_sqrt + eps;
+  p = p - step_size * (m / denom);
+}
+
+// Four parameters per thread and trip: 16-byte loads and stores of gradient, moments and master copy (every arena
+// is 256-byte aligned and slot strides are multiples of 64 elements), one 8-byte store of the bf16 weights.
 template <typename WT>
 __global__ void __launch_bounds__(kOptThreads)
 adam_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
@@ -83,19 +94,40 @@ adam_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
                  float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
                  int64_t n, float lr, float beta1, float beta2, float eps, float wd,
                  float bias_c1, float bias_c2_sqrt, float grad_scale) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const float step_size = lr / bias_c1;
-  for (; i < n; i += stride) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool vec = ((((uintptr_t)grad) | ((uintptr_t)exp_avg) | ((uintptr_t)exp_avg_sq) | ((uintptr_t)master)) & 15) == 0 &&
+                   ((((uintptr_t)w_read) | ((uintptr_t)w_write)) & (4 * sizeof(WT) - 1)) == 0;
+  const int64_t n4 = vec ? n >> 2 : 0;
+  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += stride) {
+    const int64_t i = q << 2;
+    float p[4], g[4], m[4], v[4];
+    const float4 g4 = *reinterpret_cast<const float4*>(grad + i);
+    const float4 m4 = *reinterpret_cast<const float4*>(exp_avg + i);
+    const float4 v4 = *reinterpret_cast<const float4*>(exp_avg_sq + i);
+    g[0] = g4.x * grad_scale; g[1] = g4.y * grad_scale; g[2] = g4.z * grad_scale; g[3] = g4.w * grad_scale;
+    m[0] = m4.x; m[1] = m4.y; m[2] = m4.z; m[3] = m4.w;
+    v[0] = v4.x; v[1] = v4.y; v[2] = v4.z; v[3] = v4.w;
+    if (master != nullptr) {
+      const float4 p4 = *reinterpret_cast<const float4*>(master + i);
+      p[0] = p4.x; p[1] = p4.y; p[2] = p4.z; p[3] = p4.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p[j] = pd_to_float(w_read[i + j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) adam_update(p[j], g[j], m[j], v[j], beta1, beta2, eps, wd, step_size, bias_c2_sqrt);
+    *reinterpret_cast<float4*>(exp_avg + i) = make_float4(m[0], m[1], m[2], m[3]);
+    *reinterpret_cast<float4*>(exp_avg_sq + i) = make_float4(v[0], v[1], v[2], v[3]);
+    if (master != nullptr) *reinterpret_cast<float4*>(master + i) = make_float4(p[0], p[1], p[2], p[3]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w_write[i + j] = pd_from_float<WT>(p[j]);
+  }
+  // tail, or everything when the pointers are not aligned
+  for (int64_t i = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float p = master ? master[i] : pd_to_float(w_read[i]);
-    float g = grad[i] * grad_scale;
-    if (wd != 0.f) g = fmaf(wd, p, g);
-    float m = exp_avg[i];
-    float v = exp_avg_sq[i];
-    m = m + (g - m) * (1.f - beta1);           // lerp form used by torch.optim.Adam
-    v = v * beta2 + (1.f - beta2) * g * g;
-    float denom = sqrtf(v) / bias_c2_sqrt + eps;
-    p = p - step_size * (m / denom);
+    float m = exp_avg[i], v = exp_avg_sq[i];
+    adam_update(p, grad[i] * grad_scale, m, v, beta1, beta2, eps, wd, step_size, bias_c2_sqrt);
     exp_avg[i] = m;
     exp_avg_sq[i] = v;
     if (master) master[i] = p;
