@@ -96,6 +96,8 @@ class OptimizerWithWeightStashing:
     def __init__(self, optim_name, modules, master_parameters, model_parameters,
                  loss_scale, num_versions, verbose_freq=0, macrobatch=False,
                  **optimizer_args):
+        # (an argument of this implementation, not the reference's; taken out before the rest reaches torch.optim)
+        update_interval = optimizer_args.pop("update_interval", None)
         if optim_name not in self._SUPPORTED:
             raise ValueError("optimizer %r is not supported (SGD, Adam)" % optim_name)
         self.optim_name = optim_name
@@ -114,7 +116,15 @@ class OptimizerWithWeightStashing:
         self.current_version = Version()
         self.verbose_freq = verbose_freq
         self.batch_counter = 0
+        # The reference ties the accumulation length to the (capped) version count: a macrobatch is
+        # `num_versions` <= 2 minibatches (runtime/optimizer.py:36-52).  `update_interval` (an extension, not in the
+        # reference's signature) sets it independently, e.g. 64 microbatches of 8 sequences for a global batch of
+        # 512 with two weight versions; gradients accumulate in the fp32 arena and are scaled by 1 / interval.
         self.update_interval = self.num_versions if macrobatch else 1
+        if update_interval is not None:
+            if not macrobatch or int(update_interval) < 1:
+                raise ValueError("update_interval needs macrobatch=True and a positive value")
+            self.update_interval = int(update_interval)
         self.trace = []           # (event, version) tuples; tests compare it with the reference's
         self._steps_taken = 0
         self._grad_sync = None    # set by StageRuntime for replicated stages

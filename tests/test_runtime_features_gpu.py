@@ -23,6 +23,10 @@ torch.backends.cudnn.allow_tf32 = False
 torch.backends.cuda.matmul.allow_tf32 = False
 
 
+def rel_err(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
 def small_pipeline(fp16, **kw):
     pkg = stages.vgg16("gpus=8")
     conf = dict(pkg.conf)
@@ -203,3 +207,45 @@ def test_forward_only_with_ack_clock():
     for r in (r0, r1):
         r.train(1)
     assert "ack" not in r0.send_ranks and "ack" not in r1.receive_ranks
+
+
+@pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
+def test_accumulation_over_more_than_two_microbatches(fp16):
+    """`update_interval` (an extension beside the reference's `macrobatch`, whose accumulation length is the
+    version count capped at two, runtime/optimizer.py:36-52): k micro-batches accumulate into the fp32 gradient
+    arena, one optimizer step follows the k-th with the gradients scaled by 1 / k, and two weight versions stay
+    enough.  Checked against one step of torch SGD on the k micro-batches joined into one batch."""
+    from pipedream_b200 import layers
+    from pipedream_b200.stashing_optimizers import SGDWithWeightStashing
+    k, mb, steps = 5, 16, 3
+    torch.manual_seed(3)
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 32)).cuda()
+    ours = layers.nativize(copy.deepcopy(ref))
+    if fp16:
+        ours = ours.to(torch.bfloat16)
+    assert isinstance(ours[0], layers.NativeLinear)
+    opt = SGDWithWeightStashing([ours], list(ours.parameters()), None, 1, num_versions=4, lr=0.05, momentum=0.9,
+                                weight_decay=1e-4, macrobatch=True, update_interval=k)
+    assert opt.num_versions == 2 and opt.update_interval == k
+    with pytest.raises(ValueError):
+        SGDWithWeightStashing([ours], list(ours.parameters()), None, 1, num_versions=2, lr=0.05, update_interval=3)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    g = torch.Generator().manual_seed(11)
+    for s in range(steps):
+        xs = [torch.randn(mb, 64, generator=g).cuda() for _ in range(k)]
+        ts = [torch.randn(mb, 32, generator=g).cuda() for _ in range(k)]
+        ropt.zero_grad()
+        (sum(((ref(x) - t) ** 2).mean() for x, t in zip(xs, ts)) / k).backward()
+        ropt.step()
+        for i, (x, t) in enumerate(zip(xs, ts)):
+            opt.zero_grad()
+            xin = x.to(torch.bfloat16) if fp16 else x
+            ((ours(xin).float() - t) ** 2).mean().backward()
+            before = opt.latest_version.version
+            opt.step()
+            assert opt.latest_version.version == before + (1 if i == k - 1 else 0)
+    assert [e for e in opt.trace if e[0] == "step"] == [("step", v) for v in range(1, steps + 1)]
+    tol = 3e-2 if fp16 else 2e-5
+    for p, q in zip(ours.parameters(), ref.parameters()):
+        assert rel_err(p.float(), q) <= tol
+    assert pf.gemm_poll_error() == 0
