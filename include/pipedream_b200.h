@@ -86,6 +86,15 @@ int pd_maxpool2_fwd(const void* x_pad, int N, int C, int H, int W, void* y, int 
                     int dtype, void* stream);
 int pd_maxpool2_bwd(const void* x_pad, const void* dy, int N, int C, int H, int W, void* dx_pad,
                     int dy_mode, int relu_mask, int dtype, void* stream);
+/* The same backward (dy in padded NHWC) that also reduces the bias gradient of the convolution in
+ * front of the pool: block b leaves the column sums of the gradient it routed in partial[b][C]
+ * (*partial_rows rows; partial holds at least pd_colsum_workspace_bytes(C) bytes), and
+ * pd_colsum_finish adds the rows into out[C].  Needs bf16, even H and W, C % 8 == 0 with
+ * 256 % (C / 8) == 0 and 16-byte aligned pointers (PD_ERR_INVALID otherwise).               */
+int pd_maxpool2_bwd_colsum(const void* x_pad, const void* dy_pad, int N, int C, int H, int W,
+                           void* dx_pad, int relu_mask, int dtype, float* partial,
+                           int64_t partial_bytes, int* partial_rows, void* stream);
+int pd_colsum_finish(const float* partial, int rows, int C, float* out, int accumulate, void* stream);
 int pd_dropout_fwd(const void* x, void* y, uint8_t* mask, int64_t n, float p, uint64_t seed,
                    uint64_t offset, int dtype, void* stream);
 int pd_dropout_bwd(const void* dy, const uint8_t* mask, void* dx, int64_t n, float p, int dtype,

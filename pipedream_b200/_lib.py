@@ -41,6 +41,8 @@ SIGNATURES = {
     "pd_relu_bwd_colsum": (I, [P, P, P, L, I, I, P, I, P, L, P]),
     "pd_maxpool2_fwd": (I, [P, I, I, I, I, P, I, I, P]),
     "pd_maxpool2_bwd": (I, [P, P, I, I, I, I, P, I, I, I, P]),
+    "pd_maxpool2_bwd_colsum": (I, [P, P, I, I, I, I, P, I, I, P, L, P, P]),
+    "pd_colsum_finish": (I, [P, I, I, P, I, P]),
     "pd_dropout_fwd": (I, [P, P, P, L, F, U64, U64, I, P]),
     "pd_dropout_bwd": (I, [P, P, P, L, F, I, P]),
     "pd_add": (I, [P, P, P, L, I, P]),

@@ -559,6 +559,111 @@ im2col3x3_rows_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t
   }
 }
 
+// The same for C == 3 (the first layer of the image models): one thread per (padded pixel row, 8 patch columns),
+// so a warp writes 512 contiguous bytes and the tap / channel of a column come from divisions by constants.
+template <typename S>
+__global__ void __launch_bounds__(kThreads)
+im2col3x3_c3_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
+                    int N, int H, int W, int K8, uint4* __restrict__ dst) {
+  const int Hp = H + 2, Wp = W + 2;
+  const int64_t total = (int64_t)N * Hp * Wp * K8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int q = (int)(i % K8);
+    const int64_t p = i / K8;
+    const int wp = (int)(p % Wp);
+    const int hp = (int)((p / Wp) % Hp);
+    const int n = (int)(p / ((int64_t)Wp * Hp));
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    if (hp >= 1 && hp <= H && wp >= 1 && wp <= W && q * 8 < 27) {
+      const S* base = src + n * sN;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = q * 8 + j;
+        const int t = k / 3, c = k - t * 3;
+        const int r = t / 3, sx = t - r * 3;
+        const int h = hp - 2 + r, w = wp - 2 + sx;
+        if (k < 27 && h >= 0 && h < H && w >= 0 && w < W) f[j] = pd_to_float(base[c * sC + h * sH + w * sW]);
+      }
+    }
+    dst[i] = pack8(f);
+  }
+}
+
+// Max-pool backward with the bias-gradient reduction of the producing convolution folded in: besides dx, every
+// block leaves the column sums of the gradient it routed in partial[blockIdx.x][C] (the column sums of dx are the
+// sums of the routed values).  H and W even; gridDim.x * kThreads is a multiple of C8, so a thread stays on one
+// group of 8 channels; the border of dx is enumerated directly (2 * Wp + 2 * H pixels per image).
+__global__ void __launch_bounds__(kThreads)
+maxpool2_bwd_colsum_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, int N, int C8, int H,
+                                  int W, uint4* __restrict__ dx, int relu_mask, float* __restrict__ partial) {
+  extern __shared__ float sm[];   // [kThreads / C8][C8 * 8] when partial != nullptr
+  const int Ho = H / 2, Wo = W / 2;
+  const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const int64_t total = (int64_t)N * Ho * Wo * C8;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
+    const int64_t base = (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C8 + c;
+    float v[4][8], g[8];
+    unpack8(x[base], v[0]);
+    unpack8(x[base + C8], v[1]);
+    unpack8(x[base + (int64_t)Wp * C8], v[2]);
+    unpack8(x[base + (int64_t)Wp * C8 + C8], v[3]);
+    unpack8(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C8 + c], g);
+    float o[4][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      int arg = 0; float m = v[0][k];
+      if (v[1][k] > m) { m = v[1][k]; arg = 1; }
+      if (v[2][k] > m) { m = v[2][k]; arg = 2; }
+      if (v[3][k] > m) { m = v[3][k]; arg = 3; }
+      const float gg = (relu_mask && !(m > 0.f)) ? 0.f : g[k];
+      acc[k] += gg;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o[q][k] = (q == arg) ? gg : 0.f;
+    }
+    dx[base] = pack8(o[0]);
+    dx[base + C8] = pack8(o[1]);
+    dx[base + (int64_t)Wp * C8] = pack8(o[2]);
+    dx[base + (int64_t)Wp * C8 + C8] = pack8(o[3]);
+  }
+  const int per_image = 2 * Wp + 2 * H;
+  const int64_t border = (int64_t)N * per_image * C8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < border;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const int64_t p = i / C8;
+    const int b = (int)(p % per_image), n = (int)(p / per_image);
+    int hp, wp;
+    if (b < Wp) { hp = 0; wp = b; }
+    else if (b < 2 * Wp) { hp = Hp - 1; wp = b - Wp; }
+    else { const int r = b - 2 * Wp; hp = 1 + (r >> 1); wp = (r & 1) ? Wp - 1 : 0; }
+    dx[(((int64_t)n * Hp + hp) * Wp + wp) * C8 + c] = zero;
+  }
+  if (partial != nullptr) {
+    // a thread's channel group: (blockIdx.x * kThreads + threadIdx.x) % C8 == threadIdx.x % C8 (kThreads % C8 == 0)
+    const int lanes = kThreads / C8, lane = threadIdx.x / C8, c = threadIdx.x % C8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sm[(lane * C8 + c) * 8 + k] = acc[k];
+    __syncthreads();
+    const int C = C8 * 8;
+    for (int col = threadIdx.x; col < C; col += blockDim.x) {
+      float s = 0.f;
+      for (int l = 0; l < lanes; ++l) s += sm[l * C + col];
+      partial[(int64_t)blockIdx.x * C + col] = s;
+    }
+  }
+}
+
 }  // namespace
 
 #define PD_DISPATCH_T(dtype, ...)                                   \
@@ -618,6 +723,16 @@ PD_EXPORT int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t s
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
   if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && ((uintptr_t)dst % 16) == 0) {
     const int64_t rows = (int64_t)N * (H + 2) * (W + 2);
+    if (C == 3) {
+      const int K8 = Kpad / 8;
+      const int g3 = grid_cap((rows * K8 + kThreads - 1) / kThreads, 16);
+      if (src_dtype == PD_F32)
+        im2col3x3_c3_kernel<float><<<g3, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
+      else
+        im2col3x3_c3_kernel<__nv_bfloat16><<<g3, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
+      PD_LAUNCH_CHECK("im2col3x3_c3_kernel");
+      return PD_OK;
+    }
     const int g2 = grid_cap((rows + kThreads - 1) / kThreads, 16);
     if (src_dtype == PD_F32)
       im2col3x3_rows_kernel<float><<<g2, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, C, H, W, Kpad, (__nv_bfloat16*)dst);
@@ -666,7 +781,7 @@ PD_EXPORT int pd_relu_bwd(const void* dy, const void* y, void* dx, int64_t n, in
 
 // workspace: at least pd_colsum_workspace_bytes(C) bytes of device memory.
 PD_EXPORT int64_t pd_colsum_workspace_bytes(int C) {
-  return (int64_t)pd_num_sms() * 4 * (int64_t)C * sizeof(float);   // >= blocks launched x C floats
+  return (int64_t)pd_num_sms() * 8 * (int64_t)C * sizeof(float);   // >= blocks launched x C floats
 }
 
 PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_t rows, int C,
@@ -732,6 +847,46 @@ PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y
   return PD_OK;
 }
 
+namespace {
+bool pool_bwd_fast_ok(const void* x, const void* dy, const void* dx, int C, int H, int W, int dtype) {
+  return dtype == PD_BF16 && (C % 8) == 0 && (kThreads % (C / 8)) == 0 && (H % 2) == 0 && (W % 2) == 0 &&
+         (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) % 16) == 0;
+}
+}  // namespace
+
+// Max-pool backward (dy in padded NHWC) that also leaves per-block column sums of dx in `partial`
+// (`*partial_rows` rows of C floats, at most pd_colsum_workspace_bytes(C) bytes); pd_colsum_finish adds them up.
+PD_EXPORT int pd_maxpool2_bwd_colsum(const void* x, const void* dy, int N, int C, int H, int W, void* dx,
+                                     int relu_mask, int dtype, float* partial, int64_t partial_bytes,
+                                     int* partial_rows, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(x && dy && dx && partial && partial_rows && N > 0 && C > 0 && H >= 2 && W >= 2,
+             "pd_maxpool2_bwd_colsum: bad arguments");
+  PD_REQUIRE(partial_bytes >= pd_colsum_workspace_bytes(C), "pd_maxpool2_bwd_colsum: partial buffer too small");
+  PD_REQUIRE(pool_bwd_fast_ok(x, dy, dx, C, H, W, dtype),
+             "pd_maxpool2_bwd_colsum: needs bf16, even H and W, C a multiple of 8 with 256 % (C / 8) == 0, 16-byte pointers");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int C8 = C / 8;
+  const int64_t win = (int64_t)N * (H / 2) * (W / 2) * C8;
+  const int grid = grid_cap((win + kThreads - 1) / kThreads, 8);
+  maxpool2_bwd_colsum_bf16x8_kernel<<<grid, kThreads, (size_t)kThreads * 8 * sizeof(float), s>>>(
+      (const uint4*)x, (const uint4*)dy, N, C8, H, W, (uint4*)dx, relu_mask, partial);
+  PD_LAUNCH_CHECK("maxpool2_bwd_colsum_bf16x8_kernel");
+  *partial_rows = grid;
+  return PD_OK;
+}
+
+// out[C] (+)= sum over the rows of partial[rows][C].
+PD_EXPORT int pd_colsum_finish(const float* partial, int rows, int C, float* out, int accumulate, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(partial && out && rows > 0 && C > 0, "pd_colsum_finish: bad arguments");
+  colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, rows, C, out, accumulate);
+  PD_LAUNCH_CHECK("colsum_final_fast_kernel");
+  return PD_OK;
+}
+
 PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H, int W, void* dx,
                               int dy_mode, int relu_mask, int dtype, void* stream) {
   int rc = pd_check_device();
@@ -741,6 +896,13 @@ PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H
   cudaStream_t s = (cudaStream_t)stream;
   int64_t total = (int64_t)N * (H + 2) * (W + 2) * C;
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
+  if (dy_mode == 0 && pool_bwd_fast_ok(x, dy, dx, C, H, W, dtype)) {
+    const int64_t win = (int64_t)N * (H / 2) * (W / 2) * (C / 8);
+    maxpool2_bwd_colsum_bf16x8_kernel<<<grid_cap((win + kThreads - 1) / kThreads, 16), kThreads, 0, s>>>(
+        (const uint4*)x, (const uint4*)dy, N, C / 8, H, W, (uint4*)dx, relu_mask, nullptr);
+    PD_LAUNCH_CHECK("maxpool2_bwd_colsum_bf16x8_kernel");
+    return PD_OK;
+  }
   if (dtype == PD_BF16 && dy_mode == 0 && (C % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)dy % 16) == 0 &&
       ((uintptr_t)dx % 16) == 0) {
     const int64_t win = (int64_t)N * (H / 2) * (W / 2) * (C / 8);

@@ -227,6 +227,29 @@ def maxpool2_bwd(x_pad, dy, dy_is_nchw, relu_mask):
     return dx
 
 
+def maxpool2_bwd_colsum_ok(x_pad):
+    """Whether pd_maxpool2_bwd_colsum takes this tensor (bf16, even H and W, channel count it supports)."""
+    N, Hp, Wp, C = x_pad.shape
+    return (x_pad.dtype == torch.bfloat16 and Hp % 2 == 0 and Wp % 2 == 0 and C % 8 == 0 and 256 % (C // 8) == 0)
+
+
+def maxpool2_bwd_colsum(x_pad, dy_pad, relu_mask):
+    """Max-pool backward plus per-block column sums of dx: returns (dx_pad, (partial, rows)) for `colsum_finish`."""
+    N, Hp, Wp, C = x_pad.shape
+    dx = torch.empty_like(x_pad)
+    nbytes = _lib.load().pd_colsum_workspace_bytes(C)
+    partial = torch.empty(nbytes // 4, dtype=torch.float32, device=x_pad.device)
+    rows = ctypes.c_int(0)
+    call("pd_maxpool2_bwd_colsum", _p(x_pad), _p(dy_pad), N, C, Hp - 2, Wp - 2, _p(dx), int(relu_mask), dt(x_pad),
+         _p(partial), nbytes, ctypes.byref(rows), _stream())
+    return dx, (partial, rows.value)
+
+
+def colsum_finish(partial_rows, colsum, accumulate):
+    partial, rows = partial_rows
+    call("pd_colsum_finish", _p(partial), rows, colsum.numel(), _p(colsum), int(accumulate), _stream())
+
+
 def dropout_fwd(x, p, seed, offset):
     y = torch.empty_like(x)
     mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)

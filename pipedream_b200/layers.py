@@ -113,7 +113,9 @@ class _Conv3x3Fn(torch.autograd.Function):
         # this layer's mask (see ctx.premask), only the bias gradient is left to do
         if ctx.fuse_relu and getattr(dy, "_pd_premasked", False) and pf.padded_of(dy) is not None:
             dym = dy_pad
-            if bp is not None:
+            if bp is not None and getattr(dy, "_pd_colsum", None) is not None:
+                pf.colsum_finish(dy._pd_colsum, grad_buffer(bp), take_accumulate_flag(bp))
+            elif bp is not None:
                 pf.relu_bwd_colsum(dy_pad, None, None, grad_buffer(bp), take_accumulate_flag(bp))
         elif ctx.fuse_relu:
             dym = torch.empty_like(dy_pad)
@@ -519,7 +521,11 @@ class _MaxPool2Fn(torch.autograd.Function):
     def backward(ctx, dy):
         N, C, H, W = ctx.geom
         dy_pad = pf.padded_of(dy)
-        if dy_pad is not None:
+        colsum = None
+        if dy_pad is not None and ctx.premask and pf.maxpool2_bwd_colsum_ok(ctx.x_pad):
+            # the producer is a fused conv+ReLU: its bias gradient (column sums of dx) comes out of the same pass
+            dx_pad, colsum = pf.maxpool2_bwd_colsum(ctx.x_pad, dy_pad, True)
+        elif dy_pad is not None:
             dx_pad = pf.maxpool2_bwd(ctx.x_pad, dy_pad, False, ctx.premask)
         else:
             dyc = dy if dy.is_contiguous() else dy.contiguous()
@@ -527,6 +533,8 @@ class _MaxPool2Fn(torch.autograd.Function):
         dx = pf.nchw_view(dx_pad, N, C, H, W)
         if ctx.premask:
             dx._pd_premasked = True
+        if colsum is not None:
+            dx._pd_colsum = colsum
         return dx, None
 
 

@@ -69,7 +69,43 @@ def test_im2col():
     assert torch.equal(col.view(N, H + 2, W + 2, 32), full)
 
 
+@pytest.mark.parametrize("layout", ["nchw", "channels_last"])
+def test_im2col_three_channels_bf16(layout):
+    """The first layer's patch matrix as the training path builds it: fp32 images, bf16 rows of 32."""
+    x = rnd(3, 3, 10, 14, dtype=torch.float32, seed=21)
+    if layout == "channels_last":
+        x = x.contiguous(memory_format=torch.channels_last)
+    col = pf.im2col3x3(x, 32, torch.bfloat16)
+    N, C, H, W = x.shape
+    ref = F.unfold(x.contiguous(), 3, padding=1).view(N, C, 9, H, W).permute(0, 3, 4, 2, 1).reshape(N, H, W, 27)
+    full = torch.zeros(N, H + 2, W + 2, 32, device=DEV)
+    full[:, 1:-1, 1:-1, :27] = ref
+    assert torch.equal(col.view(N, H + 2, W + 2, 32), full.to(torch.bfloat16))
+
+
 # ------------------------------------------------------------------ pointwise
+@pytest.mark.parametrize("C,H,W", [(64, 12, 16), (128, 6, 10), (512, 4, 4), (8, 2, 2)])
+def test_maxpool_bwd_with_bias_colsum(C, H, W):
+    """Pool backward that also reduces the bias gradient of the conv+ReLU in front of it."""
+    dtype = torch.bfloat16
+    xr = F.relu(rnd(3, C, H, W, dtype=dtype, seed=31))
+    xrp = pf.pack_pnhwc(xr)
+    assert pf.maxpool2_bwd_colsum_ok(xrp)
+    g = rnd(3, C, H // 2, W // 2, dtype=dtype, seed=32)
+    xr32 = xr.float().requires_grad_(True)
+    F.max_pool2d(xr32, 2).backward(g.float())
+    want = (xr32.grad * (xr32 > 0)).to(dtype)
+    dx, partial = pf.maxpool2_bwd_colsum(xrp, pf.pack_pnhwc(g), True)
+    assert torch.equal(dx, pad_ref(want))
+    assert torch.equal(dx, pf.maxpool2_bwd(xrp, pf.pack_pnhwc(g), False, True))
+    cs = torch.full((C,), 2.0, device=DEV)
+    pf.colsum_finish(partial, cs, True)
+    check(cs, want.float().sum((0, 2, 3)) + 2.0, torch.float32, "colsum accumulate")
+    pf.colsum_finish(partial, cs, False)
+    check(cs, want.float().sum((0, 2, 3)), torch.float32, "colsum")
+    assert not pf.maxpool2_bwd_colsum_ok(pf.pack_pnhwc(rnd(1, 24, 4, 4, dtype=dtype, seed=33)))   # 256 % 3 != 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_relu_pool(dtype):
     x = rnd(2, 64, 12, 16, dtype=dtype, seed=3)
