@@ -69,11 +69,19 @@ struct KParams {
   // convolution): one A box of kBox3Rows rows serves all three, num_taps counts triples
   int tap3;
   int t3_base[3], t3_off[PD_MAX_TAPS];
+  // divisions of the per-tile bookkeeping as multiply-high + shift (see fast_div): a 32-bit division is a chain of
+  // some twenty dependent instructions, and the single MMA-issuing thread runs every one of them between two tiles
+  uint32_t fd_tiles_mn[2], fd_n_tiles[2], fd_num_z[2], fd_pad_wp[2], fd_pad_hp[2];
   int* err;
   long long* stall;           // diagnostic (may be null): per CTA {cycles waiting for operands, for a free accumulator, total, tiles}
 };
 
 __device__ int g_gemm_error = 0;
+
+// n / d for 0 <= n < 2^31 with d's pair {multiplier, shift} from make_fast_div (multiplier 0 stands for d == 1).
+__device__ __forceinline__ int fast_div(int n, const uint32_t* fd) {
+  return fd[0] ? (int)(__umulhi((uint32_t)n, fd[0]) >> fd[1]) : n;
+}
 
 // Epilogue of one 32-column chunk of one accumulator row: bias, ReLU, masks, store / atomic add.
 __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t* r, int m, int nb, long long out_col0,
@@ -296,16 +304,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   // tile -> (m0, n0, z, kb_begin, kbn); n varies fastest so that CTAs running together share A rows
 #define PD_DECODE_TILE(tile)                                                   \
-  const int zs_ = (tile) / tiles_mn;                                           \
+  const int zs_ = fast_div((tile), p.fd_tiles_mn);                             \
   const int rem_ = (tile) - zs_ * tiles_mn;                                    \
-  const int m0 = (rem_ / p.n_tiles) * (kBlockM * CG * G) + (int)rank * kBlockM; \
-  const int n0 = (rem_ % p.n_tiles) * p.block_n;                               \
+  const int mt_ = fast_div(rem_, p.fd_n_tiles);                                \
+  const int m0 = mt_ * (kBlockM * CG * G) + (int)rank * kBlockM;               \
+  const int n0 = (rem_ - mt_ * p.n_tiles) * p.block_n;                         \
   const int n0l = n0 + (int)rank * p.cta_n;  /* first B row this CTA loads */  \
   /* z varies faster than the K slice: the z outputs of a weight gradient (filter taps) read the same      \
      activation rows shifted by a pixel or a row, so running them side by side fetches those rows from   \
      HBM once and serves the other taps from L2 */                                                         \
-  const int z = zs_ % p.num_z;                                                 \
-  const int kb_begin = (zs_ / p.num_z) * p.kb_per_split;                       \
+  const int ks_ = fast_div(zs_, p.fd_num_z);                                   \
+  const int z = zs_ - ks_ * p.num_z;                                           \
+  const int kb_begin = ks_ * p.kb_per_split;                                   \
   const int kb_end_ = min(kb_begin + p.kb_per_split, p.kb_per_tap);            \
   const int kbn = kb_end_ - kb_begin;                                          \
   const int iters = kbn > 0 ? kbn * p.num_taps : 0;                             \
@@ -499,6 +509,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       ++s; a_lo += stage_lo; b_lo += stage_lo; fb += 8; eb += 8;                \
       if (s == S) { s = 0; ph ^= 1u; a_lo = a_lo0; b_lo = b_lo0; fb = full0; eb = empty0; }
       uint32_t local = 0;                   // tiles done by this CTA
+      uint32_t buf = 0, use = 0;            // local % nbuf and the parity of local / nbuf, carried along
       bool ok = true;
       const bool timing = p.stall != nullptr;
       long long t_ops = 0, t_acc = 0;
@@ -507,8 +518,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         PD_DECODE_TILE(tile)
         (void)m0; (void)n0; (void)n0l; (void)kb_begin; (void)acc0;
         if (iters == 0) continue;             // (cannot happen: the host never creates empty splits)
-        const uint32_t buf = local % nbuf;
-        const uint32_t use = local / nbuf;
         // the epilogue must have drained this accumulator (passes at once on its first use)
         const long long ta = timing ? clock64() : 0;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[bar0 + buf]), (use & 1u) ^ 1u, p.err, 4);
@@ -585,6 +594,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (ok) commit_cg<CG>(smem_u32(&tmem_full_bar[bar0 + buf]));
         ++local;
+        if (++buf == nbuf) { buf = 0; use ^= 1u; }
       }
 #undef PD_NEXT_STAGE
       if (timing && grp == 0) {
@@ -600,14 +610,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t grp = G == 2 ? set : 0u;
     const uint32_t bar0 = grp * kMaxAccBufs;
     uint32_t local = 0;
+    uint32_t buf = 0, use = 0;              // local % nbuf and the parity of local / nbuf
     bool ok = true;
+#define PD_NEXT_LOCAL ++local; if (++buf == nbuf) { buf = 0; use ^= 1u; }
     for (int tile = PD_FIRST_TILE; tile < total_tiles && ok; tile += PD_TILE_STEP) {
       PD_DECODE_TILE(tile)
       (void)kb_begin; (void)n0l;
       if (iters == 0) continue;
-      if (G == 1 && (local & 1u) != set) { ++local; continue; }
-      const uint32_t buf = local % nbuf;
-      const uint32_t use = local / nbuf;
+      if (G == 1 && (local & 1u) != set) { PD_NEXT_LOCAL continue; }
       ok = mbar_wait(smem_u32(&tmem_full_bar[bar0 + buf]), use & 1u, p.err, 3);
       // the wait result can differ between lanes only when the bound ran out; make it uniform
       ok = __all_sync(0xffffffffu, ok);
@@ -616,8 +626,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int m = m0 + (int)grp * group_rows + lg * 32 + lane;
       bool border = false;
       if (p.pad_wp > 0) {
-        const int wp = m % p.pad_wp;
-        const int hp = (m / p.pad_wp) % p.pad_hp;
+        const int row_ = fast_div(m, p.fd_pad_wp);
+        const int wp = m - row_ * p.pad_wp;
+        const int hp = row_ - fast_div(row_, p.fd_pad_hp) * p.pad_hp;
         border = (wp == 0) | (wp == p.pad_wp - 1) | (hp == 0) | (hp == p.pad_hp - 1);
       }
       const bool row_ok = m < p.M;
@@ -633,11 +644,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_ld_wait();
         if (row_ok) {
           {
-            const int a = cc / p.block_n, c0 = cc - a * p.block_n;
+            const int a = accn == 1 ? 0 : cc / p.block_n, c0 = cc - a * p.block_n;
             if (n0 + c0 < p.N) epilogue_chunk(p, r0, m, n0 + c0, (long long)(acc0 + a) * p.z_out_col, border);
           }
           if (two) {
-            const int a = (cc + 32) / p.block_n, c0 = cc + 32 - a * p.block_n;
+            const int a = accn == 1 ? 0 : (cc + 32) / p.block_n, c0 = cc + 32 - a * p.block_n;
             if (n0 + c0 < p.N) epilogue_chunk(p, r1, m, n0 + c0, (long long)(acc0 + a) * p.z_out_col, border);
           }
         }
@@ -649,8 +660,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[bar0 + buf]));
         else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[bar0 + buf]), 0));
       }
-      ++local;
+      PD_NEXT_LOCAL
     }
+#undef PD_NEXT_LOCAL
   }
 #undef PD_DECODE_TILE
 #undef PD_FIRST_TILE
@@ -671,6 +683,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 }
 
 // ---- host side ----------------------------------------------------------------
+// {multiplier, shift} with n / d == umulhi(n, multiplier) >> shift for every 0 <= n < 2^31 (d >= 1; d == 1 is coded as
+// multiplier 0): multiplier = ceil(2^(31 + ceil(log2 d)) / d), which fits 32 bits, shift = ceil(log2 d) - 1.
+void make_fast_div(uint32_t d, uint32_t* fd) {
+  if (d <= 1) { fd[0] = 0; fd[1] = 0; return; }
+  uint32_t lg = 0;
+  while ((1ull << lg) < d) ++lg;
+  const uint64_t pw = 1ull << (31 + lg);
+  fd[0] = (uint32_t)((pw + d - 1) / d);
+  fd[1] = lg - 1;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -934,6 +957,11 @@ int pd_gemm_launch_tcgen05(const PdGemm& g, cudaStream_t stream) {
   }
   p.m_tiles = (g.M + kBlockM * cg * groups - 1) / (kBlockM * cg * groups);
   p.n_tiles = (g.N + block_n - 1) / block_n;
+  make_fast_div((uint32_t)(p.m_tiles * p.n_tiles), p.fd_tiles_mn);
+  make_fast_div((uint32_t)p.n_tiles, p.fd_n_tiles);
+  make_fast_div((uint32_t)p.num_z, p.fd_num_z);
+  make_fast_div((uint32_t)(p.pad_wp > 0 ? p.pad_wp : 1), p.fd_pad_wp);
+  make_fast_div((uint32_t)(p.pad_hp > 0 ? p.pad_hp : 1), p.fd_pad_hp);
   const long long total_tiles = (long long)p.m_tiles * p.n_tiles * p.num_z * p.split_k;
   PD_REQUIRE(total_tiles < (1ll << 31), "tcgen05 gemm: too many tiles");
   const int sms = pd_num_sms();

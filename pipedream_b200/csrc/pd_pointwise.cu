@@ -370,21 +370,23 @@ __device__ __forceinline__ uint4 max8(const uint4& a, const uint4& b) {
   return r;
 }
 
-// padded NHWC -> padded NHWC, 8 channels per thread
+// padded NHWC -> padded NHWC, 8 channels per thread.  IdxT: uint32_t when every vector index of x and y fits
+// (64-bit divisions cost more than the memory accesses of these kernels), int64_t otherwise.
+template <typename IdxT>
 __global__ void __launch_bounds__(kThreads)
 maxpool2_fwd_bf16x8_kernel(const uint4* __restrict__ x, int N, int C8, int H, int W, uint4* __restrict__ y) {
   const int Ho = H / 2, Wo = W / 2;
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
-  const int64_t total = (int64_t)N * Hop * Wop * C8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % C8);
-    const int64_t p = i / C8;
-    const int wo = (int)(p % Wop), ho = (int)((p / Wop) % Hop), n = (int)(p / ((int64_t)Wop * Hop));
+  const IdxT total = (IdxT)N * Hop * Wop * C8;
+  const IdxT step = (IdxT)gridDim.x * blockDim.x;
+  const IdxT row = (IdxT)Wp * C8;
+  for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const IdxT p = i / (IdxT)C8, q = p / (IdxT)Wop, n = q / (IdxT)Hop;
+    const int c = (int)(i - p * C8), wo = (int)(p - q * Wop), ho = (int)(q - n * Hop);
     uint4 m = make_uint4(0, 0, 0, 0);
     if (ho >= 1 && ho <= Ho && wo >= 1 && wo <= Wo) {
-      const uint4* b = x + (((int64_t)n * Hp + (2 * (ho - 1) + 1)) * Wp + (2 * (wo - 1) + 1)) * C8 + c;
-      m = max8(max8(b[0], b[C8]), max8(b[(int64_t)Wp * C8], b[(int64_t)Wp * C8 + C8]));
+      const uint4* b = x + ((n * Hp + (IdxT)(2 * ho - 1)) * Wp + (IdxT)(2 * wo - 1)) * C8 + c;
+      m = max8(max8(b[0], b[C8]), max8(b[row], b[row + C8]));
     }
     y[i] = m;
   }
@@ -507,22 +509,31 @@ relu_bwd_colsum_wide_bf16x8_kernel(const uint4* __restrict__ dy, const uint4* __
   o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
-// out[c] (+)= sum_b partial[b][c]; 32 columns per block, 8 row lanes per column.
-__global__ void __launch_bounds__(256)
+// out[c] (+)= sum_b partial[b][c]; 32 columns per block, 32 row lanes per column, four loads in flight per thread
+// (the rows are few hundred: the kernel is a chain of dependent loads unless they are spread out).
+__global__ void __launch_bounds__(1024)
 colsum_final_fast_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ out,
                          int accumulate) {
-  __shared__ float sm[8][33];
+  __shared__ float sm[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
-  float s = 0.f;
-  if (c < C)
-    for (int b = ty; b < nblocks; b += 8) s += partial[(int64_t)b * C + c];
-  sm[ty][tx] = s;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < C) {
+    int b = ty;
+    for (; b + 96 < nblocks; b += 128) {
+      s0 += partial[(int64_t)b * C + c];
+      s1 += partial[(int64_t)(b + 32) * C + c];
+      s2 += partial[(int64_t)(b + 64) * C + c];
+      s3 += partial[(int64_t)(b + 96) * C + c];
+    }
+    for (; b < nblocks; b += 32) s0 += partial[(int64_t)b * C + c];
+  }
+  sm[ty][tx] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (ty == 0 && c < C) {
     float t = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t += sm[j][tx];
+    for (int j = 0; j < 32; ++j) t += sm[j][tx];
     out[c] = accumulate ? out[c] + t : t;
   }
 }
@@ -559,36 +570,51 @@ im2col3x3_rows_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t
   }
 }
 
-// The same for C == 3 (the first layer of the image models): one thread per (padded pixel row, 8 patch columns),
-// so a warp writes 512 contiguous bytes and the tap / channel of a column come from divisions by constants.
+// The same for C == 3 (the first layer of the image models).  One block per padded pixel row (n, hp): the three
+// source rows of the three channels are staged in shared memory with a zero halo (nine coalesced row reads serve
+// the 27 values of every pixel of the row), then each thread assembles 8 patch columns of a pixel and writes them
+// as one 16-byte vector, a warp writing 512 contiguous bytes.
 template <typename S>
 __global__ void __launch_bounds__(kThreads)
 im2col3x3_c3_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t sH, int64_t sW,
                     int N, int H, int W, int K8, uint4* __restrict__ dst) {
+  extern __shared__ float rows_sm[];          // [3 channels][3 rows][W + 2]
   const int Hp = H + 2, Wp = W + 2;
-  const int64_t total = (int64_t)N * Hp * Wp * K8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int q = (int)(i % K8);
-    const int64_t p = i / K8;
-    const int wp = (int)(p % Wp);
-    const int hp = (int)((p / Wp) % Hp);
-    const int n = (int)(p / ((int64_t)Wp * Hp));
-    float f[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = 0.f;
-    if (hp >= 1 && hp <= H && wp >= 1 && wp <= W && q * 8 < 27) {
-      const S* base = src + n * sN;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int k = q * 8 + j;
-        const int t = k / 3, c = k - t * 3;
-        const int r = t / 3, sx = t - r * 3;
-        const int h = hp - 2 + r, w = wp - 2 + sx;
-        if (k < 27 && h >= 0 && h < H && w >= 0 && w < W) f[j] = pd_to_float(base[c * sC + h * sH + w * sW]);
-      }
+  const int rows = N * Hp;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int n = row / Hp, hp = row - n * Hp;
+    uint4* out = dst + (int64_t)row * Wp * K8;
+    if (hp == 0 || hp == Hp - 1) {
+      for (int i = threadIdx.x; i < Wp * K8; i += blockDim.x) out[i] = zero;
+      continue;
     }
-    dst[i] = pack8(f);
+    __syncthreads();                          // the previous row's readers are done
+    for (int i = threadIdx.x; i < 9 * Wp; i += blockDim.x) {
+      const int cr = i / Wp, col = i - cr * Wp;          // cr = c * 3 + r
+      const int c = cr / 3, r = cr - c * 3;
+      const int h = hp - 2 + r, w = col - 1;
+      float v = 0.f;
+      if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(src[(int64_t)n * sN + c * sC + h * sH + w * sW]);
+      rows_sm[i] = v;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < Wp * K8; i += blockDim.x) {
+      const int wp = i / K8, q = i - wp * K8;
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      if (wp >= 1 && wp <= W && q * 8 < 27) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int k = q * 8 + j;
+          const int t = k / 3, c = k - t * 3;
+          const int r = t / 3, sx = t - r * 3;
+          if (k < 27) f[j] = rows_sm[(c * 3 + r) * Wp + wp - 1 + sx];
+        }
+      }
+      out[i] = pack8(f);
+    }
   }
 }
 
@@ -596,29 +622,30 @@ im2col3x3_c3_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t s
 // block leaves the column sums of the gradient it routed in partial[blockIdx.x][C] (the column sums of dx are the
 // sums of the routed values).  H and W even; gridDim.x * kThreads is a multiple of C8, so a thread stays on one
 // group of 8 channels; the border of dx is enumerated directly (2 * Wp + 2 * H pixels per image).
+template <typename IdxT>
 __global__ void __launch_bounds__(kThreads)
 maxpool2_bwd_colsum_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, int N, int C8, int H,
                                   int W, uint4* __restrict__ dx, int relu_mask, float* __restrict__ partial) {
   extern __shared__ float sm[];   // [kThreads / C8][C8 * 8] when partial != nullptr
   const int Ho = H / 2, Wo = W / 2;
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
-  const int64_t total = (int64_t)N * Ho * Wo * C8;
+  const IdxT total = (IdxT)N * Ho * Wo * C8;
+  const IdxT step = (IdxT)gridDim.x * blockDim.x;
+  const IdxT row = (IdxT)Wp * C8;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   float acc[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % C8);
-    const int64_t p = i / C8;
-    const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
-    const int64_t base = (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C8 + c;
+  for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const IdxT p = i / (IdxT)C8, q2 = p / (IdxT)Wo, n = q2 / (IdxT)Ho;
+    const int c = (int)(i - p * C8), wo = (int)(p - q2 * Wo), ho = (int)(q2 - n * Ho);
+    const IdxT base = ((n * Hp + (IdxT)(2 * ho + 1)) * Wp + (IdxT)(2 * wo + 1)) * C8 + c;
     float v[4][8], g[8];
     unpack8(x[base], v[0]);
     unpack8(x[base + C8], v[1]);
-    unpack8(x[base + (int64_t)Wp * C8], v[2]);
-    unpack8(x[base + (int64_t)Wp * C8 + C8], v[3]);
-    unpack8(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C8 + c], g);
+    unpack8(x[base + row], v[2]);
+    unpack8(x[base + row + C8], v[3]);
+    unpack8(dy[((n * Hop + (IdxT)(ho + 1)) * Wop + (IdxT)(wo + 1)) * C8 + c], g);
     float o[4][8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -633,21 +660,19 @@ maxpool2_bwd_colsum_bf16x8_kernel(const uint4* __restrict__ x, const uint4* __re
     }
     dx[base] = pack8(o[0]);
     dx[base + C8] = pack8(o[1]);
-    dx[base + (int64_t)Wp * C8] = pack8(o[2]);
-    dx[base + (int64_t)Wp * C8 + C8] = pack8(o[3]);
+    dx[base + row] = pack8(o[2]);
+    dx[base + row + C8] = pack8(o[3]);
   }
   const int per_image = 2 * Wp + 2 * H;
-  const int64_t border = (int64_t)N * per_image * C8;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < border;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % C8);
-    const int64_t p = i / C8;
-    const int b = (int)(p % per_image), n = (int)(p / per_image);
+  const IdxT border = (IdxT)N * per_image * C8;
+  for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < border; i += step) {
+    const IdxT p = i / (IdxT)C8, n = p / (IdxT)per_image;
+    const int c = (int)(i - p * C8), b = (int)(p - n * per_image);
     int hp, wp;
     if (b < Wp) { hp = 0; wp = b; }
     else if (b < 2 * Wp) { hp = Hp - 1; wp = b - Wp; }
     else { const int r = b - 2 * Wp; hp = 1 + (r >> 1); wp = (r & 1) ? Wp - 1 : 0; }
-    dx[(((int64_t)n * Hp + hp) * Wp + wp) * C8 + c] = zero;
+    dx[((n * Hp + (IdxT)hp) * Wp + (IdxT)wp) * C8 + c] = zero;
   }
   if (partial != nullptr) {
     // a thread's channel group: (blockIdx.x * kThreads + threadIdx.x) % C8 == threadIdx.x % C8 (kThreads % C8 == 0)
@@ -723,13 +748,14 @@ PD_EXPORT int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t s
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
   if (dst_dtype == PD_BF16 && (Kpad % 8) == 0 && ((uintptr_t)dst % 16) == 0) {
     const int64_t rows = (int64_t)N * (H + 2) * (W + 2);
-    if (C == 3) {
+    const size_t sm3 = (size_t)9 * (W + 2) * sizeof(float);
+    if (C == 3 && sm3 <= 48 * 1024 && rows * (Kpad / 8) < (1ll << 31)) {
       const int K8 = Kpad / 8;
-      const int g3 = grid_cap((rows * K8 + kThreads - 1) / kThreads, 16);
+      const int g3 = grid_cap((int64_t)N * (H + 2), 8);
       if (src_dtype == PD_F32)
-        im2col3x3_c3_kernel<float><<<g3, kThreads, 0, s>>>((const float*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
+        im2col3x3_c3_kernel<float><<<g3, kThreads, sm3, s>>>((const float*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
       else
-        im2col3x3_c3_kernel<__nv_bfloat16><<<g3, kThreads, 0, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
+        im2col3x3_c3_kernel<__nv_bfloat16><<<g3, kThreads, sm3, s>>>((const __nv_bfloat16*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
       PD_LAUNCH_CHECK("im2col3x3_c3_kernel");
       return PD_OK;
     }
@@ -796,11 +822,11 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
   if (dtype == PD_BF16 && (C % 8) == 0 && C / 8 <= kThreads && ((uintptr_t)dy % 16) == 0 &&
       (y == nullptr || ((uintptr_t)y % 16) == 0) && (dx == nullptr || ((uintptr_t)dx % 16) == 0)) {
     const int C8 = C / 8, lanes8 = kThreads / C8;
-    int g8 = grid_cap((rows + lanes8 - 1) / lanes8, 2);
+    int g8 = grid_cap((rows + lanes8 - 1) / lanes8, 8);
     relu_bwd_colsum_bf16x8_kernel<<<g8, kThreads, (size_t)lanes8 * C * sizeof(float), s>>>(
         (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
     PD_LAUNCH_CHECK("relu_bwd_colsum_bf16x8_kernel");
-    colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
+    colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
     PD_LAUNCH_CHECK("colsum_final_fast_kernel");
     return PD_OK;
   }
@@ -812,7 +838,7 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
     relu_bwd_colsum_wide_bf16x8_kernel<<<dim3((unsigned)gx, (unsigned)chunks), kThreads, 0, s>>>(
         (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
     PD_LAUNCH_CHECK("relu_bwd_colsum_wide_bf16x8_kernel");
-    colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, gx, C, colsum, accumulate);
+    colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, gx, C, colsum, accumulate);
     PD_LAUNCH_CHECK("colsum_final_fast_kernel");
     return PD_OK;
   }
@@ -822,7 +848,7 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
   size_t smem = C <= kThreads ? (size_t)lanes * C * sizeof(float) : 0;
   PD_DISPATCH_T(dtype, relu_bwd_colsum_kernel<T><<<grid, kThreads, smem, s>>>((const T*)dy, (const T*)y, (T*)dx, rows, C, (float*)workspace);)
   PD_LAUNCH_CHECK("relu_bwd_colsum_kernel");
-  colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
+  colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
   PD_LAUNCH_CHECK("colsum_final_fast_kernel");
   return PD_OK;
 }
@@ -837,8 +863,11 @@ PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y
   int64_t total = out_mode == 0 ? (int64_t)N * (H / 2 + 2) * (W / 2 + 2) * C : (int64_t)N * C * (H / 2) * (W / 2);
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
   if (dtype == PD_BF16 && out_mode == 0 && (C % 8) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
-    maxpool2_fwd_bf16x8_kernel<<<grid_cap((total / 8 + kThreads - 1) / kThreads, 16), kThreads, 0, s>>>(
-        (const uint4*)x, N, C / 8, H, W, (uint4*)y);
+    const int g8 = grid_cap((total / 8 + kThreads - 1) / kThreads, 16);
+    if ((int64_t)N * (H + 2) * (W + 2) * (C / 8) < (1ll << 31) - (int64_t)g8 * kThreads)
+      maxpool2_fwd_bf16x8_kernel<uint32_t><<<g8, kThreads, 0, s>>>((const uint4*)x, N, C / 8, H, W, (uint4*)y);
+    else
+      maxpool2_fwd_bf16x8_kernel<int64_t><<<g8, kThreads, 0, s>>>((const uint4*)x, N, C / 8, H, W, (uint4*)y);
     PD_LAUNCH_CHECK("maxpool2_fwd_bf16x8_kernel");
     return PD_OK;
   }
@@ -848,6 +877,10 @@ PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y
 }
 
 namespace {
+// 32-bit vector indices are enough (with room for one grid stride past the end)
+bool pool_idx32(int N, int C8, int H, int W, int grid) {
+  return (int64_t)N * (H + 2) * (W + 2) * C8 < (1ll << 31) - (int64_t)grid * kThreads;
+}
 bool pool_bwd_fast_ok(const void* x, const void* dy, const void* dx, int C, int H, int W, int dtype) {
   return dtype == PD_BF16 && (C % 8) == 0 && (kThreads % (C / 8)) == 0 && (H % 2) == 0 && (W % 2) == 0 &&
          (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) % 16) == 0;
@@ -870,8 +903,12 @@ PD_EXPORT int pd_maxpool2_bwd_colsum(const void* x, const void* dy, int N, int C
   const int C8 = C / 8;
   const int64_t win = (int64_t)N * (H / 2) * (W / 2) * C8;
   const int grid = grid_cap((win + kThreads - 1) / kThreads, 8);
-  maxpool2_bwd_colsum_bf16x8_kernel<<<grid, kThreads, (size_t)kThreads * 8 * sizeof(float), s>>>(
-      (const uint4*)x, (const uint4*)dy, N, C8, H, W, (uint4*)dx, relu_mask, partial);
+  if (pool_idx32(N, C8, H, W, grid))
+    maxpool2_bwd_colsum_bf16x8_kernel<uint32_t><<<grid, kThreads, (size_t)kThreads * 8 * sizeof(float), s>>>(
+        (const uint4*)x, (const uint4*)dy, N, C8, H, W, (uint4*)dx, relu_mask, partial);
+  else
+    maxpool2_bwd_colsum_bf16x8_kernel<int64_t><<<grid, kThreads, (size_t)kThreads * 8 * sizeof(float), s>>>(
+        (const uint4*)x, (const uint4*)dy, N, C8, H, W, (uint4*)dx, relu_mask, partial);
   PD_LAUNCH_CHECK("maxpool2_bwd_colsum_bf16x8_kernel");
   *partial_rows = grid;
   return PD_OK;
@@ -882,7 +919,7 @@ PD_EXPORT int pd_colsum_finish(const float* partial, int rows, int C, float* out
   int rc = pd_check_device();
   if (rc != PD_OK) return rc;
   PD_REQUIRE(partial && out && rows > 0 && C > 0, "pd_colsum_finish: bad arguments");
-  colsum_final_fast_kernel<<<(C + 31) / 32, 256, 0, (cudaStream_t)stream>>>(partial, rows, C, out, accumulate);
+  colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, (cudaStream_t)stream>>>(partial, rows, C, out, accumulate);
   PD_LAUNCH_CHECK("colsum_final_fast_kernel");
   return PD_OK;
 }
@@ -898,8 +935,13 @@ PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H
   int grid = grid_cap((total + kThreads - 1) / kThreads, 16);
   if (dy_mode == 0 && pool_bwd_fast_ok(x, dy, dx, C, H, W, dtype)) {
     const int64_t win = (int64_t)N * (H / 2) * (W / 2) * (C / 8);
-    maxpool2_bwd_colsum_bf16x8_kernel<<<grid_cap((win + kThreads - 1) / kThreads, 16), kThreads, 0, s>>>(
-        (const uint4*)x, (const uint4*)dy, N, C / 8, H, W, (uint4*)dx, relu_mask, nullptr);
+    const int g8 = grid_cap((win + kThreads - 1) / kThreads, 16);
+    if (pool_idx32(N, C / 8, H, W, g8))
+      maxpool2_bwd_colsum_bf16x8_kernel<uint32_t><<<g8, kThreads, 0, s>>>(
+          (const uint4*)x, (const uint4*)dy, N, C / 8, H, W, (uint4*)dx, relu_mask, nullptr);
+    else
+      maxpool2_bwd_colsum_bf16x8_kernel<int64_t><<<g8, kThreads, 0, s>>>(
+          (const uint4*)x, (const uint4*)dy, N, C / 8, H, W, (uint4*)dx, relu_mask, nullptr);
     PD_LAUNCH_CHECK("maxpool2_bwd_colsum_bf16x8_kernel");
     return PD_OK;
   }

@@ -308,9 +308,24 @@ def gemm_nn(a, b, relu_aux=None):
     return out
 
 
+_DETERMINISTIC = False
+
+
+def set_deterministic(flag):
+    """Weight gradients are normally split along their long contraction (the pixels / tokens of the minibatch) over
+    several CTAs that add their parts with fp32 atomics, in an order that changes from run to run (last-bit
+    differences).  With this switch every weight gradient is computed without the split: bit-identical from run to
+    run, and several times slower for the layers with few output tiles.  Returns the previous setting."""
+    global _DETERMINISTIC
+    prev, _DETERMINISTIC = _DETERMINISTIC, bool(flag)
+    return prev
+
+
 def gemm_tn(a, b, out, accumulate=False, split_k=0):
     """out[M,N] (fp32, any leading dim) (+)= a[K,M]^T . b[K,N]."""
     _cuda(a, b, out)
+    if _DETERMINISTIC and split_k == 0:
+        split_k = 1
     K, M = a.shape
     N = b.shape[1]
     assert out.dtype == torch.float32
@@ -344,6 +359,8 @@ def conv2d_wgrad(x_pad, dy_pad, dw, lddw, accumulate=False, split_k=0):
     N, Hp, Wp, Cin = x_pad.shape
     Cout = dy_pad.shape[3]
     assert dw.dtype == torch.float32
+    if _DETERMINISTIC and split_k == 0:
+        split_k = 1
     _timed("conv_wgrad", 18.0 * N * (Hp - 2) * (Wp - 2) * Cin * Cout, lambda: call(
         "pd_conv2d_wgrad", dt(x_pad), _p(x_pad), _p(dy_pad), N, Hp - 2, Wp - 2, Cin, Cout, _p(dw), lddw,
         int(accumulate), int(split_k), _stream()), (N, Hp - 2, Cin, Cout))

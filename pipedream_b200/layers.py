@@ -70,6 +70,22 @@ def _dense2d(t, rows, cols):
 # --------------------------------------------------------------------------- #
 # Conv2d 3x3 / stride 1 / pad 1
 # --------------------------------------------------------------------------- #
+_SIDE_STREAMS = {}
+
+
+def _bias_grad_beside(dy_pad, colsum, accumulate):
+    """Column sums of dy_pad into `colsum` on the device's second stream, ordered after the work queued on the current
+    stream so far.  Returns the stream; the caller makes the current stream wait for it."""
+    dev = dy_pad.device
+    side = _SIDE_STREAMS.get(dev.index)
+    if side is None:
+        side = _SIDE_STREAMS[dev.index] = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        pf.relu_bwd_colsum(dy_pad, None, None, colsum, accumulate)
+    return side
+
+
 class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, fuse_relu, out_nchw):
@@ -109,12 +125,17 @@ class _Conv3x3Fn(torch.autograd.Function):
         # saved tensor aliases the parameter storage.
         w = wp.detach()
         dy_pad = pf.as_padded(dy, w.dtype)
+        side = None
         # ReLU mask and bias gradient in one pass over dy; if the consumer's backward already applied
         # this layer's mask (see ctx.premask), only the bias gradient is left to do
         if ctx.fuse_relu and getattr(dy, "_pd_premasked", False) and pf.padded_of(dy) is not None:
             dym = dy_pad
             if bp is not None and getattr(dy, "_pd_colsum", None) is not None:
                 pf.colsum_finish(dy._pd_colsum, grad_buffer(bp), take_accumulate_flag(bp))
+            elif bp is not None and ctx.direct and ctx.needs_input_grad[0]:
+                # a read-only pass over dy (bound by HBM): it runs on a second stream beside the data-gradient
+                # contraction (bound by the tensor pipe); the main stream joins it before the weight gradient
+                side = _bias_grad_beside(dy_pad, grad_buffer(bp), take_accumulate_flag(bp))
             elif bp is not None:
                 pf.relu_bwd_colsum(dy_pad, None, None, grad_buffer(bp), take_accumulate_flag(bp))
         elif ctx.fuse_relu:
@@ -131,12 +152,16 @@ class _Conv3x3Fn(torch.autograd.Function):
         dx = None
         if ctx.direct:
             x_pad = ctx.x_saved
-            pf.conv2d_wgrad(x_pad, dym, gw, gw.stride(0), accumulate=take_accumulate_flag(wp))
             if ctx.needs_input_grad[0]:
                 dx_pad = pf.conv2d_dgrad(dym, w, w.stride(0), Cin, relu_aux=x_pad if ctx.premask else None)
                 dx = pf.nchw_view(dx_pad, N, Cin, H, W)
                 if ctx.premask:
                     dx._pd_premasked = True
+            if side is not None:
+                # before the weight's gradient is announced: a gradient bucket that closes on that announcement
+                # orders its all-reduce after the main stream, which must already include the bias gradient
+                torch.cuda.current_stream(dym.device).wait_stream(side)
+            pf.conv2d_wgrad(x_pad, dym, gw, gw.stride(0), accumulate=take_accumulate_flag(wp))
         else:
             kpad = w.stride(0)
             pf.gemm_tn(dym.view(-1, Cout), ctx.x_saved, _dense2d(gw, Cout, kpad), accumulate=take_accumulate_flag(wp))

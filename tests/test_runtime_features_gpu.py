@@ -60,13 +60,24 @@ def spread(losses, want, params, want_params):
     return dl, dp
 
 
+@pytest.fixture(autouse=True)
+def deterministic_weight_gradients():
+    """Split-K weight gradients add their parts with fp32 atomics in a varying order, and this un-normalised network
+    amplifies a last-bit difference into a visible one within a few steps; the tests here compare whole runs, so
+    they switch the split off (pf.set_deterministic) and can then ask for (near) equality."""
+    prev = pf.set_deterministic(True)
+    yield
+    pf.set_deterministic(prev)
+
+
 def same_run(losses, want, params, want_params, fp16, noise=(0.0, 0.0)):
-    """Within the stated bar, or within a small multiple of the plain path's own run-to-run spread `noise`
-    (this un-normalised network amplifies last-bit differences from step to step)."""
+    """Within the stated bar (the plain path's own run-to-run spread `noise` is asserted to be zero first)."""
+    assert noise == (0.0, 0.0), "two plain runs differ in deterministic mode: %r" % (noise,)
     ltol, ptol = (2e-3, 1e-2) if fp16 else (1e-5, 1e-5)
     dl, dp = spread(losses, want, params, want_params)
-    assert dl <= max(ltol, 4 * noise[0]), (dl, noise, losses, want)
-    assert dp <= max(ptol, 4 * noise[1]), (dp, noise)
+    print("difference (loss, parameters):", (dl, dp))
+    assert dl <= ltol, (dl, losses, want)
+    assert dp <= ptol, dp
 
 
 @pytest.mark.parametrize("fp16", [False, True], ids=["fp32", "bf16"])
@@ -78,7 +89,6 @@ def test_recompute_matches_plain_run(fp16):
     ref_params = params_of(base)
     again = small_pipeline(fp16)
     noise = spread(run_steps(again, 6, 11), ref_losses, params_of(again), ref_params)
-    print("run-to-run spread of the plain path (loss, parameters):", noise)
     rec = small_pipeline(fp16, enable_recompute=True)
     assert rec.workers[0][0].enable_recompute and not rec.workers[1][0].enable_recompute
     losses = run_steps(rec, 6, 11)
