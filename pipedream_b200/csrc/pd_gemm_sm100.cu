@@ -642,6 +642,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_ld32(tmem_acc + (uint32_t)cc, r0);
         if (two) tmem_ld32(tmem_acc + (uint32_t)(cc + 32), r1);
         tmem_ld_wait();
+        if (cc + 64 >= total_cols) {
+          // the accumulator is in registers now: hand it back to the MMA warp before the arithmetic and the stores
+          // of this last pair of chunks (an arrive after them would also wait for the stores to be performed)
+          __syncwarp();
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          if (lane == 0) {
+            if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[bar0 + buf]));
+            else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[bar0 + buf]), 0));
+          }
+        }
         if (row_ok) {
           {
             const int a = accn == 1 ? 0 : cc / p.block_n, c0 = cc - a * p.block_n;
@@ -652,13 +662,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (n0 + c0 < p.N) epilogue_chunk(p, r1, m, n0 + c0, (long long)(acc0 + a) * p.z_out_col, border);
           }
         }
-      }
-      // this warp has read everything it needs from the accumulator: hand it back to the MMA warp
-      __syncwarp();
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      if (lane == 0) {
-        if (leader) mbar_arrive(smem_u32(&tmem_empty_bar[bar0 + buf]));
-        else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[bar0 + buf]), 0));
       }
       PD_NEXT_LOCAL
     }
