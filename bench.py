@@ -369,6 +369,8 @@ def run_profile_case_other(name):
     captures; prints the kernel's algorithmic bytes per launch (what its roofline fraction is measured against):
     sgd / adam : the fused optimizer over a 2-version ring, 64 M bf16 parameters with fp32 master copy;
     softmax_ce : criterion forward + backward on [6400, 32320] bf16 logits (GNMT: 50 steps x 128 pairs);
+    pool       : 2x2 max-pool forward, backward fused with the bias-gradient sums, the sums alone, the first layer's
+                 patch matrix, on a [16, 64, 224, 224] bf16 activation;
     bn         : BatchNorm2d training forward + backward on a padded-NHWC [64, 58, 58, 256] bf16 tensor;
     layernorm  : LayerNorm forward + backward on [65536, 1024] bf16 rows;
     lstm       : one LSTM layer's recurrence, T = 50, B = 128, H = 1024, forward + backward;
@@ -406,6 +408,24 @@ def run_profile_case_other(name):
             loss, lse, _ = pf.softmax_ce_fwd(logits, target, 0.1, 0, 1.0)
             pf.softmax_ce_bwd(logits, target, lse, 0.1, 0, up, 1.0)
         info["algorithmic_bytes_per_launch"] = {"forward (read logits)": rows * C * 2, "backward (read logits, write gradient)": rows * C * 4}
+    elif name == "pool":
+        # conv1_2's output of VGG-16 at a quarter of the batch: [16, 226, 226, 64] bf16 (105 MB) and its pooled gradient
+        N, H, C = 16, 224, 64
+        x = pf.pack_pnhwc(torch.randn(N, C, H, H, generator=g).cuda().to(bf).relu())
+        dy = pf.pack_pnhwc(torch.randn(N, C, H // 2, H // 2, generator=g).cuda().to(bf))
+        img = torch.randn(N, 3, H, H, generator=g).cuda()
+        cs = torch.zeros(C, device="cuda")
+        for _ in range(3):
+            pf.maxpool2_fwd(x, False)
+            dx, part = pf.maxpool2_bwd_colsum(x, dy, True)
+            pf.colsum_finish(part, cs, False)
+            pf.relu_bwd_colsum(dx, None, None, cs, False)
+            pf.im2col3x3(img, 32, bf)
+        info["algorithmic_bytes_per_launch"] = {
+            "maxpool2_fwd (read x, write y)": x.numel() * 2 + dy.numel() * 2,
+            "maxpool2_bwd_colsum (read x and dy, write dx)": 2 * x.numel() * 2 + dy.numel() * 2,
+            "relu_bwd_colsum, sums only (read dy)": x.numel() * 2,
+            "im2col3x3 (read the images, write 64-byte patch rows)": img.numel() * 4 + N * (H + 2) * (H + 2) * 64}
     elif name == "bn":
         N, H, C = 64, 56, 256
         x = pf.pack_pnhwc(torch.randn(N, C, H, H, generator=g).cuda().to(bf))
@@ -515,11 +535,11 @@ def main():
     ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50", "gpt"],
                     help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT), resnet50 or gpt (24-layer 2BW decoder)")
     ap.add_argument("--profile-case", default=None,
-                    choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd", "sgd", "adam", "softmax_ce", "bn",
+                    choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd", "sgd", "adam", "softmax_ce", "pool", "bn",
                              "layernorm", "lstm", "attn"],
                     help="run a few launches of one kernel family on a small case (for ncu) and exit")
     a = ap.parse_args()
-    if a.profile_case in ("sgd", "adam", "softmax_ce", "bn", "layernorm", "lstm", "attn"):
+    if a.profile_case in ("sgd", "adam", "softmax_ce", "pool", "bn", "layernorm", "lstm", "attn"):
         run_profile_case_other(a.profile_case)
         return
     if a.profile_case:

@@ -509,31 +509,33 @@ relu_bwd_colsum_wide_bf16x8_kernel(const uint4* __restrict__ dy, const uint4* __
   o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
-// out[c] (+)= sum_b partial[b][c]; 32 columns per block, 32 row lanes per column, four loads in flight per thread
-// (the rows are few hundred: the kernel is a chain of dependent loads unless they are spread out).
+// out[c] (+)= sum_b partial[b][c].  The partial rows are a few hundred to a thousand and C is small, so the kernel is
+// a latency chain unless the rows are spread wide: 8 columns per block, 128 threads per column (four warps, each
+// lane summing every 128th row with independent loads), a shuffle tree per warp and one thread per column at the end.
 __global__ void __launch_bounds__(1024)
 colsum_final_fast_kernel(const float* __restrict__ partial, int nblocks, int C, float* __restrict__ out,
                          int accumulate) {
-  __shared__ float sm[32][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + tx;
+  __shared__ float sm[8][4];
+  const int col = threadIdx.x >> 7, r = threadIdx.x & 127;
+  const int c = blockIdx.x * 8 + col;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   if (c < C) {
-    int b = ty;
-    for (; b + 96 < nblocks; b += 128) {
+    int b = r;
+    for (; b + 384 < nblocks; b += 512) {
       s0 += partial[(int64_t)b * C + c];
-      s1 += partial[(int64_t)(b + 32) * C + c];
-      s2 += partial[(int64_t)(b + 64) * C + c];
-      s3 += partial[(int64_t)(b + 96) * C + c];
+      s1 += partial[(int64_t)(b + 128) * C + c];
+      s2 += partial[(int64_t)(b + 256) * C + c];
+      s3 += partial[(int64_t)(b + 384) * C + c];
     }
-    for (; b < nblocks; b += 32) s0 += partial[(int64_t)b * C + c];
+    for (; b < nblocks; b += 128) s0 += partial[(int64_t)b * C + c];
   }
-  sm[ty][tx] = (s0 + s1) + (s2 + s3);
-  __syncthreads();
-  if (ty == 0 && c < C) {
-    float t = 0.f;
+  float s = (s0 + s1) + (s2 + s3);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) t += sm[j][tx];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) sm[col][r >> 5] = s;
+  __syncthreads();
+  if (r == 0 && c < C) {
+    const float t = (sm[col][0] + sm[col][1]) + (sm[col][2] + sm[col][3]);
     out[c] = accumulate ? out[c] + t : t;
   }
 }
@@ -590,13 +592,23 @@ im2col3x3_c3_kernel(const S* __restrict__ src, int64_t sN, int64_t sC, int64_t s
       continue;
     }
     __syncthreads();                          // the previous row's readers are done
-    for (int i = threadIdx.x; i < 9 * Wp; i += blockDim.x) {
-      const int cr = i / Wp, col = i - cr * Wp;          // cr = c * 3 + r
-      const int c = cr / 3, r = cr - c * 3;
-      const int h = hp - 2 + r, w = col - 1;
-      float v = 0.f;
-      if (h >= 0 && h < H && w >= 0 && w < W) v = pd_to_float(src[(int64_t)n * sN + c * sC + h * sH + w * sW]);
-      rows_sm[i] = v;
+    for (int i0 = 0; i0 < 9 * Wp; i0 += 8 * kThreads) {
+      float v[8];                                          // eight loads in flight per thread
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * kThreads + threadIdx.x;
+        const int cr = i / Wp, col = i - cr * Wp;          // cr = c * 3 + r
+        const int c = cr / 3, r = cr - c * 3;
+        const int h = hp - 2 + r, w = col - 1;
+        v[u] = 0.f;
+        if (i < 9 * Wp && h >= 0 && h < H && w >= 0 && w < W)
+          v[u] = pd_to_float(src[(int64_t)n * sN + c * sC + h * sH + w * sW]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * kThreads + threadIdx.x;
+        if (i < 9 * Wp) rows_sm[i] = v[u];
+      }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < Wp * K8; i += blockDim.x) {
@@ -826,7 +838,7 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
     relu_bwd_colsum_bf16x8_kernel<<<g8, kThreads, (size_t)lanes8 * C * sizeof(float), s>>>(
         (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
     PD_LAUNCH_CHECK("relu_bwd_colsum_bf16x8_kernel");
-    colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
+    colsum_final_fast_kernel<<<(C + 7) / 8, 1024, 0, s>>>((const float*)workspace, g8, C, colsum, accumulate);
     PD_LAUNCH_CHECK("colsum_final_fast_kernel");
     return PD_OK;
   }
@@ -838,7 +850,7 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
     relu_bwd_colsum_wide_bf16x8_kernel<<<dim3((unsigned)gx, (unsigned)chunks), kThreads, 0, s>>>(
         (const uint4*)dy, (const uint4*)y, (uint4*)dx, rows, C8, (float*)workspace);
     PD_LAUNCH_CHECK("relu_bwd_colsum_wide_bf16x8_kernel");
-    colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, gx, C, colsum, accumulate);
+    colsum_final_fast_kernel<<<(C + 7) / 8, 1024, 0, s>>>((const float*)workspace, gx, C, colsum, accumulate);
     PD_LAUNCH_CHECK("colsum_final_fast_kernel");
     return PD_OK;
   }
@@ -848,7 +860,7 @@ PD_EXPORT int pd_relu_bwd_colsum(const void* dy, const void* y, void* dx, int64_
   size_t smem = C <= kThreads ? (size_t)lanes * C * sizeof(float) : 0;
   PD_DISPATCH_T(dtype, relu_bwd_colsum_kernel<T><<<grid, kThreads, smem, s>>>((const T*)dy, (const T*)y, (T*)dx, rows, C, (float*)workspace);)
   PD_LAUNCH_CHECK("relu_bwd_colsum_kernel");
-  colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
+  colsum_final_fast_kernel<<<(C + 7) / 8, 1024, 0, s>>>((const float*)workspace, grid, C, colsum, accumulate);
   PD_LAUNCH_CHECK("colsum_final_fast_kernel");
   return PD_OK;
 }
@@ -919,7 +931,7 @@ PD_EXPORT int pd_colsum_finish(const float* partial, int rows, int C, float* out
   int rc = pd_check_device();
   if (rc != PD_OK) return rc;
   PD_REQUIRE(partial && out && rows > 0 && C > 0, "pd_colsum_finish: bad arguments");
-  colsum_final_fast_kernel<<<(C + 31) / 32, 1024, 0, (cudaStream_t)stream>>>(partial, rows, C, out, accumulate);
+  colsum_final_fast_kernel<<<(C + 7) / 8, 1024, 0, (cudaStream_t)stream>>>(partial, rows, C, out, accumulate);
   PD_LAUNCH_CHECK("colsum_final_fast_kernel");
   return PD_OK;
 }
