@@ -495,11 +495,22 @@ class SpecStage(nn.Module):
             setattr(self, name, self.TYPES[kind](**kw))
         self._flow = [tuple(st) for st in spec["flow"]]
         self._returns = list(spec["returns"])
+        # "init": "generator" = what the generator appends for its vgg16 / resnet50 targets
+        # (optimizer/convert_graph_to_model.py:331-344: zero convolution biases and N(0, 0.01) Linear weights as well);
+        # "none" = torch's defaults; otherwise the initialisation of the shipped resnet50 stage files
+        init = spec.get("init", "shipped")
         for m in self.modules():
+            if init == "none":
+                break
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+                if init == "generator" and m.bias is not None:
+                    nn.init.constant_(m.bias, 0)
             elif isinstance(m, nn.BatchNorm2d):
                 nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+            elif init == "generator" and isinstance(m, nn.Linear):
+                nn.init.normal_(m.weight, 0, 0.01)
                 nn.init.constant_(m.bias, 0)
 
     def forward(self, *inputs):

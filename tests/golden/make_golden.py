@@ -595,6 +595,8 @@ def describe_stage(stage):
             kw = {"kernel_size": m.kernel_size, "stride": m.stride, "padding": m.padding}
         elif kind == "Linear":
             kw = {"in_features": m.in_features, "out_features": m.out_features, "bias": m.bias is not None}
+        elif kind == "Dropout":
+            kw = {"p": m.p}
         else:
             raise ValueError("unexpected module type %s" % kind)
         mods.append([name, kind, kw])
@@ -661,6 +663,161 @@ def make_resnet50(ref, steps=6, batch=8):
 
 
 # ----------------------------------------------------------------------------- GNMT (8+8 layers)
+# --------------------------------------------------------------------------- #
+# stage generator: the reference's generator run on two small partitioned graphs written for this purpose
+# --------------------------------------------------------------------------- #
+def _graph_text(nodes, edges):
+    """Profile-graph text (graph/graph.py:451-461) from [(id, description, stage)] and [(src, dst)]."""
+    lines = ["%s -- %s -- forward_compute_time=1.000, backward_compute_time=2.000, activation_size=4096.000, "
+             "parameter_size=0.000 -- stage_id=%d" % (i, d, s) for (i, d, s) in nodes]
+    lines += ["\t%s -- %s" % e for e in edges]
+    return "\n".join(lines)
+
+
+def stagegen_graphs():
+    """Two partitioned graphs in the profiler's format: a VGG-like chain cut into three stages (the classifier's
+    x.view(x.size(0), -1) straddles nothing) and a small residual network cut into three stages so that the
+    first cut crosses an identity shortcut (two tensors over the boundary) and the second one a projection
+    shortcut.  Node ids are deliberately not in topological order."""
+    conv = "Conv2d(%d, %d, kernel_size=(3, 3), stride=(%d, %d), padding=(1, 1)%s)"
+    chain = [("node1", "Input", 0),
+             ("node2", conv % (3, 8, 1, 1, ""), 0), ("node3", "ReLU(inplace)", 0),
+             ("node4", "MaxPool2d(kernel_size=2, stride=2, padding=0, dilation=1, ceil_mode=False)", 0),
+             ("node5", conv % (8, 16, 1, 1, ""), 1), ("node6", "ReLU(inplace)", 1),
+             ("node7", "MaxPool2d(kernel_size=2, stride=2, padding=0, dilation=1, ceil_mode=False)", 1),
+             ("node8", "Size(0)", 1), ("node9", "View(-1)", 1),
+             ("node10", "Linear(in_features=64, out_features=32, bias=True)", 1), ("node11", "ReLU(inplace)", 1),
+             ("node12", "Dropout(p=0.5)", 2), ("node13", "Linear(in_features=32, out_features=10, bias=True)", 2)]
+    chain_edges = [("node1", "node2"), ("node2", "node3"), ("node3", "node4"), ("node4", "node5"), ("node5", "node6"),
+                   ("node6", "node7"), ("node7", "node8"), ("node7", "node9"), ("node8", "node9"), ("node9", "node10"),
+                   ("node10", "node11"), ("node11", "node12"), ("node12", "node13")]
+    bn = "BatchNorm2d(%d, eps=1e-05, momentum=0.1, affine=True, track_running_stats=True)"
+    nb = ", bias=False"
+    res = [("node1", "Input", 0),
+           ("node2", conv % (3, 8, 1, 1, nb), 0), ("node3", bn % 8, 0), ("node4", "ReLU(inplace)", 0),
+           # identity block: conv-bn-relu-conv-bn (+ node4) relu; the cut falls after the first ReLU of the block
+           ("node21", conv % (8, 8, 1, 1, nb), 0), ("node20", bn % 8, 0), ("node19", "ReLU(inplace)", 0),
+           ("node18", conv % (8, 8, 1, 1, nb), 1), ("node17", bn % 8, 1), ("node16", "Add", 1), ("node15", "ReLU(inplace)", 1),
+           # projection block: main path conv(s2)-bn-relu-conv-bn, shortcut conv1x1(s2)-bn; cut inside the main path
+           ("node30", conv % (8, 16, 2, 2, nb), 1), ("node31", bn % 16, 1), ("node32", "ReLU(inplace)", 1),
+           ("node33", conv % (16, 16, 1, 1, nb), 2), ("node34", bn % 16, 2),
+           ("node35", "Conv2d(8, 16, kernel_size=(1, 1), stride=(2, 2), bias=False)", 2), ("node36", bn % 16, 2),
+           ("node37", "Add", 2), ("node38", "ReLU(inplace)", 2),
+           ("node39", "AvgPool2d(kernel_size=4, stride=1, padding=0)", 2), ("node40", "Size(0)", 2), ("node41", "View(-1)", 2),
+           ("node42", "Linear(in_features=16, out_features=10, bias=True)", 2)]
+    res_edges = [("node1", "node2"), ("node2", "node3"), ("node3", "node4"), ("node4", "node21"), ("node21", "node20"),
+                 ("node20", "node19"), ("node19", "node18"), ("node18", "node17"), ("node17", "node16"), ("node4", "node16"),
+                 ("node16", "node15"), ("node15", "node30"), ("node30", "node31"), ("node31", "node32"), ("node32", "node33"),
+                 ("node33", "node34"), ("node15", "node35"), ("node35", "node36"), ("node34", "node37"), ("node36", "node37"),
+                 ("node37", "node38"), ("node38", "node39"), ("node39", "node40"), ("node39", "node41"), ("node40", "node41"),
+                 ("node41", "node42")]
+    return {"chain": ("vgg16", _graph_text(chain, chain_edges), (2, 3, 8, 8)),
+            "residual": ("resnet50", _graph_text(res, res_edges), (2, 3, 8, 8))}
+
+
+def _run_reference_generator(ref, text, arch, workdir):
+    """optimizer/convert_graph_to_model.py as its authors run it (a script, from its own directory), on `text`."""
+    os.makedirs(workdir, exist_ok=True)
+    gpath = os.path.join(workdir, "graph.txt")
+    with open(gpath, "w") as f:
+        f.write(text)
+    out = os.path.join(workdir, "pkg")
+    # graph/graph.py imports graphviz for its plots (not installed here, not used by the generator): an empty stand-in
+    stubs = os.path.join(workdir, "stubs")
+    os.makedirs(stubs, exist_ok=True)
+    open(os.path.join(stubs, "graphviz.py"), "w").close()
+    env = dict(os.environ, PYTHONPATH=stubs + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    subprocess.check_call([sys.executable, "convert_graph_to_model.py", "-f", gpath, "-n", "Net", "-a", arch, "-o", out],
+                          cwd=os.path.join(ref, "optimizer"), stdout=subprocess.DEVNULL, env=env)
+    return out
+
+
+def _load_generated(pkg_dir, tag):
+    """The generated package imported under a unique name; returns model(criterion) of its __init__."""
+    import importlib.util
+    name = "generated_%s" % tag
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _canonical(desc):
+    """A description with every assignment of a stage's dataflow given a fresh number in order (so `a = a + b` and
+    `c = a + b` read the same) and the keyword arguments of the declarations in sorted order."""
+    out = {"arch": desc["arch"], "stages": []}
+    for st in desc["stages"]:
+        cur, flow = {}, []
+        for stt in st["flow"]:
+            res, op, args = stt[0], stt[1], stt[2:]
+            args = [cur[a] if isinstance(a, str) else a for a in args]
+            cur[res] = "v%d" % len(flow)
+            flow.append([cur[res], op] + args)
+        out["stages"].append({"modules": [[n, k, dict(sorted(kw.items()))] for n, k, kw in st["modules"]], "flow": flow,
+                              "returns": [cur[r] for r in st["returns"]],
+                              "inputs": list(st["inputs"]), "outputs": list(st["outputs"])})
+    return out
+
+
+def make_stagegen(ref):
+    import hashlib
+    import tempfile
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from pipedream_b200 import stagegen, stages as pd_stages
+    golden = {"graphs": {}, "checked_on_reference_graphs": {}}
+    work = tempfile.mkdtemp(prefix="pd_stagegen_")
+
+    def generated_description(text, arch, tag):
+        pkg = _run_reference_generator(ref, text, arch, os.path.join(work, tag))
+        mod = _load_generated(pkg, tag)
+        torch.manual_seed(0)
+        model = mod.model(torch.nn.CrossEntropyLoss())
+        desc = {"arch": mod.arch(), "stages": []}
+        for (m, ins, outs) in model[:-1]:
+            d = describe_stage(m)
+            d["inputs"], d["outputs"] = list(ins), list(outs)
+            desc["stages"].append(d)
+        return desc, model
+
+    for name, (arch, text, shape) in stagegen_graphs().items():
+        desc, model = generated_description(text, arch, name)
+        mine = stagegen.describe(text, arch)
+        assert _canonical(mine) == _canonical(desc), name
+        # the generated stages run on a seeded input; the description built here must give the same numbers
+        torch.manual_seed(1)
+        x = torch.randn(*shape)
+        vals = {"input0": x}
+        for (m, ins, outs) in model[:-1]:
+            m.eval()
+            r = m(*[vals[i] for i in ins])
+            r = r if isinstance(r, tuple) else (r,)
+            vals.update(dict(zip(outs, r)))
+        last = model[-2][2][0]
+        sd = {}
+        for si, (m, _, _) in enumerate(model[:-1]):
+            for k, v in m.state_dict().items():
+                sd["%d.%s" % (si, k)] = tensor_checksum(v)
+        golden["graphs"][name] = {"arch": arch, "text": text, "input_shape": list(shape), "description": desc,
+                                  "output": vals[last].detach().double().flatten().tolist(), "state_dict": sd}
+    # the reference's own partitioned test graphs: checked here, where the reference is at hand; only the outcome,
+    # the stage count and the file's digest are recorded
+    for fname, arch in (("vgg16_partitioned.txt", "vgg16"), ("resnet50_partitioned.txt", "resnet50")):
+        path = os.path.join(ref, "graph", "test_graphs", fname)
+        text = open(path).read()
+        desc, _ = generated_description(text, arch, fname.split(".")[0])
+        mine = stagegen.describe(text, arch)
+        same = _canonical(mine) == _canonical(desc)
+        assert same, fname
+        golden["checked_on_reference_graphs"][fname] = {
+            "sha256": hashlib.sha256(text.encode()).hexdigest(), "stages": len(desc["stages"]),
+            "modules": sum(len(s["modules"]) for s in desc["stages"]), "equal_to_generator_output": same}
+    with open(os.path.join(HERE, "stagegen_golden.json"), "w") as f:
+        json.dump(golden, f, indent=1)
+    print("wrote stagegen_golden.json", golden["checked_on_reference_graphs"])
+
+
 def _inject_pack_utils():
     """Pure-torch stand-in for the reference's pack_utils CUDA extension (csrc/pack_utils_kernel.cu:24-63,
     pack_utils.cpp:13-31), which does not build against current PyTorch."""
@@ -871,6 +1028,9 @@ if __name__ == "__main__":
         if a.only in (None, "signatures"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_signatures(%r)" % (HERE, a.ref)])
+        if a.only in (None, "stagegen"):
+            subprocess.check_call([sys.executable, "-c",
+                                   "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_stagegen(%r)" % (HERE, a.ref)])
         if a.only in (None, "stashing"):
             subprocess.check_call([sys.executable, "-O", "-c",
                                    "import sys; sys.path.insert(0, %r); import make_golden; make_golden.make_stashing(%r)" % (HERE, a.ref)])

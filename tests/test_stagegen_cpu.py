@@ -1,0 +1,101 @@
+"""Stage generator front end (pipedream_b200/stagegen.py) against the reference's generator
+(optimizer/convert_graph_to_model.py): tests/golden/stagegen_golden.json holds two small partitioned graphs written
+for this test, what the reference's generator made of them (its generated stage modules, described), their
+parameters under seed 0 and their output on a seeded input.  The same comparison on the reference's own
+vgg16 / resnet50 test graphs was made when the golden file was written (make_golden.py --only stagegen); the file
+records its outcome."""
+import json
+import os
+
+import pytest
+import torch
+
+from pipedream_b200 import stagegen, stages
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = json.load(open(os.path.join(HERE, "golden", "stagegen_golden.json")))
+
+
+def canonical(desc):
+    """Every assignment of a stage's dataflow numbered in order (`a = a + b` and `c = a + b` read the same)."""
+    out = []
+    for st in desc["stages"]:
+        cur, flow = {}, []
+        for stt in st["flow"]:
+            args = [cur[a] if isinstance(a, str) else a for a in stt[2:]]
+            cur[stt[0]] = "v%d" % len(flow)
+            flow.append([cur[stt[0]], stt[1]] + args)
+        out.append({"modules": [[n, k, dict(sorted(kw.items()))] for n, k, kw in st["modules"]], "flow": flow,
+                    "returns": [cur[r] for r in st["returns"]], "inputs": list(st["inputs"]), "outputs": list(st["outputs"])})
+    return out
+
+
+def checksum(t):
+    t = t.detach().double().flatten()
+    k = min(8, t.numel())
+    idx = torch.tensor([(j * (t.numel() - 1)) // max(1, k - 1) for j in range(k)], dtype=torch.long)
+    return {"sum": t.sum().item(), "abs_sum": t.abs().sum().item(), "sq_sum": (t * t).sum().item(), "samples": t[idx].tolist()}
+
+
+@pytest.mark.parametrize("name", sorted(GOLD["graphs"]))
+def test_description_equals_the_generators(name):
+    g = GOLD["graphs"][name]
+    mine = stagegen.describe(g["text"], g["arch"])
+    assert canonical(mine) == canonical(g["description"])
+    # names the runtime and checkpoints depend on
+    for a, b in zip(mine["stages"], g["description"]["stages"]):
+        assert [m[0] for m in a["modules"]] == [m[0] for m in b["modules"]]
+        assert a["inputs"] == b["inputs"] and a["outputs"] == b["outputs"]
+
+
+@pytest.mark.parametrize("name", sorted(GOLD["graphs"]))
+def test_stages_built_from_the_description_match_the_generated_modules(name):
+    g = GOLD["graphs"][name]
+    pkg = stages.SpecPackage(stagegen.describe(g["text"], g["arch"]))
+    torch.manual_seed(0)
+    model = pkg.model(torch.nn.CrossEntropyLoss())
+    got = {}
+    for si, (m, _, _) in enumerate(model[:-1]):
+        for k, v in m.state_dict().items():
+            got["%d.%s" % (si, k)] = checksum(v)
+    assert sorted(got) == sorted(g["state_dict"])
+    for k, want in g["state_dict"].items():
+        assert got[k]["samples"] == pytest.approx(want["samples"], rel=1e-6, abs=1e-7), k
+        assert got[k]["sq_sum"] == pytest.approx(want["sq_sum"], rel=1e-6, abs=1e-9), k
+    torch.manual_seed(1)
+    vals = {"input0": torch.randn(*g["input_shape"])}
+    for (m, ins, outs) in model[:-1]:
+        m.eval()
+        r = m(*[vals[i] for i in ins])
+        vals.update(dict(zip(outs, r if isinstance(r, tuple) else (r,))))
+    out = vals[model[-2][2][0]].detach().double().flatten()
+    assert torch.allclose(out, torch.tensor(g["output"], dtype=torch.float64), rtol=1e-5, atol=1e-6)
+    assert model[-1][1] == [model[-2][2][0]] and model[-1][2] == ["loss"]
+
+
+def test_the_reference_graphs_were_checked_when_the_golden_file_was_written():
+    rec = GOLD["checked_on_reference_graphs"]
+    assert set(rec) == {"vgg16_partitioned.txt", "resnet50_partitioned.txt"}
+    assert all(r["equal_to_generator_output"] for r in rec.values())
+    assert rec["resnet50_partitioned.txt"]["stages"] == 4 and rec["vgg16_partitioned.txt"]["stages"] == 3
+
+
+def test_graph_errors_and_configuration_maps():
+    line = "%s -- %s -- forward_compute_time=1.000, backward_compute_time=1.000, activation_size=1.000, parameter_size=0.000 -- stage_id=0"
+    with pytest.raises(ValueError, match="not supported"):
+        stagegen.describe("\n".join([line % ("node1", "Input"), line % ("node2", "Concat(1)"), "\tnode1 -- node2"]), "x")
+    with pytest.raises(ValueError, match="cycle"):
+        stagegen.describe("\n".join([line % ("node1", "ReLU(inplace)"), line % ("node2", "ReLU(inplace)"),
+                                     "\tnode1 -- node2", "\tnode2 -- node1"]), "x")
+    with pytest.raises(ValueError, match="unknown node"):
+        stagegen.Graph.parse("\n".join([line % ("node1", "Input"), "\tnode1 -- node9"]))
+    assert stagegen.parse_module("Conv2d(3, 8, kernel_size=(3, 3), stride=(2, 2), bias=False)") == (
+        "Conv2d", {"in_channels": 3, "out_channels": 8, "kernel_size": [3, 3], "stride": [2, 2], "padding": [0, 0], "bias": False})
+    assert stagegen.parse_module("ReLU(inplace)") == ("ReLU", {"inplace": True})
+    assert stagegen.configuration_maps(3) == {"module_to_stage_map": [0, 1, 2, 2],
+                                              "stage_to_rank_map": {"0": [0], "1": [1], "2": [2]}}
+    assert stagegen.configuration_maps(2, [3, 1]) == {"module_to_stage_map": [0, 1, 1],
+                                                      "stage_to_rank_map": {"0": [0, 1, 2], "1": [3]}}
+    # activation sizes of nodes with several outputs are written as a list
+    g = stagegen.Graph.parse(line.replace("activation_size=1.000", "activation_size=[2.0; 3.0]") % ("node1", "Input"))
+    assert g.nodes["node1"].activation == 5.0
