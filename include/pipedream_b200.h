@@ -193,6 +193,15 @@ int pd_embedding_bwd(const int64_t* ids, const void* dy, int64_t n, int D, int64
 int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
                int out_dtype, int64_t ldo, int M, int N, int K, const void* bias, int bias_dtype,
                int relu, int pad_hp, int pad_wp, void* stream);
+/* pd_gemm_nt for a short, wide problem (a Linear layer at a batch of 64: a handful of output tiles,
+ * hundreds of MB of weights): K is cut into slices that add into `workspace`
+ * (pd_gemm_nt_splitk_workspace_bytes(M, N) bytes of device memory, cleared by the call) with fp32
+ * atomics, then bias / ReLU / conversion into `out`.  bf16 operands only.                       */
+int64_t pd_gemm_nt_splitk_workspace_bytes(int M, int N);
+int pd_gemm_nt_splitk(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+                      int out_dtype, int64_t ldo, int M, int N, int K, const void* bias,
+                      int bias_dtype, int relu, void* workspace, int64_t workspace_bytes,
+                      void* stream);
 int pd_gemm_nn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
                int out_dtype, int64_t ldo, int M, int N, int K, const void* relu_aux,
                int64_t ld_aux, void* stream);

@@ -71,6 +71,8 @@ SIGNATURES = {
     "pd_embedding_fwd": (I, [P, P, L, I, L, P, I, P]),
     "pd_embedding_bwd": (I, [P, P, L, I, L, L, P, I, P]),
     "pd_gemm_nt": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, I, I, P]),
+    "pd_gemm_nt_splitk_workspace_bytes": (L, [I, I]),
+    "pd_gemm_nt_splitk": (I, [I, P, L, P, L, P, I, L, I, I, I, P, I, I, P, L, P]),
     "pd_gemm_nn": (I, [I, P, L, P, L, P, I, L, I, I, I, P, L, P]),
     "pd_gemm_tn": (I, [I, P, L, P, L, P, L, I, I, I, I, I, P]),
     "pd_conv2d_fwd": (I, [I, P, I, I, I, I, P, L, I, P, I, I, P, P]),

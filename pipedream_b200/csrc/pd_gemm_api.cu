@@ -89,6 +89,63 @@ PD_EXPORT int pd_gemm_nt(int dtype, const void* a, int64_t lda, const void* b, i
   return dispatch(g, (cudaStream_t)stream);
 }
 
+namespace {
+// out[m][n] = act(acc[m][n] + bias[n]) as bf16 (or fp32): the second half of a split-K forward contraction.
+template <typename O>
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const float* __restrict__ acc, int M, int N, const void* __restrict__ bias, int bias_dtype,
+                     int relu, O* __restrict__ out, long long ldo) {
+  const long long total = (long long)M * N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int n = (int)(i % N);
+    const long long m = i / N;
+    float v = acc[i];
+    if (bias != nullptr)
+      v += bias_dtype == PD_BF16 ? __bfloat162float(((const __nv_bfloat16*)bias)[n]) : ((const float*)bias)[n];
+    if (relu) v = fmaxf(v, 0.f);
+    out[m * ldo + n] = pd_from_float<O>(v);
+  }
+}
+}  // namespace
+
+// The same product for a short, wide problem - a Linear layer at a batch of 64: [64, 25088] x [4096, 25088]^T has 16
+// output tiles for 148 SMs and 205 MB of weights to stream.  The contraction is cut into K slices that add their
+// parts into `workspace` (M x N floats, cleared here) with fp32 atomics, and a second small kernel applies bias and
+// ReLU and writes `out`.  The order of the additions varies from run to run (last-bit differences).
+PD_EXPORT int64_t pd_gemm_nt_splitk_workspace_bytes(int M, int N) { return (int64_t)M * N * (int64_t)sizeof(float); }
+
+PD_EXPORT int pd_gemm_nt_splitk(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
+                                int out_dtype, int64_t ldo, int M, int N, int K, const void* bias,
+                                int bias_dtype, int relu, void* workspace, int64_t workspace_bytes, void* stream) {
+  PD_REQUIRE(a && b && out && workspace, "pd_gemm_nt_splitk: null pointer");
+  PD_REQUIRE(dtype == PD_BF16, "pd_gemm_nt_splitk: bf16 operands only");
+  PD_REQUIRE(out_dtype == PD_BF16 || out_dtype == PD_F32, "pd_gemm_nt_splitk: bad output type");
+  PD_REQUIRE(workspace_bytes >= pd_gemm_nt_splitk_workspace_bytes(M, N), "pd_gemm_nt_splitk: workspace too small");
+  cudaStream_t s = (cudaStream_t)stream;
+  PdGemm g; init(g);
+  g.dtype = dtype;
+  g.a = a; g.a_rows = M; g.a_cols = K; g.lda = lda; g.a_major = 0;
+  g.b = b; g.b_rows = N; g.b_cols = K; g.ldb = ldb; g.b_major = 0;
+  g.M = M; g.N = N; g.K = K;
+  g.out = workspace; g.out_dtype = PD_F32; g.ldo = N;
+  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  g.split_k = grad_split(dtype, M, N, 1, 1, 128, bn, (K + 63) / 64);
+  int rc = prepare_grad_out(g, 0, M, N, s);
+  if (rc != PD_OK) return rc;
+  rc = dispatch(g, s);
+  if (rc != PD_OK) return rc;
+  const long long total = (long long)M * N;
+  int grid = (int)((total + 255) / 256);
+  if (grid > pd_num_sms() * 8) grid = pd_num_sms() * 8;
+  if (out_dtype == PD_BF16)
+    splitk_finish_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const float*)workspace, M, N, bias, bias_dtype, relu,
+                                                            (__nv_bfloat16*)out, ldo);
+  else
+    splitk_finish_kernel<float><<<grid, 256, 0, s>>>((const float*)workspace, M, N, bias, bias_dtype, relu, (float*)out, ldo);
+  PD_LAUNCH_CHECK("splitk_finish_kernel");
+  return PD_OK;
+}
+
 // out[M,N] = a[M,K] . b[K,N]; optional mask: out = aux > 0 ? out : 0   -- Linear data gradient
 PD_EXPORT int pd_gemm_nn(int dtype, const void* a, int64_t lda, const void* b, int64_t ldb, void* out,
                          int out_dtype, int64_t ldo, int M, int N, int K, const void* relu_aux,

@@ -198,7 +198,18 @@ __device__ __forceinline__ void epilogue_chunk(const KParams& p, const uint32_t*
     }
   } else {
     float* o = (float*)p.out + (long long)m * p.ldo + out_col0 + nb;
-    if (full && (((uintptr_t)o) & 15) == 0) {
+    if (full && (((uintptr_t)o) & 31) == 0) {
+      // 32-byte stores, as for bf16 above (a weight gradient with a short contraction - a Linear layer at batch 64 -
+      // is all epilogue: 128 KiB of fp32 per tile for four MMAs)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"l"(o + q * 8), "r"(__float_as_uint(v[q * 8])), "r"(__float_as_uint(v[q * 8 + 1])),
+                       "r"(__float_as_uint(v[q * 8 + 2])), "r"(__float_as_uint(v[q * 8 + 3])),
+                       "r"(__float_as_uint(v[q * 8 + 4])), "r"(__float_as_uint(v[q * 8 + 5])),
+                       "r"(__float_as_uint(v[q * 8 + 6])), "r"(__float_as_uint(v[q * 8 + 7]))
+                     : "memory");
+    } else if (full && (((uintptr_t)o) & 15) == 0) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         reinterpret_cast<float4*>(o)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);

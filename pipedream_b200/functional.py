@@ -290,6 +290,15 @@ def gemm_nt(a, b, bias=None, relu=False, out_dtype=None, pad_hw=None):
     N = b.shape[0]
     out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
     hp, wp = pad_hw if pad_hw is not None else (0, 0)
+    if (a.dtype == torch.bfloat16 and 32 <= M <= 128 and pad_hw is None and K >= 4096 and N <= 16384
+            and out.dtype in (torch.bfloat16, torch.float32) and not _DETERMINISTIC):
+        # a few output tiles and a long contraction (a Linear layer at a small batch): split along K over all SMs
+        ws = torch.empty(M * N, dtype=torch.float32, device=a.device)
+        _timed("gemm_nt", 2.0 * M * N * K, lambda: call(
+            "pd_gemm_nt_splitk", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0),
+            M, N, K, _p(bias), dt(bias) if bias is not None else 0, int(relu), _p(ws), ws.numel() * 4, _stream()),
+            (M, N, K))
+        return out
     _timed("gemm_nt", 2.0 * M * N * K, lambda: call(
         "pd_gemm_nt", dt(a), _p(a), a.stride(0), _p(b), b.stride(0), _p(out), _DT[out.dtype], out.stride(0), M, N, K,
         _p(bias), dt(bias) if bias is not None else 0, int(relu), hp, wp, _stream()), (M, N, K))

@@ -15,6 +15,8 @@ for the parameters of native modules.
 """
 import itertools
 
+import os
+
 import torch
 import torch.nn as nn
 
@@ -71,6 +73,8 @@ def _dense2d(t, rows, cols):
 # Conv2d 3x3 / stride 1 / pad 1
 # --------------------------------------------------------------------------- #
 _SIDE_STREAMS = {}
+# PD_BIAS_GRAD_STREAM=0 keeps the bias-gradient sums on the main stream (for timing comparisons)
+_USE_SIDE_STREAM = os.environ.get("PD_BIAS_GRAD_STREAM", "1") != "0"
 
 
 def _bias_grad_beside(dy_pad, colsum, accumulate):
@@ -132,7 +136,7 @@ class _Conv3x3Fn(torch.autograd.Function):
             dym = dy_pad
             if bp is not None and getattr(dy, "_pd_colsum", None) is not None:
                 pf.colsum_finish(dy._pd_colsum, grad_buffer(bp), take_accumulate_flag(bp))
-            elif bp is not None and ctx.direct and ctx.needs_input_grad[0]:
+            elif bp is not None and ctx.direct and ctx.needs_input_grad[0] and _USE_SIDE_STREAM:
                 # a read-only pass over dy (bound by HBM): it runs on a second stream beside the data-gradient
                 # contraction (bound by the tensor pipe); the main stream joins it before the weight gradient
                 side = _bias_grad_beside(dy_pad, grad_buffer(bp), take_accumulate_flag(bp))

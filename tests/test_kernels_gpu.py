@@ -248,6 +248,29 @@ def test_gemm_nt(dtype, M, N, K):
     check(pf.gemm_nt(a, b, bias=bias, relu=True), F.relu(ref + bias.float()), dtype, "gemm_nt bias relu")
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 25088), (64, 1000, 4096), (33, 520, 4160), (128, 4096, 4096)])
+def test_gemm_nt_short_and_wide_splits_k(M, N, K):
+    """Linear layers at a small batch take the split-K path (fp32 partial sums in a workspace, bias / ReLU / bf16
+    conversion in a second kernel); with the deterministic switch they take the plain one."""
+    dtype = torch.bfloat16
+    a = rnd(M, K, dtype=dtype, seed=40) * 0.1
+    b = rnd(N, K, dtype=dtype, seed=41) * 0.1
+    bias = rnd(N, dtype=dtype, seed=42)
+    ref = a.float() @ b.float().t()
+    got = pf.gemm_nt(a, b, bias=bias, relu=True)
+    check(got, F.relu(ref + bias.float()), dtype, "gemm_nt split-K bias relu")
+    check(pf.gemm_nt(a, b, out_dtype=torch.float32), ref, dtype, "gemm_nt split-K fp32 out")
+    prev = pf.set_deterministic(True)
+    try:
+        plain = pf.gemm_nt(a, b, bias=bias, relu=True)
+        again = pf.gemm_nt(a, b, bias=bias, relu=True)
+    finally:
+        pf.set_deterministic(prev)
+    assert torch.equal(plain, again)
+    check(plain, F.relu(ref + bias.float()), dtype, "gemm_nt plain")
+    assert pf.gemm_poll_error() == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
 def test_gemm_nn(dtype, M, N, K):

@@ -7,7 +7,8 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-pytestmark = pytest.mark.gpu
+# whole-run comparisons: weight gradients without the run-to-run varying split (see conftest.py)
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("deterministic_weight_gradients")]
 
 from oracle import pipedream_oracle as oracle            # noqa: E402
 from pipedream_b200 import layers, runtime, schedule, sgd, stages  # noqa: E402

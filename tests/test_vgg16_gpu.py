@@ -9,7 +9,8 @@ import os
 import pytest
 import torch
 
-pytestmark = pytest.mark.gpu
+# whole-run comparisons: weight gradients without the run-to-run varying split (see conftest.py)
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("deterministic_weight_gradients")]
 
 from oracle import pipedream_oracle as oracle           # noqa: E402
 from pipedream_b200 import stages, schedule, sgd, layers  # noqa: E402
