@@ -13,6 +13,18 @@ namespace {
 
 constexpr int kOptThreads = 256;
 
+// Four consecutive weights as one store (16 bytes of fp32, 8 bytes of bf16); `dst` is aligned to that size.
+__device__ __forceinline__ void store4(float* dst, const float* p) {
+  *reinterpret_cast<float4*>(dst) = make_float4(p[0], p[1], p[2], p[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, const float* p) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = v;
+}
+
 template <typename WT>
 __global__ void __launch_bounds__(kOptThreads)
 sgd_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
@@ -23,7 +35,9 @@ sgd_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
   // 4 elements per thread per iteration; arena offsets are 16-byte aligned.
   int64_t i4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  const int64_t n4 = n >> 2;
+  const bool vec = ((((uintptr_t)grad) | ((uintptr_t)mom) | ((uintptr_t)master)) & 15) == 0 &&
+                   ((((uintptr_t)w_read) | ((uintptr_t)w_write)) & (4 * sizeof(WT) - 1)) == 0;
+  const int64_t n4 = vec ? n >> 2 : 0;
   for (; i4 < n4; i4 += stride) {
     const int64_t i = i4 << 2;
     float4 g = *reinterpret_cast<const float4*>(grad + i);
@@ -56,12 +70,10 @@ sgd_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
       *reinterpret_cast<float4*>(mom + i) = make_float4(b[0], b[1], b[2], b[3]);
     if (master != nullptr)
       *reinterpret_cast<float4*>(master + i) = make_float4(p[0], p[1], p[2], p[3]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) w_write[i + j] = pd_from_float<WT>(p[j]);
+    store4(w_write + i, p);
   }
-  // tail (n not a multiple of 4)
-  int64_t t = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < n) {
+  // tail (n not a multiple of 4), or everything when the pointers are not aligned
+  for (int64_t t = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += stride) {
     float pj = master ? master[t] : pd_to_float(w_read[t]);
     float d = grad[t] * grad_scale;
     if (wd != 0.f) d = fmaf(wd, pj, d);
@@ -120,8 +132,7 @@ adam_ring_kernel(const WT* __restrict__ w_read, WT* __restrict__ w_write,
     *reinterpret_cast<float4*>(exp_avg + i) = make_float4(m[0], m[1], m[2], m[3]);
     *reinterpret_cast<float4*>(exp_avg_sq + i) = make_float4(v[0], v[1], v[2], v[3]);
     if (master != nullptr) *reinterpret_cast<float4*>(master + i) = make_float4(p[0], p[1], p[2], p[3]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) w_write[i + j] = pd_from_float<WT>(p[j]);
+    store4(w_write + i, p);
   }
   // tail, or everything when the pointers are not aligned
   for (int64_t i = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {

@@ -211,39 +211,35 @@ colsum_final_kernel(const float* __restrict__ partial, int nblocks, int C, float
 
 // ---- 2x2 stride-2 max-pool on padded NHWC -----------------------------------
 // out_mode 0: padded NHWC output; 1: contiguous NCHW output.
-template <typename T>
+template <typename T, typename IdxT>
 __global__ void __launch_bounds__(kThreads)
 maxpool2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, T* __restrict__ y,
                     int out_mode) {
   const int Ho = H / 2, Wo = W / 2;
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
+  const IdxT step = (IdxT)gridDim.x * blockDim.x;
+  const IdxT row = (IdxT)Wp * C;
   if (out_mode == 0) {
-    const int64_t total = (int64_t)N * Hop * Wop * C;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-      const int c = (int)(i % C);
-      const int64_t p = i / C;
-      const int wo = (int)(p % Wop), ho = (int)((p / Wop) % Hop), n = (int)(p / ((int64_t)Wop * Hop));
+    const IdxT total = (IdxT)N * Hop * Wop * C;
+    for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+      const IdxT p = i / (IdxT)C, q = p / (IdxT)Wop, n = q / (IdxT)Hop;
+      const int c = (int)(i - p * C), wo = (int)(p - q * Wop), ho = (int)(q - n * Hop);
       float m = 0.f;
       if (ho >= 1 && ho <= Ho && wo >= 1 && wo <= Wo) {
-        const T* b = x + (((int64_t)n * Hp + (2 * (ho - 1) + 1)) * Wp + (2 * (wo - 1) + 1)) * C + c;
-        m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])),
-                  fmaxf(pd_to_float(b[(int64_t)Wp * C]), pd_to_float(b[(int64_t)Wp * C + C])));
+        const T* b = x + ((n * Hp + (IdxT)(2 * ho - 1)) * Wp + (IdxT)(2 * wo - 1)) * C + c;
+        m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])), fmaxf(pd_to_float(b[row]), pd_to_float(b[row + C])));
       }
       y[i] = pd_from_float<T>(m);
     }
   } else {
-    const int64_t total = (int64_t)N * C * Ho * Wo;
+    const IdxT total = (IdxT)N * C * Ho * Wo;
     // iterate in NHWC order for coalesced reads; small tensors only use this mode
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-      const int c = (int)(i % C);
-      const int64_t p = i / C;
-      const int wo = (int)(p % Wo), ho = (int)((p / Wo) % Ho), n = (int)(p / ((int64_t)Wo * Ho));
-      const T* b = x + (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C + c;
-      float m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])),
-                      fmaxf(pd_to_float(b[(int64_t)Wp * C]), pd_to_float(b[(int64_t)Wp * C + C])));
-      y[(((int64_t)n * C + c) * Ho + ho) * Wo + wo] = pd_from_float<T>(m);
+    for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+      const IdxT p = i / (IdxT)C, q = p / (IdxT)Wo, n = q / (IdxT)Ho;
+      const int c = (int)(i - p * C), wo = (int)(p - q * Wo), ho = (int)(q - n * Ho);
+      const T* b = x + ((n * Hp + (IdxT)(2 * ho + 1)) * Wp + (IdxT)(2 * wo + 1)) * C + c;
+      float m = fmaxf(fmaxf(pd_to_float(b[0]), pd_to_float(b[C])), fmaxf(pd_to_float(b[row]), pd_to_float(b[row + C])));
+      y[((n * C + c) * Ho + (IdxT)ho) * Wo + wo] = pd_from_float<T>(m);
     }
   }
 }
@@ -252,25 +248,25 @@ maxpool2_fwd_kernel(const T* __restrict__ x, int N, int C, int H, int W, T* __re
 // maximum of the window in (h,w) scan order, as ATen's max_pool2d does.
 // dy_mode 0: dy is padded NHWC; 1: dy is contiguous NCHW.
 // relu_mask != 0: x is a ReLU output and dx is additionally multiplied by (x > 0).
-template <typename T>
+template <typename T, typename IdxT>
 __global__ void __launch_bounds__(kThreads)
 maxpool2_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, int N, int C, int H, int W,
                     T* __restrict__ dx, int dy_mode, int relu_mask) {
   const int Ho = H / 2, Wo = W / 2;
   const int Hp = H + 2, Wp = W + 2, Hop = Ho + 2, Wop = Wo + 2;
-  const int64_t total = (int64_t)N * Hp * Wp * C;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % C);
-    const int64_t p = i / C;
-    const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), n = (int)(p / ((int64_t)Wp * Hp));
+  const IdxT total = (IdxT)N * Hp * Wp * C;
+  const IdxT step = (IdxT)gridDim.x * blockDim.x;
+  const IdxT row = (IdxT)Wp * C;
+  for (IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+    const IdxT p = i / (IdxT)C, q = p / (IdxT)Wp, n = q / (IdxT)Hp;
+    const int c = (int)(i - p * C), wp = (int)(p - q * Wp), hp = (int)(q - n * Hp);
     float g = 0.f;
     const int h = hp - 1, w = wp - 1;
     if (h >= 0 && w >= 0 && h < 2 * Ho && w < 2 * Wo) {
       const int ho = h >> 1, wo = w >> 1;
-      const T* b = x + (((int64_t)n * Hp + (2 * ho + 1)) * Wp + (2 * wo + 1)) * C + c;
+      const T* b = x + ((n * Hp + (IdxT)(2 * ho + 1)) * Wp + (IdxT)(2 * wo + 1)) * C + c;
       const float v00 = pd_to_float(b[0]), v01 = pd_to_float(b[C]);
-      const float v10 = pd_to_float(b[(int64_t)Wp * C]), v11 = pd_to_float(b[(int64_t)Wp * C + C]);
+      const float v10 = pd_to_float(b[row]), v11 = pd_to_float(b[row + C]);
       int arg = 0; float m = v00;
       if (v01 > m) { m = v01; arg = 1; }
       if (v10 > m) { m = v10; arg = 2; }
@@ -278,8 +274,8 @@ maxpool2_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, int N, in
       const int me = ((h & 1) << 1) | (w & 1);
       if (me == arg && !(relu_mask && !(m > 0.f))) {
         g = dy_mode == 0
-                ? pd_to_float(dy[(((int64_t)n * Hop + ho + 1) * Wop + wo + 1) * C + c])
-                : pd_to_float(dy[(((int64_t)n * C + c) * Ho + ho) * Wo + wo]);
+                ? pd_to_float(dy[((n * Hop + (IdxT)(ho + 1)) * Wop + (IdxT)(wo + 1)) * C + c])
+                : pd_to_float(dy[((n * C + c) * Ho + (IdxT)ho) * Wo + wo]);
       }
     }
     dx[i] = pd_from_float<T>(g);
@@ -883,7 +879,11 @@ PD_EXPORT int pd_maxpool2_fwd(const void* x, int N, int C, int H, int W, void* y
     PD_LAUNCH_CHECK("maxpool2_fwd_bf16x8_kernel");
     return PD_OK;
   }
-  PD_DISPATCH_T(dtype, maxpool2_fwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, N, C, H, W, (T*)y, out_mode);)
+  if ((int64_t)N * (H + 2) * (W + 2) * C < (1ll << 31) - (int64_t)grid * kThreads) {
+    PD_DISPATCH_T(dtype, maxpool2_fwd_kernel<T, uint32_t><<<grid, kThreads, 0, s>>>((const T*)x, N, C, H, W, (T*)y, out_mode);)
+  } else {
+    PD_DISPATCH_T(dtype, maxpool2_fwd_kernel<T, int64_t><<<grid, kThreads, 0, s>>>((const T*)x, N, C, H, W, (T*)y, out_mode);)
+  }
   PD_LAUNCH_CHECK("maxpool2_fwd_kernel");
   return PD_OK;
 }
@@ -965,7 +965,11 @@ PD_EXPORT int pd_maxpool2_bwd(const void* x, const void* dy, int N, int C, int H
     PD_LAUNCH_CHECK("maxpool2_bwd_bf16x8_kernel");
     return PD_OK;
   }
-  PD_DISPATCH_T(dtype, maxpool2_bwd_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)dy, N, C, H, W, (T*)dx, dy_mode, relu_mask);)
+  if (total < (1ll << 31) - (int64_t)grid * kThreads) {
+    PD_DISPATCH_T(dtype, maxpool2_bwd_kernel<T, uint32_t><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)dy, N, C, H, W, (T*)dx, dy_mode, relu_mask);)
+  } else {
+    PD_DISPATCH_T(dtype, maxpool2_bwd_kernel<T, int64_t><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)dy, N, C, H, W, (T*)dx, dy_mode, relu_mask);)
+  }
   PD_LAUNCH_CHECK("maxpool2_bwd_kernel");
   return PD_OK;
 }
