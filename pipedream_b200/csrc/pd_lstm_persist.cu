@@ -47,6 +47,31 @@ __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
   return v;
 }
 
+// One thread waits for the grid-wide counter; returns false when the bound ran out or an error is pending.  The poll
+// is the link of the per-step chain that every CTA sits on: it is one acquire load per trip, and the error word
+// (another round trip to L2) and the clock are looked at on every 32nd trip only.
+__device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* err, int code) {
+  const long long t0 = clock64();
+  unsigned int trips = 0;
+  while (ld_acquire(counter) < target) {
+    if ((++trips & 31u) == 0u) {
+      if (*(volatile int*)err != 0) return false;
+      if (clock64() - t0 > kWaitCycles) { atomicCAS(err, 0, code); return false; }
+    }
+  }
+  return true;
+}
+
+// Publish after a named barrier of the 128 epilogue threads: their global writes are ordered before the barrier,
+// one thread then makes them visible device-wide and counts this CTA in (the pattern of a cooperative grid sync).
+__device__ __forceinline__ void publish_step(unsigned int* counter, bool elected) {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (elected) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+  }
+}
+
 // mbarrier wait that also gives up when another role or CTA has reported an error
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, int* err, int code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -133,11 +158,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
       for (int t = 1; t < p.T && ok; ++t) {
         // every CTA has published its part of h_{t-1}
         const unsigned int target = (unsigned int)p.G * (unsigned int)t;
-        const long long t0 = clock64();
-        while (ld_acquire(p.counter) < target) {
-          if (*(volatile int*)p.err != 0) { ok = false; break; }
-          if (clock64() - t0 > kWaitCycles) { atomicCAS(p.err, 0, 5); ok = false; break; }
-        }
+        ok = wait_counter(p.counter, target, p.err, 5);
         if (!ok) break;
         asm volatile("fence.proxy.async;" ::: "memory");      // the TMA reads below come after what was just observed
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -205,6 +226,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
 #pragma unroll
       for (int g = 0; g < 4; ++g) gxv[g] = *reinterpret_cast<const uint4*>(p.gx + row4 + (int64_t)g * H);
       uint32_t r[kCols];
+      uint4 hold[4];                                 // gate activations of this step, stored after the publish
       if (t > 0) {
         ok = wait_bar(smem_u32(&acc_bar), (uint32_t)(t - 1) & 1u, p.err, 3);
         // one decision for all four epilogue warps (they meet at a named barrier further down)
@@ -246,20 +268,23 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
         }
         const int64_t rowh = ((int64_t)t * p.B + b) * H + u0;
         *reinterpret_cast<uint4*>(p.y + rowh) = pack8(hi);
+        hold[0] = pack8(ai); hold[1] = pack8(af); hold[2] = pack8(ag); hold[3] = pack8(ao);
+      }
+      // publish: the accumulator has been read (the next step may overwrite it) and h_t is written
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      publish_step(p.counter, warp == 2 && lane == 0);
+      // what only the backward pass reads goes out after the other CTAs have been let go
+      if (row) {
+        const int64_t rowh = ((int64_t)t * p.B + b) * H + u0;
         float4* cp = reinterpret_cast<float4*>(p.c_all + rowh);
         cp[0] = make_float4(c[0], c[1], c[2], c[3]);
         cp[1] = make_float4(c[4], c[5], c[6], c[7]);
         __nv_bfloat16* ap = p.act + ((int64_t)t * p.B + b) * 4 * H + u0;
-        *reinterpret_cast<uint4*>(ap) = pack8(ai);
-        *reinterpret_cast<uint4*>(ap + H) = pack8(af);
-        *reinterpret_cast<uint4*>(ap + 2 * (int64_t)H) = pack8(ag);
-        *reinterpret_cast<uint4*>(ap + 3 * (int64_t)H) = pack8(ao);
+        *reinterpret_cast<uint4*>(ap) = hold[0];
+        *reinterpret_cast<uint4*>(ap + H) = hold[1];
+        *reinterpret_cast<uint4*>(ap + 2 * (int64_t)H) = hold[2];
+        *reinterpret_cast<uint4*>(ap + 3 * (int64_t)H) = hold[3];
       }
-      // publish: the accumulator has been read (the next step may overwrite it) and h_t is written
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) atomicAdd(p.counter, 1u);
     }
   }
 
@@ -300,15 +325,6 @@ struct LstmBwdP {
   uint32_t idesc;
 };
 
-// one thread waits for the grid-wide counter; returns false when the bound ran out or an error is pending
-__device__ __forceinline__ bool wait_counter(const unsigned int* counter, unsigned int target, int* err, int code) {
-  const long long t0 = clock64();
-  while (ld_acquire(counter) < target) {
-    if (*(volatile int*)err != 0) return false;
-    if (clock64() - t0 > kWaitCycles) { atomicCAS(err, 0, code); return false; }
-  }
-  return true;
-}
 
 // AND of a flag over the 128 epilogue threads (named barrier 2)
 __device__ __forceinline__ bool all_epilogue(bool ok) {
@@ -477,9 +493,7 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
           dhp[1] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) atomicAdd(p.counter, 1u);
+      publish_step(p.counter, warp == 2 && lane == 0);
       if (t == 0) break;
       // ---- phase B(t): add this CTA's tile of dgates[t] . W_hh to dh_acc
       ok = all_epilogue(wait_bar(smem_u32(&acc_bar), (uint32_t)i & 1u, p.err, 3));
@@ -502,9 +516,7 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) atomicAdd(p.counter, 1u);
+      publish_step(p.counter, warp == 2 && lane == 0);
     }
   }
 
