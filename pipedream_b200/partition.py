@@ -109,6 +109,16 @@ def plan(times, param_bytes, act_bytes, out_bytes, num_gpus, bandwidth, straight
     return best[L - 1][M - 1][0], stages
 
 
+def plan_graph(graph, num_gpus, bandwidth, **kw):
+    """`plan` on a profile graph (`stagegen.Graph`, unpartitioned): returns (bottleneck time, stages, partitioned
+    graph text) - the text is the graph with a `stage_id` on every node, i.e. what the reference's partitioner writes
+    as `gpus=N.txt` and `stagegen.describe` turns into stages."""
+    from . import stagegen
+    groups, times, params, acts, outs = stagegen.chain_layers(graph)
+    t, stages = plan(times, params, acts, outs, num_gpus, bandwidth, **kw)
+    return t, stages, stagegen.with_stages(graph, groups, stages)
+
+
 def hybrid_conf(stages, num_layers, criterion=True):
     """`module_to_stage_map` / `stage_to_rank_map` for a model list of `num_layers` entries (+ the criterion, which
     joins the last stage), ranks numbered stage by stage."""

@@ -116,6 +116,59 @@ class Graph:
         return sorted((s for s in self.succ.get(nid, []) if s in inside), key=lambda s: self.nodes[s].desc)
 
 
+def chain_layers(g):
+    """The graph as the chain of layers `partition.plan` cuts (the reference's partitioner walks antichains of the
+    general graph, optimizer/optimizer_graph_hierarchical.py:200-260; the networks this runtime executes from
+    descriptions are chains with short side branches, for which a topological order and its prefixes are enough).
+    A position is a legal cut when every edge that crosses it carries a tensor - not the integer of a `Size` node,
+    which cannot travel between stages - and the nodes between two legal cuts form one layer.
+
+    Returns (groups, times, param_bytes, act_bytes, out_bytes): groups[i] = node ids of layer i in execution order;
+    times in seconds per minibatch (forward + backward, the graph records milliseconds); out_bytes[i] = bytes that
+    cross a cut placed after layer i."""
+    order = [n.id for n in g.order(g.stage_ids()[0])] if len(g.stage_ids()) == 1 else None
+    if order is None:
+        raise ValueError("chain_layers takes an unpartitioned graph (one stage id, or none)")
+    pos = {nid: i for i, nid in enumerate(order)}
+    L = len(order)
+    crossing = [set() for _ in range(L)]               # crossing[k]: sources of the edges over the cut after position k
+    for u, vs in g.succ.items():
+        for v in vs:
+            for k in range(pos[u], pos[v]):
+                crossing[k].add(u)
+    groups, cur = [], []
+    for k, nid in enumerate(order):
+        cur.append(nid)
+        legal = k == L - 1 or not any(g.nodes[u].desc.startswith("Size") for u in crossing[k])
+        if legal:
+            groups.append(cur)
+            cur = []
+    times = [sum(g.nodes[i].fwd + g.nodes[i].bwd for i in grp) * 1e-3 for grp in groups]
+    params = [sum(g.nodes[i].parameters for i in grp) for grp in groups]
+    acts = [sum(g.nodes[i].activation for i in grp) for grp in groups]
+    outs = [sum(g.nodes[u].activation for u in crossing[pos[grp[-1]]]) if grp[-1] != order[-1] else 0.0 for grp in groups]
+    return groups, times, params, acts, outs
+
+
+def with_stages(g, groups, stages):
+    """The text of `g` with a stage id on every node: layers stages[s] = (first, one past last, replicas) of `groups`
+    (what `partition.plan` returns) become stage s.  The result is what `describe` takes."""
+    stage_of = {}
+    for s, (start, end, _) in enumerate(stages):
+        for grp in groups[start:end]:
+            for nid in grp:
+                stage_of[nid] = s
+    if len(stage_of) != len(g.nodes):
+        raise ValueError("the stages do not cover every layer")
+    lines = ["%s -- %s -- forward_compute_time=%.3f, backward_compute_time=%.3f, activation_size=%.3f, "
+             "parameter_size=%.3f -- stage_id=%d" % (n.id, n.desc, n.fwd, n.bwd, n.activation, n.parameters, stage_of[n.id])
+             for n in g.nodes.values()]
+    for dst, srcs in g.pred.items():
+        for src in srcs:
+            lines.append("\t%s -- %s" % (src, dst))
+    return "\n".join(lines)
+
+
 def parse_module(desc):
     """`Conv2d(3, 64, kernel_size=(3, 3), ...)` -> ("Conv2d", {keyword arguments}); a bare `inplace` means True
     (the profiler prints modules with their repr, convert_graph_to_model.py:120-121)."""
@@ -202,7 +255,7 @@ def describe_stage(g, stage):
             raise ValueError("node kind %r (%s) is not supported by SpecStage" % (n.desc, n.id))
     inputs = _stage_inputs(g, stage)
     value = {}                       # node id -> name of the value that holds its result
-    flow, modules = [], []
+    flow, modules, node_of = [], [], {}
     local_inputs = _by_node_id(inputs)                    # the order of forward()'s arguments
     for pos, name in enumerate(local_inputs):
         flow.append([name, "input", pos])
@@ -239,11 +292,13 @@ def describe_stage(g, stage):
             kind, kw = parse_module(n.desc)
             name = "layer%d" % k
             modules.append([name, kind, kw])
+            node_of[name] = n.id
             flow.append([res, name] + [value[p] for p in preds])
         k += 1
     outputs, _ = _stage_outputs(g, stage, 0)
     returns = [value[nid] for nid in sorted(outputs)]
-    return {"modules": modules, "flow": flow, "returns": returns}
+    # "nodes": which graph node a module came from (to carry weights from one partition of a graph to another)
+    return {"modules": modules, "flow": flow, "returns": returns, "nodes": node_of}
 
 
 def describe(text, arch):

@@ -10,7 +10,7 @@ import os
 import pytest
 import torch
 
-from pipedream_b200 import stagegen, stages
+from pipedream_b200 import partition, stagegen, stages
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLD = json.load(open(os.path.join(HERE, "golden", "stagegen_golden.json")))
@@ -99,3 +99,46 @@ def test_graph_errors_and_configuration_maps():
     # activation sizes of nodes with several outputs are written as a list
     g = stagegen.Graph.parse(line.replace("activation_size=1.000", "activation_size=[2.0; 3.0]") % ("node1", "Input"))
     assert g.nodes["node1"].activation == 5.0
+
+
+@pytest.mark.parametrize("name", sorted(GOLD["graphs"]))
+@pytest.mark.parametrize("gpus,straight", [(2, True), (3, True), (4, False)])
+def test_partitioner_and_generator_compose(name, gpus, straight):
+    """Profile graph -> partition.plan_graph -> stagegen.describe -> SpecPackage: the stages, run one after the other
+    with the weights of the unpartitioned network (carried over by graph node), give its output."""
+    import re
+    g = GOLD["graphs"][name]
+    flat = stagegen.Graph.parse(re.sub(r"stage_id=\d+", "stage_id=0", g["text"]))
+    groups, times, params, acts, outs = stagegen.chain_layers(flat)
+    assert sum(len(x) for x in groups) == len(flat.nodes)
+    assert all(not flat.nodes[grp[-1]].desc.startswith("Size") for grp in groups)      # no integer crosses a cut
+    t, plan, text = partition.plan_graph(flat, gpus, 1e9, straight=straight, cost="b200")
+    assert sum(r for _, _, r in plan) == gpus and plan[0][0] == 0 and plan[-1][1] == len(groups)
+    whole = stages.SpecPackage(stagegen.describe(stagegen.with_stages(flat, groups, [(0, len(groups), 1)]), g["arch"]))
+    parts = stages.SpecPackage(stagegen.describe(text, g["arch"]))
+    assert len(parts.description["stages"]) == len(plan)
+    conf = stagegen.configuration_maps(len(plan), [r for _, _, r in plan])
+    assert conf["stage_to_rank_map"][str(len(plan) - 1)][-1] == gpus - 1
+    assert conf["module_to_stage_map"] == list(range(len(plan))) + [len(plan) - 1]
+    torch.manual_seed(0)
+    wm = whole.model(torch.nn.CrossEntropyLoss())
+    pm = parts.model(torch.nn.CrossEntropyLoss())
+    # weights by graph node
+    src = {}
+    for (m, _, _), st in zip(wm[:-1], whole.description["stages"]):
+        for lname, node in st["nodes"].items():
+            src[node] = getattr(m, lname).state_dict()
+    for (m, _, _), st in zip(pm[:-1], parts.description["stages"]):
+        for lname, node in st["nodes"].items():
+            getattr(m, lname).load_state_dict(src[node])
+    torch.manual_seed(1)
+    x = torch.randn(*g["input_shape"])
+
+    def run(model):
+        vals = {"input0": x}
+        for (m, ins, outs_) in model[:-1]:
+            m.eval()
+            r = m(*[vals[i] for i in ins])
+            vals.update(dict(zip(outs_, r if isinstance(r, tuple) else (r,))))
+        return vals[model[-2][2][0]]
+    assert torch.allclose(run(pm), run(wm), rtol=1e-5, atol=1e-6)
