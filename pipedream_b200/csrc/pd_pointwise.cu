@@ -7,6 +7,8 @@
 // p + (r-1)*(W+2) + (s-1) of the flattened [N*(H+2)*(W+2), C] matrix, which is
 // what lets the implicit-GEMM kernels fetch every tap with a plain 2-D TMA box.
 // Every kernel that writes such a buffer keeps the border at zero.
+#include <algorithm>
+
 #include "pd_common.cuh"
 
 namespace {
@@ -759,7 +761,7 @@ PD_EXPORT int pd_im2col3x3(const void* src, int src_dtype, int64_t sN, int64_t s
     const size_t sm3 = (size_t)9 * (W + 2) * sizeof(float);
     if (C == 3 && sm3 <= 48 * 1024 && rows * (Kpad / 8) < (1ll << 31)) {
       const int K8 = Kpad / 8;
-      const int g3 = grid_cap((int64_t)N * (H + 2), 8);
+      const int g3 = (int)std::min<int64_t>((int64_t)N * (H + 2), 1 << 20);   // one padded row per block
       if (src_dtype == PD_F32)
         im2col3x3_c3_kernel<float><<<g3, kThreads, sm3, s>>>((const float*)src, sN, sC, sH, sW, N, H, W, K8, (uint4*)dst);
       else
