@@ -2,8 +2,7 @@
 PipeDream-2BW configuration (sequence 512, vocabulary 50257 padded to 50304), bf16, Adam lr 1.5e-4,
 double-buffered weights (at most two versions, one optimizer step per two microbatches), microbatch 8
 sequences with uniform token ids.  One GPU: the whole network in one stage; N GPUs under torch.distributed.run:
-an N-stage straight pipeline.  The attention core is torch's scaled_dot_product_attention; every other
-operator runs in this repository's kernels."""
+an N-stage straight pipeline.  Every operator, the attention core included, runs in this repository's kernels."""
 import os
 
 import torch
@@ -74,8 +73,7 @@ def _line(value, ms, steps, warmup, world, label, clocks, e2e_value, ms_e2e, lau
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": round(ach, 1),
                      "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": round(ach / pk["bf16_tflops_sustained"], 4),
-                     "traffic": None, "note": "whole-step model FLOP rate per GPU (6 x parameters x tokens + attention); "
-                                              "includes torch's attention kernel"},
+                     "traffic": None, "note": "whole-step model FLOP rate per GPU (6 x parameters x tokens + attention)"},
     }
 
 

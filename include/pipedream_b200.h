@@ -232,6 +232,15 @@ int pd_layernorm_bwd(int dtype, const void* x, const void* dy, const void* gamma
                      void* workspace, int64_t workspace_bytes, void* stream);
 int pd_gelu_fwd(int dtype, const void* x, void* y, int64_t n, int tanh_form, void* stream);
 int pd_gelu_bwd(int dtype, const void* x, const void* dy, void* dx, int64_t n, int tanh_form, void* stream);
+/* Causal self-attention of a transformer block, softmax(Q K^T scale) V per head (the PipeDream-2BW GPT stages; the
+ * reference tree holds no transformer stage files).  qkv [B, T, 3, H, d]: the fused projection's output, read in
+ * place; out [B, T, H*d]; probs [B*H, T, T]: the attention weights, kept for the backward pass.  Backward: dqkv
+ * [B, T, 3, H, d] from dout [B, T, H*d]; dscores [B*H, T, T] is scratch.  bf16, d == 64, T a multiple of 128 up to
+ * 2048 (PD_ERR_INVALID otherwise).                                                                            */
+int pd_sdpa_causal_fwd(int dtype, const void* qkv, int B, int T, int H, int d, float scale, void* out,
+                       void* probs, void* stream);
+int pd_sdpa_causal_bwd(int dtype, const void* qkv, const void* probs, const void* dout, int B, int T, int H,
+                       int d, float scale, void* dqkv, void* dscores, void* stream);
 /* torch.nn.LSTM(I, H), one layer, one direction, [T,B,*] sequences (runtime/translation/models/
  * gnmt_large/gpus=4/stage0.py:11-19; the reference reaches cuDNN's RNN through it): the time loop.
  * The caller computes the input projections gx = x . W_ih^T + b_ih for all steps with pd_gemm_nt;

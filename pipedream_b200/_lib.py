@@ -49,6 +49,8 @@ SIGNATURES = {
     "pd_layernorm_workspace_bytes": (L, [L, I]),
     "pd_layernorm_fwd": (I, [I, P, L, I, P, P, F, P, P, P, P]),
     "pd_layernorm_bwd": (I, [I, P, P, P, P, P, L, I, P, P, P, I, P, L, P]),
+    "pd_sdpa_causal_fwd": (I, [I, P, I, I, I, I, F, P, P, P]),
+    "pd_sdpa_causal_bwd": (I, [I, P, P, P, I, I, I, I, F, P, P, P]),
     "pd_gelu_fwd": (I, [I, P, P, L, I, P]),
     "pd_gelu_bwd": (I, [I, P, P, P, L, I, P]),
     "pd_bn_workspace_bytes": (L, [I]),

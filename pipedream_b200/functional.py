@@ -478,6 +478,43 @@ def lstm_bwd(dy, w_hh, act, c_all):
 
 
 # --------------------------------------------------------------------------- #
+# causal self-attention (transformer stages)
+# --------------------------------------------------------------------------- #
+def sdpa_causal_supported(qkv, heads):
+    """Whether pd_sdpa_causal_fwd takes this projection output: bf16, head size 64, T a multiple of 128 up to 2048."""
+    if qkv.dim() != 3 or qkv.dtype != torch.bfloat16 or not qkv.is_cuda:
+        return False
+    B, T, C3 = qkv.shape
+    return C3 % (3 * heads) == 0 and C3 // (3 * heads) == 64 and T % 128 == 0 and 128 <= T <= 2048
+
+
+def sdpa_causal_fwd(qkv, heads):
+    """qkv [B, T, 3 * H * 64] contiguous bf16 -> (out [B, T, H * 64], probs [B * H, T, T])."""
+    _cuda(qkv)
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    d = C // heads
+    out = torch.empty((B, T, C), dtype=qkv.dtype, device=qkv.device)
+    probs = torch.empty((B * heads, T, T), dtype=qkv.dtype, device=qkv.device)
+    _timed("sdpa_fwd", 2.0 * B * heads * T * T * d, lambda: call(
+        "pd_sdpa_causal_fwd", dt(qkv), _p(qkv), B, T, heads, d, 1.0 / (d ** 0.5), _p(out), _p(probs), _stream()),
+        (B, heads, T))
+    return out, probs
+
+
+def sdpa_causal_bwd(qkv, probs, dout, heads):
+    """Gradient of sdpa_causal_fwd with respect to qkv."""
+    B, T, C3 = qkv.shape
+    d = C3 // 3 // heads
+    dqkv = torch.empty_like(qkv)
+    ws = torch.empty_like(probs)
+    _timed("sdpa_bwd", 5.0 * B * heads * T * T * d, lambda: call(
+        "pd_sdpa_causal_bwd", dt(qkv), _p(qkv), _p(probs), _p(dout), B, T, heads, d, 1.0 / (d ** 0.5), _p(dqkv), _p(ws),
+        _stream()), (B, heads, T))
+    return dqkv
+
+
+# --------------------------------------------------------------------------- #
 # additive attention
 # --------------------------------------------------------------------------- #
 def attn_fwd(pq, pk, keys_tbn, v, nb, ctx_len):

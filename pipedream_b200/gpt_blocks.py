@@ -2,12 +2,30 @@
 512, vocabulary 50257).  The reference tree holds no transformer stage files (its 2BW branch lives elsewhere),
 so these are written from the architecture description: pre-LayerNorm blocks, learned position embeddings,
 tanh-GELU MLP of width 4h, untied output projection.  They are plain torch modules - the CPU oracle runs them
-as they are, StageRuntime swaps their leaves (Linear, LayerNorm, GELU, Embedding, Dropout) for native ones; the
-softmax(QK^T)V core stays torch's scaled_dot_product_attention.
+as they are, StageRuntime swaps their leaves (Linear, LayerNorm, GELU, Embedding, Dropout and the attention core)
+for native ones.
 """
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+
+class CausalAttentionCore(nn.Module):
+    """softmax(Q K^T / sqrt(d)) V with a causal mask, per head, on the fused projection's output [B, T, 3 * hidden]
+    (q, k, v each [heads, d] per token).  A module of its own so that StageRuntime can swap it like any other leaf
+    (layers.NativeCausalAttentionCore); this form is what the CPU oracle runs."""
+
+    def __init__(self, heads):
+        super().__init__()
+        self.heads = heads
+
+    def forward(self, qkv):
+        B, T, C3 = qkv.shape
+        C = C3 // 3
+        qkv = qkv.view(B, T, 3, self.heads, C // self.heads)
+        q, k, v = qkv[:, :, 0].transpose(1, 2), qkv[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return y.transpose(1, 2).reshape(B, T, C)
 
 
 class CausalSelfAttention(nn.Module):
@@ -16,16 +34,12 @@ class CausalSelfAttention(nn.Module):
         assert hidden % heads == 0
         self.heads = heads
         self.c_attn = nn.Linear(hidden, 3 * hidden)
+        self.core = CausalAttentionCore(heads)
         self.c_proj = nn.Linear(hidden, hidden)
         self.drop = nn.Dropout(dropout)
 
     def forward(self, x):
-        B, T, C = x.shape
-        qkv = self.c_attn(x).view(B, T, 3, self.heads, C // self.heads)
-        q, k, v = qkv[:, :, 0].transpose(1, 2), qkv[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        y = y.transpose(1, 2).reshape(B, T, C)
-        return self.drop(self.c_proj(y))
+        return self.drop(self.c_proj(self.core(self.c_attn(x))))
 
 
 class Block(nn.Module):

@@ -763,6 +763,45 @@ class NativeLinear(nn.Module):
 # --------------------------------------------------------------------------- #
 # LSTM (one layer, one direction, sequence first)
 # --------------------------------------------------------------------------- #
+class _CausalAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, heads):
+        qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+        out, probs = pf.sdpa_causal_fwd(qkv, heads)
+        ctx.heads = heads
+        ctx.save_for_backward(qkv, probs)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, probs = ctx.saved_tensors
+        dout = dout if dout.is_contiguous() else dout.contiguous()
+        return pf.sdpa_causal_bwd(qkv, probs, dout, ctx.heads), None
+
+
+class NativeCausalAttentionCore(nn.Module):
+    """The attention core of a GPT block (gpt_blocks.CausalAttentionCore) on the tensor cores: batched tcgen05
+    contractions for Q K^T, P V and their gradients, row kernels for the causal softmax (csrc/pd_sdpa.cu).  Shapes the
+    kernels are not written for (head size other than 64, sequence not a multiple of 128, fp32 - the parity
+    configuration) run the original module, torch's scaled_dot_product_attention; `native_calls` counts the others."""
+
+    def __init__(self, core):
+        super().__init__()
+        self.heads = core.heads
+        self.reference = core
+        self.native_calls = 0
+
+    @staticmethod
+    def supports(m):
+        return type(m).__name__ == "CausalAttentionCore" and hasattr(m, "heads")
+
+    def forward(self, qkv):
+        if pf.sdpa_causal_supported(qkv, self.heads):
+            self.native_calls += 1
+            return _CausalAttnFn.apply(qkv, self.heads)
+        return self.reference(qkv)
+
+
 class _LSTMFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_ih, w_hh, b_ih, b_hh):
@@ -1049,7 +1088,7 @@ _LAYOUT_AWARE = (NativeConv2d, NativeReLU, NativeMaxPool2d, FusedAway, NativeBat
 _NATIVE_TYPES = _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
                                  NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention,
                                  NativeBatchNorm2d, NativeConvGeneric, NativeMaxPool3s2, NativeGlobalAvgPool,
-                                 NativeLayerNorm, NativeGELU)
+                                 NativeLayerNorm, NativeGELU, NativeCausalAttentionCore)
 
 
 _PADDED_PRODUCERS = (NativeConv2d, NativeReLU, NativeMaxPool2d, NativeBatchNorm2d, NativeMaxPool3s2, NativeConvGeneric)
@@ -1059,7 +1098,8 @@ _PADDED_CONSUMERS = (NativeConv2d, NativeReLU, NativeMaxPool2d, NativeBatchNorm2
 
 def _swap_leaf(m):
     if isinstance(m, _LAYOUT_AWARE + (NativeLinear, NativeDropout, NativeCrossEntropyLoss, NativeLabelSmoothing,
-                                      NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention)):
+                                      NativeLSTM, NativeEmuBidirLSTM, NativeEmbedding, NativeBahdanauAttention,
+                                      NativeCausalAttentionCore)):
         return m
     if NativeConv2d.supports(m):
         return NativeConv2d(m)
@@ -1081,6 +1121,8 @@ def _swap_leaf(m):
         return NativeLayerNorm(m)
     if isinstance(m, nn.GELU):
         return NativeGELU(m.approximate)
+    if NativeCausalAttentionCore.supports(m):
+        return NativeCausalAttentionCore(m)
     if NativeLSTM.supports(m):
         return NativeLSTM(m)
     if NativeEmuBidirLSTM.supports(m):

@@ -107,3 +107,38 @@ def test_gpt_two_stage_pipeline_2bw_matches_oracle(fp16):
                 # a fraction of lr either way, which is what these bounds allow for (weights ~0.02, lr 1e-3)
                 assert rel(v.cpu(), sd[k]) <= (1e-2 if v.dim() >= 2 else 2e-2), k
     assert pf.gemm_poll_error() == 0
+
+
+@pytest.mark.parametrize("B,H,T", [(2, 3, 128), (1, 2, 384), (2, 16, 512)])
+def test_causal_attention_core_vs_torch(B, H, T):
+    """The attention core on the tensor cores (batched contractions + causal softmax rows) against torch's
+    scaled_dot_product_attention in fp32 on the same bf16 inputs, forward and gradient."""
+    from pipedream_b200 import gpt_blocks
+    d = 64
+    C = H * d
+    g = torch.Generator().manual_seed(5)
+    qkv = (torch.randn(B, T, 3 * C, generator=g) * 0.8).cuda().to(torch.bfloat16)
+    dout = torch.randn(B, T, C, generator=g).cuda().to(torch.bfloat16)
+    core = gpt_blocks.CausalAttentionCore(H)
+    ref_in = qkv.float().detach().clone().requires_grad_(True)
+    ref = core(ref_in)
+    ref.backward(dout.float())
+    nat = layers.nativize(torch.nn.Sequential(gpt_blocks.CausalAttentionCore(H)))[0]
+    assert isinstance(nat, layers.NativeCausalAttentionCore)
+    x = qkv.detach().clone().requires_grad_(True)
+    y = nat(x)
+    y.backward(dout)
+    assert nat.native_calls == 1
+    assert rel(y, ref) <= 2e-2, rel(y, ref)
+    assert rel(x.grad, ref_in.grad) <= 3e-2, rel(x.grad, ref_in.grad)
+    # the three parts of the gradient separately (a wrong block would hide in the norm of the whole)
+    gq, gk, gv = [x.grad.view(B, T, 3, C)[:, :, i] for i in range(3)]
+    rq, rk, rv = [ref_in.grad.view(B, T, 3, C)[:, :, i] for i in range(3)]
+    for name, a, b in (("dq", gq, rq), ("dk", gk, rk), ("dv", gv, rv)):
+        assert rel(a, b) <= 3e-2, (name, rel(a, b))
+    assert pf.gemm_poll_error() == 0
+    # shapes the kernels are not written for run the original module
+    small = torch.randn(2, 32, 3 * 4 * 32, generator=g).cuda().to(torch.bfloat16)
+    nat2 = layers.NativeCausalAttentionCore(gpt_blocks.CausalAttentionCore(4))
+    nat2(small)
+    assert nat2.native_calls == 0
