@@ -369,6 +369,7 @@ def run_profile_case_other(name):
     captures; prints the kernel's algorithmic bytes per launch (what its roofline fraction is measured against):
     sgd / adam : the fused optimizer over a 2-version ring, 64 M bf16 parameters with fp32 master copy;
     softmax_ce : criterion forward + backward on [6400, 32320] bf16 logits (GNMT: 50 steps x 128 pairs);
+    sdpa       : causal self-attention core forward + backward, 16 x 16 heads x 512 tokens x 64;
     pool       : 2x2 max-pool forward, backward fused with the bias-gradient sums, the sums alone, the first layer's
                  patch matrix, on a [16, 64, 224, 224] bf16 activation;
     bn         : BatchNorm2d training forward + backward on a padded-NHWC [64, 58, 58, 256] bf16 tensor;
@@ -426,6 +427,19 @@ def run_profile_case_other(name):
             "maxpool2_bwd_colsum (read x and dy, write dx)": 2 * x.numel() * 2 + dy.numel() * 2,
             "relu_bwd_colsum, sums only (read dy)": x.numel() * 2,
             "im2col3x3 (read the images, write 64-byte patch rows)": img.numel() * 4 + N * (H + 2) * (H + 2) * 64}
+    elif name == "sdpa":
+        # the attention core of a GPT block: 16 sequences x 16 heads x 512 tokens x 64 (attention weights: 134 MB)
+        B, H, T, d = 16, 16, 512, 64
+        qkv = (torch.randn(B, T, 3 * H * d, generator=g) * 0.8).cuda().to(bf)
+        dout = torch.randn(B, T, H * d, generator=g).cuda().to(bf)
+        for _ in range(3):
+            out, probs = pf.sdpa_causal_fwd(qkv, H)
+            pf.sdpa_causal_bwd(qkv, probs, dout, H)
+        info["algorithmic_bytes_per_launch"] = {
+            "S = Q K^T / dP = dO V^T (write the lower tiles of the T x T matrix)": B * H * T * T * 2 * 5 // 8,
+            "causal softmax rows (read and write the lower triangle, write zeros above)": B * H * T * T * 2 * 3 // 2,
+            "P V / dS K / P^T dO / dS^T Q (read the lower tiles)": B * H * T * T * 2 * 5 // 8}
+        info["algorithmic_flops"] = {"forward": 4 * B * H * T * T * d // 2, "backward": 10 * B * H * T * T * d // 2}
     elif name == "bn":
         N, H, C = 64, 56, 256
         x = pf.pack_pnhwc(torch.randn(N, C, H, H, generator=g).cuda().to(bf))
@@ -535,11 +549,11 @@ def main():
     ap.add_argument("--model", default="vgg16", choices=["vgg16", "gnmt", "resnet50", "gpt"],
                     help="vgg16 (default, the headline line), gnmt (8+8-layer GNMT), resnet50 or gpt (24-layer 2BW decoder)")
     ap.add_argument("--profile-case", default=None,
-                    choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd", "sgd", "adam", "softmax_ce", "pool", "bn",
+                    choices=["fwd", "dgrad", "wgrad", "narrow_fwd", "narrow_dgrad", "patch_fwd", "sgd", "adam", "softmax_ce", "pool", "sdpa", "bn",
                              "layernorm", "lstm", "attn"],
                     help="run a few launches of one kernel family on a small case (for ncu) and exit")
     a = ap.parse_args()
-    if a.profile_case in ("sgd", "adam", "softmax_ce", "pool", "bn", "layernorm", "lstm", "attn"):
+    if a.profile_case in ("sgd", "adam", "softmax_ce", "pool", "sdpa", "bn", "layernorm", "lstm", "attn"):
         run_profile_case_other(a.profile_case)
         return
     if a.profile_case:

@@ -152,17 +152,20 @@ attn_bgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         __syncwarp();
         tmem_ld32(tmem_acc + ((uint32_t)(lg * 32) << 16) + (uint32_t)cc, r);
         tmem_ld_wait();
+        uint32_t w[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 pk;
-          uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[q * 8 + 2 * e]), __uint_as_float(r[q * 8 + 2 * e + 1]));
-            w[e] = *reinterpret_cast<uint32_t*>(&v);
-          }
-          *reinterpret_cast<uint4*>(o + cc + q * 8) = pk;
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+          w[e] = *reinterpret_cast<uint32_t*>(&v);
         }
+        // 32-byte stores: a lane writes whole sectors of its row (rows, leading dimensions and tile origins are
+        // multiples of 64 bytes here)
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                       ::"l"(o + cc + q * 16), "r"(w[q * 8]), "r"(w[q * 8 + 1]), "r"(w[q * 8 + 2]), "r"(w[q * 8 + 3]),
+                         "r"(w[q * 8 + 4]), "r"(w[q * 8 + 5]), "r"(w[q * 8 + 6]), "r"(w[q * 8 + 7])
+                       : "memory");
       }
     }
   }
@@ -203,9 +206,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 constexpr int kMaxVecPerLane = 8;      // T <= 32 * 8 * 8 = 2048
+// (the row kernels are instantiated for 1, 2, 4 and 8 vectors of 8 per lane - T up to 256, 512, 1024, 2048 - so that
+// a row of 512 keeps 16 values per lane in registers, not 64, and enough warps fit on an SM to hide the latency)
 
 // One warp per row of the [B H T, T] score matrix, in place: P[i, j] = softmax_j(scale S[i, j]) over j <= i, 0 beyond
 // (the tiles right of the diagonal were never written by the contraction: every element there is written here).
+template <int VPL>
 __global__ void __launch_bounds__(256)
 causal_softmax_fwd_kernel(__nv_bfloat16* __restrict__ s, int64_t rows, int T, float scale) {
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -214,10 +220,10 @@ causal_softmax_fwd_kernel(__nv_bfloat16* __restrict__ s, int64_t rows, int T, fl
   const int t = (int)(row % T);
   uint4* base = reinterpret_cast<uint4*>(s + row * T);
   const int nvec = T / 8;
-  float v[kMaxVecPerLane][8];
+  float v[VPL][8];
   float mx = -3.0e38f;
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerLane; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec && vi * 8 <= t) {
       unpack8(base[vi], v[i]);
@@ -231,7 +237,7 @@ causal_softmax_fwd_kernel(__nv_bfloat16* __restrict__ s, int64_t rows, int T, fl
   mx = warp_max(mx);
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerLane; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec && vi * 8 <= t) {
 #pragma unroll
@@ -243,7 +249,7 @@ causal_softmax_fwd_kernel(__nv_bfloat16* __restrict__ s, int64_t rows, int T, fl
   }
   const float inv = 1.f / warp_sum(sum);
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerLane; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
       float o[8];
@@ -255,6 +261,7 @@ causal_softmax_fwd_kernel(__nv_bfloat16* __restrict__ s, int64_t rows, int T, fl
 }
 
 // dS[i, j] = P[i, j] (dP[i, j] - sum_k P[i, k] dP[i, k]) scale over j <= i, 0 beyond; in place on dP.
+template <int VPL>
 __global__ void __launch_bounds__(256)
 causal_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, __nv_bfloat16* __restrict__ dp, int64_t rows, int T,
                           float scale) {
@@ -265,10 +272,10 @@ causal_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, __nv_bfloat16* __
   const uint4* pb = reinterpret_cast<const uint4*>(p + row * T);
   uint4* db = reinterpret_cast<uint4*>(dp + row * T);
   const int nvec = T / 8;
-  float pv[kMaxVecPerLane][8], dv[kMaxVecPerLane][8];
+  float pv[VPL][8], dv[VPL][8];
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerLane; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec && vi * 8 <= t) {
       unpack8(pb[vi], pv[i]);
@@ -280,7 +287,7 @@ causal_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, __nv_bfloat16* __
   }
   dot = warp_sum(dot);
 #pragma unroll
-  for (int i = 0; i < kMaxVecPerLane; ++i) {
+  for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
       float o[8];
@@ -366,7 +373,11 @@ PD_EXPORT int pd_sdpa_causal_fwd(int dtype, const void* qkv, int B, int T, int H
   // S = Q K^T
   rc = launch_bgemm(0, q, k, T, T, d, 128, 1, (__nv_bfloat16*)probs, (long long)H * T * T, (long long)T * T, T, B, H, s);
   if (rc != PD_OK) return rc;
-  causal_softmax_fwd_kernel<<<(unsigned)((BHT + 7) / 8), 256, 0, s>>>((__nv_bfloat16*)probs, BHT, T, scale);
+  const unsigned sgrid = (unsigned)((BHT + 7) / 8);
+  if (T <= 256) causal_softmax_fwd_kernel<1><<<sgrid, 256, 0, s>>>((__nv_bfloat16*)probs, BHT, T, scale);
+  else if (T <= 512) causal_softmax_fwd_kernel<2><<<sgrid, 256, 0, s>>>((__nv_bfloat16*)probs, BHT, T, scale);
+  else if (T <= 1024) causal_softmax_fwd_kernel<4><<<sgrid, 256, 0, s>>>((__nv_bfloat16*)probs, BHT, T, scale);
+  else causal_softmax_fwd_kernel<8><<<sgrid, 256, 0, s>>>((__nv_bfloat16*)probs, BHT, T, scale);
   PD_LAUNCH_CHECK("causal_softmax_fwd_kernel");
   // O = P V
   return launch_bgemm(1, pr, v, T, d, T, 64, 2, (__nv_bfloat16*)out, (long long)T * C, d, C, B, H, s);
@@ -398,7 +409,13 @@ PD_EXPORT int pd_sdpa_causal_bwd(int dtype, const void* qkv, const void* probs, 
   // dV = P^T dO (before dP is overwritten by dS: P is read, dP not)
   rc = launch_bgemm(2, pr, dO, T, d, T, 64, 3, g + 2 * C, gb, gh, gld, B, H, s);
   if (rc != PD_OK) return rc;
-  causal_softmax_bwd_kernel<<<(unsigned)((BHT + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)probs, (__nv_bfloat16*)dscores, BHT, T, scale);
+  const unsigned sgrid = (unsigned)((BHT + 7) / 8);
+  const __nv_bfloat16* pp = (const __nv_bfloat16*)probs;
+  __nv_bfloat16* dd = (__nv_bfloat16*)dscores;
+  if (T <= 256) causal_softmax_bwd_kernel<1><<<sgrid, 256, 0, s>>>(pp, dd, BHT, T, scale);
+  else if (T <= 512) causal_softmax_bwd_kernel<2><<<sgrid, 256, 0, s>>>(pp, dd, BHT, T, scale);
+  else if (T <= 1024) causal_softmax_bwd_kernel<4><<<sgrid, 256, 0, s>>>(pp, dd, BHT, T, scale);
+  else causal_softmax_bwd_kernel<8><<<sgrid, 256, 0, s>>>(pp, dd, BHT, T, scale);
   PD_LAUNCH_CHECK("causal_softmax_bwd_kernel");
   // dK = dS^T Q, dQ = dS K
   rc = launch_bgemm(2, ds, q, T, d, T, 64, 3, g + C, gb, gh, gld, B, H, s);
