@@ -132,7 +132,8 @@ def last_error():
 
 
 # kernels launched per call of each entry point (for launch accounting in benchmarks)
-LAUNCHES = {"pd_relu_bwd_colsum": 2, "pd_softmax_ce_fwd": 2}
+LAUNCHES = {"pd_relu_bwd_colsum": 2, "pd_softmax_ce_fwd": 2, "pd_gemm_nt_splitk": 2, "pd_sdpa_causal_fwd": 3,
+            "pd_sdpa_causal_bwd": 5}
 COUNTERS = None          # dict name -> calls, when a benchmark switches counting on
 
 
