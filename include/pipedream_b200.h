@@ -260,6 +260,15 @@ int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const void* b_hh, i
 int pd_lstm_bwd(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all,
                 int T, int B, int H, void* dgates, float* dh_ws, float* dc_ws, void* stream);
 
+/* The two recurrences on the batch rows b0 .. b0 + B - 1 of tensors that hold Bt rows per time step (bf16, whole
+ * sequence in one cooperative kernel): the halves of a batch, launched on two streams, run side by side.  Return 1,
+ * with nothing enqueued, where the cooperative kernels do not apply - call pd_lstm_fwd / pd_lstm_bwd on the whole
+ * batch then.  counter_ws: 4 bytes of device scratch; dh_ws, dc_ws: [B, H] fp32, per call in flight.          */
+int pd_lstm_fwd_rows(int dtype, const void* gx, const void* w_hh, const void* b_hh, int T, int Bt, int b0, int B,
+                     int H, void* y, void* act, float* c_all, void* counter_ws, void* stream);
+int pd_lstm_bwd_rows(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int Bt,
+                     int b0, int B, int H, void* dgates, float* dh_ws, float* dc_ws, void* stream);
+
 /* Normalised additive attention (runtime/translation/seq2seq/models/attention.py:84-170:
  * `calc_score`, mask, softmax, `bmm`) fused so that tanh(q + k + b) is never stored.  pq [b,tq,n] and
  * pk [b,tk,n] are the projected queries / keys (pd_gemm_nt); v [n] fp32 is linear_att / |linear_att| *

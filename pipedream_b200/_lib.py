@@ -82,6 +82,8 @@ SIGNATURES = {
     "pd_conv2d_wgrad": (I, [I, P, P, I, I, I, I, I, P, L, I, I, P]),
     "pd_lstm_fwd": (I, [I, P, P, P, I, I, I, P, P, P, P, P]),
     "pd_lstm_bwd": (I, [I, P, P, P, P, I, I, I, P, P, P, P]),
+    "pd_lstm_fwd_rows": (I, [I, P, P, P, I, I, I, I, I, P, P, P, P, P]),
+    "pd_lstm_bwd_rows": (I, [I, P, P, P, P, I, I, I, I, I, P, P, P, P]),
     "pd_attn_bahdanau_fwd": (I, [I, P, P, P, L, L, P, P, P, I, I, I, I, I, P, P, L, L, P]),
     "pd_attn_bahdanau_bwd": (I, [I, P, P, P, L, L, P, P, P, P, L, L, I, I, I, I, I, P, P, P, L, L, P, P, P, P]),
     "pd_gemm_poll_error": (I, [POINTER(c_int)]),
@@ -149,6 +151,19 @@ def launches_counted():
     if not COUNTERS:
         return 0
     return sum(n * LAUNCHES.get(name, 1) for name, n in COUNTERS.items())
+
+
+def call_or_decline(name, *args):
+    """Like `call`, for entry points that may answer 1 = "not applicable, nothing enqueued": returns False then."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc == 1:
+        return False
+    if rc != 0:
+        raise PipedreamB200Error("%s failed (status %d): %s" % (name, rc, last_error()))
+    if COUNTERS is not None:
+        COUNTERS[name] = COUNTERS.get(name, 0) + 1
+    return True
 
 
 def call(name, *args):

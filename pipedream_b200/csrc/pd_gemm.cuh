@@ -51,6 +51,11 @@ int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, i
                            float* c_all, unsigned int* counter, cudaStream_t s);
 int pd_lstm_bwd_persistent(const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int B, int H,
                            void* dgates, float* dh_ws, float* dc_ws, cudaStream_t s);
+// The same on batch rows b0 .. b0 + B - 1 of tensors holding Bt rows per time step (two halves of a batch side by side).
+int pd_lstm_fwd_persistent_rows(const void* gx, const void* w_hh, const void* b_hh, int T, int Bt, int b0, int B, int H,
+                                void* y, void* act, float* c_all, unsigned int* counter, cudaStream_t s);
+int pd_lstm_bwd_persistent_rows(const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int Bt,
+                                int b0, int B, int H, void* dgates, float* dh_ws, float* dc_ws, cudaStream_t s);
 struct CUtensorMap_st;
 int pd_make_map_2d(CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols,
                    int box_rows);

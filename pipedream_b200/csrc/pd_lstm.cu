@@ -145,6 +145,34 @@ PD_EXPORT int pd_lstm_fwd(int dtype, const void* gx, const void* w_hh, const voi
   return PD_OK;
 }
 
+// pd_lstm_fwd / pd_lstm_bwd on the batch rows b0 .. b0 + B - 1 of tensors that hold Bt rows per time step, whole
+// sequence in one cooperative kernel: the halves of a batch, launched on two streams, run side by side on the GPU
+// (the recurrence is a chain of latencies, and each half hides the other's).  bf16 only.  Returns 1 - nothing
+// enqueued - where the cooperative kernels do not apply (the caller then uses pd_lstm_fwd / pd_lstm_bwd on the whole
+// batch).  counter_ws: 4 bytes of device scratch per call in flight; dh_ws, dc_ws: [B, H] fp32 per call in flight.
+PD_EXPORT int pd_lstm_fwd_rows(int dtype, const void* gx, const void* w_hh, const void* b_hh, int T, int Bt, int b0,
+                               int B, int H, void* y, void* act, float* c_all, void* counter_ws, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(gx && w_hh && y && act && c_all && counter_ws && T > 0 && B > 0 && H > 0, "pd_lstm_fwd_rows: bad arguments");
+  if (dtype != PD_BF16) return 1;
+  static const bool enabled = [] { const char* e = getenv("PD_LSTM_PERSISTENT"); return !(e && e[0] == '0'); }();
+  if (!enabled) return 1;
+  return pd_lstm_fwd_persistent_rows(gx, w_hh, b_hh, T, Bt, b0, B, H, y, act, c_all, (unsigned int*)counter_ws,
+                                     (cudaStream_t)stream);
+}
+
+PD_EXPORT int pd_lstm_bwd_rows(int dtype, const void* dy, const void* w_hh, const void* act, const float* c_all, int T,
+                               int Bt, int b0, int B, int H, void* dgates, float* dh_ws, float* dc_ws, void* stream) {
+  int rc = pd_check_device();
+  if (rc != PD_OK) return rc;
+  PD_REQUIRE(dy && w_hh && act && c_all && dgates && dh_ws && dc_ws && T > 0 && B > 0 && H > 0, "pd_lstm_bwd_rows: bad arguments");
+  if (dtype != PD_BF16) return 1;
+  static const bool enabled = [] { const char* e = getenv("PD_LSTM_PERSISTENT"); return !(e && e[0] == '0'); }();
+  if (!enabled) return 1;
+  return pd_lstm_bwd_persistent_rows(dy, w_hh, act, c_all, T, Bt, b0, B, H, dgates, dh_ws, dc_ws, (cudaStream_t)stream);
+}
+
 // Backward recurrence.  dy: [T,B,H]; act, c_all: saved by pd_lstm_fwd; dgates: [T,B,4H] (out) gradients
 // of the gate pre-activations, from which the caller forms dx, dW_ih, dW_hh and the bias gradients with
 // three contractions and a column sum.  dh_ws, dc_ws: [B,H] fp32 scratch.

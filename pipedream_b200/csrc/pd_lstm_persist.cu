@@ -29,6 +29,8 @@ constexpr uint32_t kWBlockBytes = kCols * kBlockK * 2;   // one [32 x 64] K-bloc
 
 struct LstmP {
   int T, B, H, G, num_stages;
+  int Bt, b0;                  // the tensors hold Bt batch rows per time step; this launch works on rows b0 .. b0 + B - 1
+  uint32_t stage_bytes;        // one K-block of the h tile in shared memory: 128 rows (16 KiB), or 64 rows when B <= 64
   const __nv_bfloat16* gx;     // [T, B, 4H]
   const __nv_bfloat16* b_hh;   // [4H] or null
   __nv_bfloat16* y;            // [T, B, H]
@@ -166,8 +168,8 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
           const uint32_t ph = (it / (uint32_t)S) & 1u;
           if (!wait_bar(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) { ok = false; break; }
           const uint32_t fb = smem_u32(&full_bar[s]);
-          mbar_expect_tx(fb, kStageBytes);
-          tma_load_2d(smem_a + (uint32_t)s * kStageBytes, &map_h, fb, kb * kBlockK, (t - 1) * p.B);
+          mbar_expect_tx(fb, p.stage_bytes);
+          tma_load_2d(smem_a + (uint32_t)s * p.stage_bytes, &map_h, fb, kb * kBlockK, (t - 1) * p.Bt + p.b0);
         }
       }
     }
@@ -197,7 +199,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
             umma_lo<1, 1>(tmem_acc, a_lo + kk * 2, a_hi, b_lo + kk * 2, b_hi, idesc, 1u);
           umma_commit(eb);
           b_lo += kWBlockBytes >> 4;
-          ++s; a_lo += kStageBytes >> 4; fb += 8; eb += 8;
+          ++s; a_lo += p.stage_bytes >> 4; fb += 8; eb += 8;
           if (s == S) { s = 0; ph ^= 1u; a_lo = a_lo0; fb = full0; eb = empty0; }
         }
         if (ok) umma_commit(smem_u32(&acc_bar));
@@ -222,7 +224,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
     for (int t = 0; t < p.T && ok; ++t) {
       // input projection of this row: four 16-byte pieces (one per gate), in flight while the MMAs run
       uint4 gxv[4];
-      const int64_t row4 = ((int64_t)t * p.B + (row ? b : 0)) * 4 * H + u0;
+      const int64_t row4 = ((int64_t)t * p.Bt + p.b0 + (row ? b : 0)) * 4 * H + u0;
 #pragma unroll
       for (int g = 0; g < 4; ++g) gxv[g] = *reinterpret_cast<const uint4*>(p.gx + row4 + (int64_t)g * H);
       uint32_t r[kCols];
@@ -266,7 +268,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
           c[j] = af[j] * c[j] + ai[j] * ag[j];
           hi[j] = ao[j] * tanhf(c[j]);
         }
-        const int64_t rowh = ((int64_t)t * p.B + b) * H + u0;
+        const int64_t rowh = ((int64_t)t * p.Bt + p.b0 + b) * H + u0;
         *reinterpret_cast<uint4*>(p.y + rowh) = pack8(hi);
         hold[0] = pack8(ai); hold[1] = pack8(af); hold[2] = pack8(ag); hold[3] = pack8(ao);
       }
@@ -275,11 +277,11 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap map_h, const __gr
       publish_step(p.counter, warp == 2 && lane == 0);
       // what only the backward pass reads goes out after the other CTAs have been let go
       if (row) {
-        const int64_t rowh = ((int64_t)t * p.B + b) * H + u0;
+        const int64_t rowh = ((int64_t)t * p.Bt + p.b0 + b) * H + u0;
         float4* cp = reinterpret_cast<float4*>(p.c_all + rowh);
         cp[0] = make_float4(c[0], c[1], c[2], c[3]);
         cp[1] = make_float4(c[4], c[5], c[6], c[7]);
-        __nv_bfloat16* ap = p.act + ((int64_t)t * p.B + b) * 4 * H + u0;
+        __nv_bfloat16* ap = p.act + ((int64_t)t * p.Bt + p.b0 + b) * 4 * H + u0;
         *reinterpret_cast<uint4*>(ap) = hold[0];
         *reinterpret_cast<uint4*>(ap + H) = hold[1];
         *reinterpret_cast<uint4*>(ap + 2 * (int64_t)H) = hold[2];
@@ -314,6 +316,7 @@ constexpr uint32_t kBwdWBytes = kBwdK * kBwdN * 2;       // 128 KiB
 
 struct LstmBwdP {
   int T, B, H, G, U, NS;
+  int Bt, b0;                   // as in LstmP
   const __nv_bfloat16* dy;      // [T, B, H]
   const __nv_bfloat16* act;     // [T, B, 4H]
   const float* c_all;           // [T, B, H]
@@ -392,7 +395,7 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
           if (!wait_bar(smem_u32(&empty_bar[s]), ph ^ 1u, p.err, 1)) { ok = false; break; }
           const uint32_t fb = smem_u32(&full_bar[s]);
           mbar_expect_tx(fb, kStageBytes);
-          tma_load_2d(smem_a + (uint32_t)s * kStageBytes, &map_g, fb, ks * kBwdK + kb * kBlockK, t * p.B);
+          tma_load_2d(smem_a + (uint32_t)s * kStageBytes, &map_g, fb, ks * kBwdK + kb * kBlockK, t * p.Bt + p.b0);
         }
       }
     }
@@ -443,8 +446,8 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
       }
       if (row) {
         for (int u = ua; u < ua + p.U; u += 8) {
-          const int64_t e = ((int64_t)t * p.B + b) * H + u;                 // [T,B,H] element
-          const int64_t e4 = ((int64_t)t * p.B + b) * 4 * H + u;            // [T,B,4H] element of gate 0
+          const int64_t e = ((int64_t)t * p.Bt + p.b0 + b) * H + u;         // [T,Bt,H] element
+          const int64_t e4 = ((int64_t)t * p.Bt + p.b0 + b) * 4 * H + u;    // [T,Bt,4H] element of gate 0
           const int64_t bh = (int64_t)b * H + u;
           float dyf[8], ai[8], af[8], ag[8], ao[8];
           unpack8(*reinterpret_cast<const uint4*>(p.dy + e), dyf);
@@ -460,8 +463,8 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap map_g, const __gr
           const float4 c1 = *(reinterpret_cast<const float4*>(p.c_all + e) + 1);
           float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
           if (t > 0) {
-            q0 = *reinterpret_cast<const float4*>(p.c_all + e - (int64_t)p.B * H);
-            q1 = *(reinterpret_cast<const float4*>(p.c_all + e - (int64_t)p.B * H) + 1);
+            q0 = *reinterpret_cast<const float4*>(p.c_all + e - (int64_t)p.Bt * H);
+            q1 = *(reinterpret_cast<const float4*>(p.c_all + e - (int64_t)p.Bt * H) + 1);
           }
           const float dhv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
           const float dcv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
@@ -545,15 +548,28 @@ int g_state[64];          // per device: 0 unknown, 1 usable, -1 not usable
 // per-step path), or an error code.  `counter` must point at 4 bytes of device scratch.
 int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, int T, int B, int H, void* y, void* act,
                            float* c_all, unsigned int* counter, cudaStream_t s) {
-  if (B > 128 || H % kBlockK != 0 || H % kUnits != 0 || T < 2) return 1;
+  return pd_lstm_fwd_persistent_rows(gx, w_hh, b_hh, T, B, 0, B, H, y, act, c_all, counter, s);
+}
+
+// The same on the batch rows b0 .. b0 + B - 1 of tensors that hold Bt rows per time step.  Two such launches on two
+// streams (the halves of a batch) run side by side: with B <= 64 the h tile is staged 64 rows at a time and a CTA
+// takes half of an SM's shared memory, so both grids are resident at once and each hides the other's waits.
+int pd_lstm_fwd_persistent_rows(const void* gx, const void* w_hh, const void* b_hh, int T, int Bt, int b0, int B, int H,
+                                void* y, void* act, float* c_all, unsigned int* counter, cudaStream_t s) {
+  if (B > 128 || H % kBlockK != 0 || H % kUnits != 0 || T < 2 || b0 < 0 || b0 + B > Bt) return 1;
   const int G = H / kUnits;
   const int kblocks = H / kBlockK;
   const uint32_t w_bytes = (uint32_t)kblocks * kWBlockBytes;
   if (w_bytes > 96u * 1024u) return 1;
-  int stages = (int)((200u * 1024u - w_bytes) / kStageBytes);
+  const bool half = B <= 64 && B < Bt;       // one of several launches that share the GPU
+  const uint32_t stage_bytes = half ? kStageBytes / 2 : kStageBytes;
+  const uint32_t budget = half ? 96u * 1024u : 200u * 1024u;     // half: two CTAs (105 KiB each with the slack) per SM
+  if (w_bytes + 2 * stage_bytes > budget) return 1;
+  int stages = (int)((budget - w_bytes) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) return 1;
-  const size_t smem = (size_t)w_bytes + (size_t)stages * kStageBytes + 1024;
+  // (an MMA reads 128 rows from a stage's start: with 64-row stages the last one needs 8 KiB of slack behind it)
+  const size_t smem = (size_t)w_bytes + (size_t)stages * stage_bytes + (half ? kStageBytes / 2 : 0) + 1024;
   int dev = 0;
   PD_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return 1;
@@ -563,7 +579,7 @@ int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, i
       int coop = 0, per_sm = 0;
       PD_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
       PD_CUDA(cudaFuncSetAttribute(lstm_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
-      PD_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_fwd_persistent_kernel, kThreads, smem));
+      PD_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_fwd_persistent_kernel, kThreads, 200 * 1024));
       g_state[dev] = (coop && per_sm >= 1) ? 1 : -1;
     }
     if (g_state[dev] < 0) return 1;
@@ -573,13 +589,14 @@ int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, i
   LstmP p;
   memset(&p, 0, sizeof(p));
   p.T = T; p.B = B; p.H = H; p.G = G; p.num_stages = stages;
+  p.Bt = Bt; p.b0 = b0; p.stage_bytes = stage_bytes;
   p.gx = (const __nv_bfloat16*)gx; p.b_hh = (const __nv_bfloat16*)b_hh;
   p.y = (__nv_bfloat16*)y; p.act = (__nv_bfloat16*)act; p.c_all = c_all; p.counter = counter;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   int rc = pd_gemm_error_word(&p.err);
   if (rc != PD_OK) return rc;
   CUtensorMap mh, mw;
-  rc = pd_make_map_2d(&mh, y, (int64_t)T * B, H, H, kBlockK, 128);
+  rc = pd_make_map_2d(&mh, y, (int64_t)T * Bt, H, H, kBlockK, half ? 64 : 128);
   if (rc != PD_OK) return rc;
   rc = pd_make_map_2d(&mw, w_hh, 4ll * H, H, H, kBlockK, 8);
   if (rc != PD_OK) return rc;
@@ -593,7 +610,14 @@ int pd_lstm_fwd_persistent(const void* gx, const void* w_hh, const void* b_hh, i
 // dh_ws and dc_ws: fp32 [B, H] scratch each.
 int pd_lstm_bwd_persistent(const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int B, int H,
                            void* dgates, float* dh_ws, float* dc_ws, cudaStream_t s) {
-  if (B > 128 || H < kBwdN || H > 1024 || (H & (H - 1)) != 0) return 1;
+  return pd_lstm_bwd_persistent_rows(dy, w_hh, act, c_all, T, B, 0, B, H, dgates, dh_ws, dc_ws, s);
+}
+
+// Batch rows b0 .. b0 + B - 1 of tensors with Bt rows per time step (dh_ws, dc_ws: [B, H] of this launch alone).  The
+// grid is (H / 128)^2 CTAs - 64 at H = 1024 - so the halves of a batch, launched on two streams, run side by side.
+int pd_lstm_bwd_persistent_rows(const void* dy, const void* w_hh, const void* act, const float* c_all, int T, int Bt,
+                                int b0, int B, int H, void* dgates, float* dh_ws, float* dc_ws, cudaStream_t s) {
+  if (B > 128 || H < kBwdN || H > 1024 || (H & (H - 1)) != 0 || b0 < 0 || b0 + B > Bt) return 1;
   const int NS = H / kBwdN, KS = 4 * H / kBwdK;
   const int G = NS * KS;
   if (H % G != 0 || (H / G) % 8 != 0 || G > pd_num_sms()) return 1;
@@ -625,13 +649,14 @@ int pd_lstm_bwd_persistent(const void* dy, const void* w_hh, const void* act, co
   LstmBwdP p;
   memset(&p, 0, sizeof(p));
   p.T = T; p.B = B; p.H = H; p.G = G; p.U = H / G; p.NS = NS;
+  p.Bt = Bt; p.b0 = b0;
   p.dy = (const __nv_bfloat16*)dy; p.act = (const __nv_bfloat16*)act; p.c_all = c_all;
   p.dgates = (__nv_bfloat16*)dgates; p.dh_acc = dh_ws; p.dc = dc_ws; p.counter = counter;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kBwdN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   int rc = pd_gemm_error_word(&p.err);
   if (rc != PD_OK) return rc;
   CUtensorMap mg, mw;
-  rc = pd_make_map_2d(&mg, dgates, (int64_t)T * B, 4ll * H, 4ll * H, kBlockK, 128);
+  rc = pd_make_map_2d(&mg, dgates, (int64_t)T * Bt, 4ll * H, 4ll * H, kBlockK, 128);
   if (rc != PD_OK) return rc;
   rc = pd_make_map_2d(&mw, w_hh, 4ll * H, H, H, 64, kBlockK);
   if (rc != PD_OK) return rc;

@@ -451,6 +451,44 @@ def test_lstm_layer(dtype, T, B, I, H):
         assert e <= 2 * tol, "%s: %.3e" % (name, e)
 
 
+@pytest.mark.parametrize("T,B,H", [(9, 128, 1024), (6, 64, 256), (5, 96, 512)])
+def test_lstm_halves_side_by_side_equal_one_launch(T, B, H):
+    """The backward recurrence of a batch of 64..128 rows runs as two launches on two streams (rows b0 .. b0 + B/2 - 1
+    of the same tensors): gate gradients equal to the single launch up to the order of the fp32 reductions.  The
+    forward entry point for a row range is checked directly: two calls on the halves give the single launch's
+    results bit for bit."""
+    import ctypes
+    from pipedream_b200 import _lib
+    dtype = torch.bfloat16
+    gx = rnd(T * B, 4 * H, dtype=dtype, seed=80) * 0.5
+    w = rnd(4 * H, H, dtype=dtype, seed=81) * 0.05
+    b = rnd(4 * H, dtype=dtype, seed=82) * 0.1
+    dy = rnd(T, B, H, dtype=dtype, seed=83) * 0.1
+    assert pf._lstm_halves(B, dtype) == ((0, B // 2), (B // 2, B // 2))
+    y1, act1, c1 = pf.lstm_fwd(gx, w, b, T, B, H)
+    dg2 = pf.lstm_bwd(dy, w, act1, c1)
+    prev, pf._LSTM_SPLIT = pf._LSTM_SPLIT, False
+    try:
+        assert pf._lstm_halves(B, dtype) is None
+        dg1 = pf.lstm_bwd(dy, w, act1, c1)
+    finally:
+        pf._LSTM_SPLIT = prev
+    e = rel_err(dg2, dg1)
+    print("two launches vs one, gate gradients: %.2e" % e)
+    assert e <= 1e-2
+    # forward on row ranges
+    y2, act2, c2 = torch.empty_like(y1), torch.empty_like(act1), torch.empty_like(c1)
+    ws = torch.zeros(128, dtype=torch.int32, device=DEV)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())          # noqa: E731
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for i, b0 in enumerate((0, B // 2)):
+        assert _lib.call_or_decline("pd_lstm_fwd_rows", 1, p(gx), p(w), p(b), T, B, b0, B // 2, H, p(y2), p(act2), p(c2),
+                                    ctypes.c_void_p(ws.data_ptr() + 256 * i), st)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2) and torch.equal(act1, act2) and torch.equal(c1, c2)
+    assert pf.gemm_poll_error() == 0
+
+
 def test_emu_bidir_lstm_and_embedding():
     """The swapped bidirectional encoder layer and embedding against their torch formulations."""
     from pipedream_b200 import layers, gnmt_blocks
