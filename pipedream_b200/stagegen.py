@@ -28,11 +28,14 @@ _POSITIONAL = {
     "AvgPool2d": ["kernel_size", "stride", "padding", "ceil_mode", "count_include_pad"],
     "Linear": ["in_features", "out_features", "bias"],
     "Dropout": ["p", "inplace"],
+    "Embedding": ["num_embeddings", "embedding_dim", "padding_idx"],
+    "LSTM": ["input_size", "hidden_size", "num_layers", "bias", "batch_first", "dropout", "bidirectional"],
 }
-# node kinds that are dataflow, not modules (convert_graph_to_model.py:14-25; the sequence-model kinds among them
-# - hidden states, tuple items, concatenation, transposes - have no counterpart in SpecStage and are refused)
-_DATAFLOW = ("Input", "Size", "View", "Add")
-_UNSUPPORTED = ("hidden", "__getitem__", "Mul", "Concat", "Transpose", "self.get_seq_lens")
+# node kinds that are dataflow, not modules (convert_graph_to_model.py:14-25); of those, products, transposes and the
+# speech model's sequence-length helper have no counterpart in SpecStage and are refused
+_DATAFLOW = ("Input", "Size", "View", "Add", "hidden", "__getitem__", "Concat")
+_UNSUPPORTED = ("Mul", "Transpose", "self.get_seq_lens", "MaskConv", "ResizeInput", "InferenceBatchSoftmax", "BatchRNN",
+                "SequenceWise")
 
 
 class Graph:
@@ -66,6 +69,16 @@ class Graph:
                 if n not in g.nodes:
                     raise ValueError("edge names an unknown node %r" % n)
         return g
+
+    def drop_unused_items(self):
+        """Sinks that only pick an item out of a tuple nobody reads are dropped before anything is generated
+        (convert_graph_to_model.py:452-456, one sweep over the sinks of the graph as read)."""
+        for nid in [n.id for n in self.nodes.values() if not self.succ.get(n.id) and n.desc.startswith("__getitem__")]:
+            for p in self.pred.pop(nid, []):
+                self.succ[p].remove(nid)
+            self.succ.pop(nid, None)
+            del self.nodes[nid]
+        return self
 
     def stage_ids(self):
         return sorted({n.stage for n in self.nodes.values()}, key=lambda s: (s is None, s))
@@ -172,6 +185,22 @@ def with_stages(g, groups, stages):
 def parse_module(desc):
     """`Conv2d(3, 64, kernel_size=(3, 3), ...)` -> ("Conv2d", {keyword arguments}); a bare `inplace` means True
     (the profiler prints modules with their repr, convert_graph_to_model.py:120-121)."""
+    import re
+    # composite modules of the translation model: the profiler prints their whole repr, the generator keeps the sizes
+    # (convert_graph_to_model.py:129-152).  RecurrentAttention is declared as (input, hidden, context) there and taken as
+    # (input_size, context_size, hidden_size) by the class: the two are equal in every shipped model, and the
+    # generator's order is kept.
+    if desc.startswith("EmuBidirLSTM"):
+        m = re.search(r"LSTM\((\d+), (\d+)", desc)
+        return "EmuBidirLSTM", {"input_size": int(m.group(1)), "hidden_size": int(m.group(2))}
+    if desc.startswith("RecurrentAttention"):
+        m = re.search(r"LSTM\((\d+), (\d+)\)", desc)
+        k = re.search(r"in_features=(\d+), out_features=(\d+)", desc)
+        return "RecurrentAttention", {"input_size": int(m.group(1)), "context_size": int(m.group(2)),
+                                      "hidden_size": int(k.group(1))}
+    if desc.startswith("Classifier"):
+        k = re.search(r"in_features=(\d+), out_features=(\d+)", desc)
+        return "Classifier", {"in_features": int(k.group(1)), "out_features": int(k.group(2))}
     tree = ast.parse(desc.replace("inplace)", "inplace=True)").replace("(inplace,", "(inplace=True,"), mode="eval").body
     if not isinstance(tree, ast.Call) or not isinstance(tree.func, ast.Name):
         raise ValueError("not a module description: %r" % desc)
@@ -206,6 +235,8 @@ def parse_module(desc):
         kw.setdefault("padding", 0)
     elif kind == "Linear":
         kw.setdefault("bias", True)
+    elif kind == "Embedding":
+        kw.setdefault("padding_idx", None)
     return kind, kw
 
 
@@ -219,6 +250,8 @@ def _stage_inputs(g, stage):
         if preds:
             for p in preds:
                 if g.nodes[p].stage != stage:
+                    if g.nodes[p].desc.startswith("hidden"):
+                        continue                      # initial hidden states are None on the other side as well
                     names[p] = "input%d" % k
                     k += 1
         elif n.desc.startswith("Input"):
@@ -236,6 +269,8 @@ def _stage_outputs(g, stage, counter):
         if succs:
             for s in succs:
                 if g.nodes[s].stage != stage:
+                    if n.desc.startswith("hidden"):
+                        continue
                     names[n.id] = "out%d" % counter
                     counter += 1
         else:
@@ -280,6 +315,18 @@ def describe_stage(g, stage):
             if n.desc != "View(-1)" or len(sizes) != 1 or len(data) != 1:
                 raise ValueError("only x.view(x.size(0), -1) is supported, got %r" % n.desc)
             flow.append([res, "flatten", value[data[0]], value[sizes[0]]])
+        elif n.desc.startswith("hidden"):
+            pass                                          # no statement; its items read as None
+        elif n.desc.startswith("__getitem__"):
+            if len(preds) != 1:
+                raise ValueError("__getitem__ takes one operand (%s)" % n.id)
+            idx = int(n.desc[len("__getitem__("):-1])
+            if "hidden" in g.nodes[preds[0]].desc:
+                flow.append([res, "none"])
+            else:
+                flow.append([res, "getitem", value[preds[0]], idx])
+        elif n.desc.startswith("Concat"):
+            flow.append([res, "cat", int(n.desc[len("Concat("):-1])] + [value[p] for p in preds])
         elif n.desc.startswith("Add"):
             if len(preds) != 2:
                 raise ValueError("Add takes two operands (%s)" % n.id)
@@ -305,6 +352,7 @@ def describe(text, arch):
     """The whole package: {"arch", "stages": [{"modules", "flow", "returns", "inputs", "outputs"}, ...]} with the
     package-wide tensor names the runtime's configuration uses ("input0", "out0", ...)."""
     g = Graph.parse(text) if isinstance(text, str) else text
+    g.drop_unused_items()
     ids = g.stage_ids()
     if ids == [None]:
         ids = [None]

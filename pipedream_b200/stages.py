@@ -479,20 +479,32 @@ class SyntheticTokens:
 class SpecStage(nn.Module):
     """A pipeline stage built from a description instead of a source file: the declarations
     `[name, type, kwargs]` in order, and the dataflow `[result, op, operands...]` with op one of a declared
-    module's name, "input", "clone", "add", "size0", "flatten" - the statement kinds the reference's stage
+    module's name, "input", "clone", "add", "size0", "flatten", "getitem", "none", "cat" - the statement kinds the reference's stage
     generator emits (optimizer/convert_graph_to_model.py:89-356 writes them as Python source, e.g.
     runtime/image_classification/models/resnet50/gpus=4/stage1.py:7-120).  Modules are created in declaration
     order and initialised as the generated files do (`kaiming_normal_(fan_out)` convolutions, unit BatchNorm),
     so under the same seed the parameters equal those of the generated stage, name for name."""
 
     TYPES = {"Conv2d": nn.Conv2d, "BatchNorm2d": nn.BatchNorm2d, "ReLU": nn.ReLU, "MaxPool2d": nn.MaxPool2d,
-             "AvgPool2d": nn.AvgPool2d, "Linear": nn.Linear, "Dropout": nn.Dropout}
+             "AvgPool2d": nn.AvgPool2d, "Linear": nn.Linear, "Dropout": nn.Dropout, "Embedding": nn.Embedding,
+             "LSTM": nn.LSTM}
+
+    @classmethod
+    def module_type(cls, kind):
+        """torch.nn layers, and the translation model's composite blocks (seq2seq/models/encoder.py:24-62,
+        decoder.py:13-118 in the reference; restated in gnmt_blocks.py)."""
+        if kind in cls.TYPES:
+            return cls.TYPES[kind]
+        if kind in ("EmuBidirLSTM", "RecurrentAttention", "Classifier"):
+            from . import gnmt_blocks
+            return getattr(gnmt_blocks, kind)
+        raise ValueError("module type %r is not known to SpecStage" % kind)
 
     def __init__(self, spec):
         super().__init__()
         for name, kind, kwargs in spec["modules"]:
             kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in kwargs.items()}
-            setattr(self, name, self.TYPES[kind](**kw))
+            setattr(self, name, self.module_type(kind)(**kw))
         self._flow = [tuple(st) for st in spec["flow"]]
         self._returns = list(spec["returns"])
         # "init": "generator" = what the generator appends for its vgg16 / resnet50 targets
@@ -527,8 +539,14 @@ class SpecStage(nn.Module):
                 v[res] = v[st[2]].size(0)
             elif op == "flatten":
                 v[res] = v[st[2]].view(v[st[3]], -1)
+            elif op == "getitem":
+                v[res] = v[st[2]][st[3]]
+            elif op == "none":
+                v[res] = None
+            elif op == "cat":
+                v[res] = torch.cat([v[a] for a in st[3:]], st[2])
             else:
-                v[res] = getattr(self, op)(v[st[2]])
+                v[res] = getattr(self, op)(*[v[a] for a in st[2:]])
         out = tuple(v[n] for n in self._returns)
         return out[0] if len(out) == 1 else out
 

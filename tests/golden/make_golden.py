@@ -597,17 +597,50 @@ def describe_stage(stage):
             kw = {"in_features": m.in_features, "out_features": m.out_features, "bias": m.bias is not None}
         elif kind == "Dropout":
             kw = {"p": m.p}
+        elif kind == "Embedding":
+            kw = {"num_embeddings": m.num_embeddings, "embedding_dim": m.embedding_dim, "padding_idx": m.padding_idx}
+        elif kind == "LSTM":
+            assert m.num_layers == 1 and not m.bidirectional
+            kw = {"input_size": m.input_size, "hidden_size": m.hidden_size}
+        elif kind == "EmuBidirLSTM":
+            kw = {"input_size": m.bidir.input_size, "hidden_size": m.bidir.hidden_size}
+        elif kind == "RecurrentAttention":
+            # (constructor order input, context, hidden; seq2seq/models/decoder.py:13-24)
+            kw = {"input_size": m.rnn.input_size, "context_size": m.attn.linear_k.in_features, "hidden_size": m.rnn.hidden_size}
+        elif kind == "Classifier":
+            kw = {"in_features": m.classifier.in_features, "out_features": m.classifier.out_features}
         else:
             raise ValueError("unexpected module type %s" % kind)
         mods.append([name, kind, kw])
-    g = torch.fx.symbolic_trace(stage).graph
+
+    class _LeafTracer(torch.fx.Tracer):
+        def is_leaf_module(self, m, qualname):
+            return True
+    g = _LeafTracer().trace(stage)
     flow, returns, n_in = [], [], 0
+
+    def arg_name(a):
+        return a.name if isinstance(a, torch.fx.Node) else a
+    none_names = {}
     for node in g.nodes:
         if node.op == "placeholder":
             flow.append([node.name, "input", n_in])
             n_in += 1
         elif node.op == "call_module":
-            flow.append([node.name, node.target, node.args[0].name])
+            args = []
+            for a in node.args:
+                if a is None:                       # `outK = None` in the generated source: a statement of its own
+                    nm = "none_%d" % len(none_names)
+                    none_names[nm] = True
+                    flow.append([nm, "none"])
+                    args.append(nm)
+                else:
+                    args.append(a.name)
+            flow.append([node.name, node.target] + args)
+        elif node.op == "call_function" and node.target is operator.getitem:
+            flow.append([node.name, "getitem", node.args[0].name, node.args[1]])
+        elif node.op == "call_function" and node.target is torch.cat:
+            flow.append([node.name, "cat", node.args[1]] + [a.name for a in node.args[0]])
         elif node.op == "call_method" and node.target == "clone":
             flow.append([node.name, "clone", node.args[0].name])
         elif node.op == "call_method" and node.target == "size":
@@ -715,6 +748,47 @@ def stagegen_graphs():
             "residual": ("resnet50", _graph_text(res, res_edges), (2, 3, 8, 8))}
 
 
+def stagegen_translation_graph():
+    """A small translation network in the profiler's format, cut into three stages: the encoder's first layers
+    (embedding, the bidirectional block, two LSTM layers with a residual connection), the rest of the encoder with the
+    decoder's embedding and its attention layer (initial hidden states: a `hidden` node whose items read as None),
+    and two decoder layers fed with the attention context (Concat) plus the classifier.  Hidden size 16, vocabulary
+    40.  Tuple items nobody reads are left in, as the profiler leaves them."""
+    H, V = 16, 40
+    emu = "EmuBidirLSTM(  (bidir): LSTM(%d, %d, bidirectional=True)  (layer1): LSTM(%d, %d)  (layer2): LSTM(%d, %d))" % ((H, H) * 3)
+    att = ("RecurrentAttention(  (rnn): LSTM(%d, %d)  (attn): BahdanauAttention(    (linear_q): Linear(in_features=%d, "
+           "out_features=%d, bias=False)    (linear_k): Linear(in_features=%d, out_features=%d, bias=False)    (dropout): "
+           "Dropout(p=0)  )  (dropout): Dropout(p=0))") % ((H, H) * 3)
+    cls = "Classifier(  (classifier): Linear(in_features=%d, out_features=%d, bias=True))" % (H, V)
+    drop = "Dropout(p=0.2)"
+    nodes = [("node1", "Input0", 0), ("node4", "Embedding(%d, %d, padding_idx=0)" % (V, H), 0), ("node5", emu, 0),
+             ("node2", "Input1", 0), ("node6", drop, 0), ("node7", "LSTM(%d, %d)" % (2 * H, H), 0),
+             ("node8", "__getitem__(0)", 0), ("node9", "__getitem__(1)", 0), ("node10", drop, 0),
+             ("node11", "LSTM(%d, %d)" % (H, H), 0), ("node12", "__getitem__(0)", 0), ("node13", "__getitem__(1)", 0),
+             ("node14", "Add", 0),
+             ("node15", drop, 1), ("node16", "LSTM(%d, %d)" % (H, H), 1), ("node17", "__getitem__(0)", 1),
+             ("node18", "__getitem__(1)", 1), ("node19", "Add", 1),
+             ("node3", "Input2", 1), ("node41", "Embedding(%d, %d, padding_idx=0)" % (V, H), 1), ("node40", "hidden", 1),
+             ("node42", "__getitem__(0)", 1), ("node43", att, 1), ("node44", "__getitem__(0)", 1),
+             ("node45", "__getitem__(1)", 1), ("node46", "__getitem__(2)", 1), ("node47", "__getitem__(3)", 1),
+             ("node48", drop, 2), ("node49", "Concat(2)", 2), ("node50", "__getitem__(1)", 2),
+             ("node51", "LSTM(%d, %d)" % (2 * H, H), 2), ("node52", "__getitem__(0)", 2), ("node53", "__getitem__(1)", 2),
+             ("node54", drop, 2), ("node55", "Concat(2)", 2), ("node56", "__getitem__(2)", 2),
+             ("node57", "LSTM(%d, %d)" % (2 * H, H), 2), ("node58", "__getitem__(0)", 2), ("node59", "__getitem__(1)", 2),
+             ("node60", "Add", 2), ("node96", cls, 2)]
+    edges = [("node1", "node4"), ("node4", "node5"), ("node2", "node5"), ("node5", "node6"), ("node6", "node7"),
+             ("node7", "node8"), ("node7", "node9"), ("node8", "node10"), ("node10", "node11"), ("node11", "node12"),
+             ("node11", "node13"), ("node12", "node14"), ("node8", "node14"), ("node14", "node15"), ("node15", "node16"),
+             ("node16", "node17"), ("node16", "node18"), ("node17", "node19"), ("node14", "node19"), ("node3", "node41"),
+             ("node40", "node42"), ("node41", "node43"), ("node42", "node43"), ("node19", "node43"), ("node2", "node43"),
+             ("node43", "node44"), ("node43", "node45"), ("node43", "node46"), ("node43", "node47"), ("node44", "node48"),
+             ("node48", "node49"), ("node46", "node49"), ("node40", "node50"), ("node49", "node51"), ("node50", "node51"),
+             ("node51", "node52"), ("node51", "node53"), ("node52", "node54"), ("node54", "node55"), ("node46", "node55"),
+             ("node40", "node56"), ("node55", "node57"), ("node56", "node57"), ("node57", "node58"), ("node57", "node59"),
+             ("node58", "node60"), ("node52", "node60"), ("node60", "node96")]
+    return "gnmt", _graph_text(nodes, edges)
+
+
 def _run_reference_generator(ref, text, arch, workdir):
     """optimizer/convert_graph_to_model.py as its authors run it (a script, from its own directory), on `text`."""
     os.makedirs(workdir, exist_ok=True)
@@ -752,6 +826,9 @@ def _canonical(desc):
         cur, flow = {}, []
         for stt in st["flow"]:
             res, op, args = stt[0], stt[1], stt[2:]
+            if op == "none":                    # `x = None`: where the statement stands does not matter
+                cur[res] = "None"
+                continue
             args = [cur[a] if isinstance(a, str) else a for a in args]
             cur[res] = "v%d" % len(flow)
             flow.append([cur[res], op] + args)
@@ -801,6 +878,40 @@ def make_stagegen(ref):
                 sd["%d.%s" % (si, k)] = tensor_checksum(v)
         golden["graphs"][name] = {"arch": arch, "text": text, "input_shape": list(shape), "description": desc,
                                   "output": vals[last].detach().double().flatten().tolist(), "state_dict": sd}
+    # the translation model's node kinds: descriptions compared here and in the test, numbers in the test only on
+    # shapes (the composite blocks initialise themselves, in an order of their own)
+    _import_reference(ref, domain="translation")
+    _inject_pack_utils()
+    arch, text = stagegen_translation_graph()
+    desc, model = generated_description(text, arch, "translation")
+    mine = stagegen.describe(text, arch)
+    assert _canonical(mine) == _canonical(desc), "translation"
+    shapes = {}
+    for si, (m, _, _) in enumerate(model[:-1]):
+        for k, v in m.state_dict().items():
+            shapes["%d.%s" % (si, k)] = list(v.shape)
+    golden["graphs"]["translation"] = {"arch": arch, "text": text, "description": desc, "state_dict_shapes": shapes}
+    # the reference's profile of its large translation model, cut here into four stages at node numbers (the
+    # partitioned file the shipped stages were generated from is not in the tree)
+    gpath = os.path.join(ref, "profiler", "translation", "profiles", "gnmt_large", "graph.txt")
+    gtext = open(gpath).read()
+
+    def cut(nid):
+        n = int(nid[4:])
+        if n in (1, 2):
+            return 0
+        if n == 3:
+            return 1
+        return 0 if n <= 23 else (1 if n <= 47 else (2 if n <= 74 else 3))
+    glines = gtext.strip().split("\n")
+    ptext = "\n".join([ln + " -- stage_id=%d" % cut(ln.split(" -- ")[0]) for ln in glines if not ln.startswith("\t")] +
+                      [ln for ln in glines if ln.startswith("\t")])
+    desc, _ = generated_description(ptext, "gnmt_large", "gnmt_large_cut")
+    same = _canonical(stagegen.describe(ptext, "gnmt_large")) == _canonical(desc)
+    assert same, "gnmt_large"
+    golden["checked_on_reference_graphs"]["profiles/gnmt_large/graph.txt, cut into 4 stages"] = {
+        "sha256": hashlib.sha256(gtext.encode()).hexdigest(), "stages": len(desc["stages"]),
+        "modules": sum(len(st["modules"]) for st in desc["stages"]), "equal_to_generator_output": same}
     # the reference's own partitioned test graphs: checked here, where the reference is at hand; only the outcome,
     # the stage count and the file's digest are recorded
     for fname, arch in (("vgg16_partitioned.txt", "vgg16"), ("resnet50_partitioned.txt", "resnet50")):

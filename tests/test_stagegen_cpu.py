@@ -22,6 +22,9 @@ def canonical(desc):
     for st in desc["stages"]:
         cur, flow = {}, []
         for stt in st["flow"]:
+            if stt[1] == "none":                # `x = None`: where the statement stands does not matter
+                cur[stt[0]] = "None"
+                continue
             args = [cur[a] if isinstance(a, str) else a for a in stt[2:]]
             cur[stt[0]] = "v%d" % len(flow)
             flow.append([cur[stt[0]], stt[1]] + args)
@@ -48,7 +51,7 @@ def test_description_equals_the_generators(name):
         assert a["inputs"] == b["inputs"] and a["outputs"] == b["outputs"]
 
 
-@pytest.mark.parametrize("name", sorted(GOLD["graphs"]))
+@pytest.mark.parametrize("name", sorted(k for k, v in GOLD["graphs"].items() if "output" in v))
 def test_stages_built_from_the_description_match_the_generated_modules(name):
     g = GOLD["graphs"][name]
     pkg = stages.SpecPackage(stagegen.describe(g["text"], g["arch"]))
@@ -75,7 +78,8 @@ def test_stages_built_from_the_description_match_the_generated_modules(name):
 
 def test_the_reference_graphs_were_checked_when_the_golden_file_was_written():
     rec = GOLD["checked_on_reference_graphs"]
-    assert set(rec) == {"vgg16_partitioned.txt", "resnet50_partitioned.txt"}
+    assert set(rec) == {"vgg16_partitioned.txt", "resnet50_partitioned.txt", "profiles/gnmt_large/graph.txt, cut into 4 stages"}
+    assert rec["profiles/gnmt_large/graph.txt, cut into 4 stages"]["stages"] == 4
     assert all(r["equal_to_generator_output"] for r in rec.values())
     assert rec["resnet50_partitioned.txt"]["stages"] == 4 and rec["vgg16_partitioned.txt"]["stages"] == 3
 
@@ -83,7 +87,7 @@ def test_the_reference_graphs_were_checked_when_the_golden_file_was_written():
 def test_graph_errors_and_configuration_maps():
     line = "%s -- %s -- forward_compute_time=1.000, backward_compute_time=1.000, activation_size=1.000, parameter_size=0.000 -- stage_id=0"
     with pytest.raises(ValueError, match="not supported"):
-        stagegen.describe("\n".join([line % ("node1", "Input"), line % ("node2", "Concat(1)"), "\tnode1 -- node2"]), "x")
+        stagegen.describe("\n".join([line % ("node1", "Input"), line % ("node2", "Transpose(0, 1)"), "\tnode1 -- node2"]), "x")
     with pytest.raises(ValueError, match="cycle"):
         stagegen.describe("\n".join([line % ("node1", "ReLU(inplace)"), line % ("node2", "ReLU(inplace)"),
                                      "\tnode1 -- node2", "\tnode2 -- node1"]), "x")
@@ -101,7 +105,7 @@ def test_graph_errors_and_configuration_maps():
     assert g.nodes["node1"].activation == 5.0
 
 
-@pytest.mark.parametrize("name", sorted(GOLD["graphs"]))
+@pytest.mark.parametrize("name", sorted(k for k, v in GOLD["graphs"].items() if "output" in v))
 @pytest.mark.parametrize("gpus,straight", [(2, True), (3, True), (4, False)])
 def test_partitioner_and_generator_compose(name, gpus, straight):
     """Profile graph -> partition.plan_graph -> stagegen.describe -> SpecPackage: the stages, run one after the other
@@ -142,3 +146,32 @@ def test_partitioner_and_generator_compose(name, gpus, straight):
             vals.update(dict(zip(outs_, r if isinstance(r, tuple) else (r,))))
         return vals[model[-2][2][0]]
     assert torch.allclose(run(pm), run(wm), rtol=1e-5, atol=1e-6)
+
+
+def test_translation_stages_from_a_graph():
+    """The translation model's node kinds (tuple items, initial hidden states that read as None, concatenation,
+    modules with several inputs, the composite blocks): the description equals the generator's, the stages built from
+    it have the generated modules' parameter names and shapes, and they run end to end on the CPU."""
+    g = GOLD["graphs"]["translation"]
+    desc = stagegen.describe(g["text"], g["arch"])
+    assert canonical(desc) == canonical(g["description"])
+    pkg = stages.SpecPackage(desc)
+    torch.manual_seed(0)
+    model = pkg.model(torch.nn.CrossEntropyLoss())
+    shapes = {}
+    for si, (m, _, _) in enumerate(model[:-1]):
+        for k, v in m.state_dict().items():
+            shapes["%d.%s" % (si, k)] = list(v.shape)
+    assert shapes == g["state_dict_shapes"]
+    assert [st["inputs"] for st in desc["stages"]] == [st["inputs"] for st in g["description"]["stages"]]
+    T, B, V = 7, 3, 40
+    gen = torch.Generator().manual_seed(2)
+    src = torch.randint(4, V, (T, B), generator=gen)
+    tgt = torch.randint(4, V, (T, B), generator=gen)
+    vals = {"input0": src, "input1": torch.tensor([T, T - 1, T - 2]), "input2": tgt}
+    for (m, ins, outs) in model[:-1]:
+        m.eval()
+        r = m(*[vals[i] for i in ins])
+        vals.update(dict(zip(outs, r if isinstance(r, tuple) else (r,))))
+    out = vals[model[-2][2][0]]
+    assert tuple(out.shape) == (T, B, V) and torch.isfinite(out).all()
