@@ -133,15 +133,28 @@ def chain_layers(g):
     """The graph as the chain of layers `partition.plan` cuts (the reference's partitioner walks antichains of the
     general graph, optimizer/optimizer_graph_hierarchical.py:200-260; the networks this runtime executes from
     descriptions are chains with short side branches, for which a topological order and its prefixes are enough).
-    A position is a legal cut when every edge that crosses it carries a tensor - not the integer of a `Size` node,
-    which cannot travel between stages - and the nodes between two legal cuts form one layer.
+    A position is a legal cut when every edge that crosses it carries a tensor - not the integer of a `Size` node and
+    not the tuple of a recurrent layer whose items are picked apart by `__getitem__` nodes, neither of which can travel
+    between stages (initial hidden states can: they read as None on either side) - and the nodes between two legal
+    cuts form one layer.
 
     Returns (groups, times, param_bytes, act_bytes, out_bytes): groups[i] = node ids of layer i in execution order;
     times in seconds per minibatch (forward + backward, the graph records milliseconds); out_bytes[i] = bytes that
     cross a cut placed after layer i."""
-    order = [n.id for n in g.order(g.stage_ids()[0])] if len(g.stage_ids()) == 1 else None
-    if order is None:
+    if len(g.stage_ids()) != 1:
         raise ValueError("chain_layers takes an unpartitioned graph (one stage id, or none)")
+    g.drop_unused_items()
+    order = [n.id for n in g.order(g.stage_ids()[0])]
+
+    def of_hidden(nid):
+        return g.nodes[nid].desc.startswith("__getitem__") and any(g.nodes[p].desc.startswith("hidden") for p in g.pred.get(nid, []))
+    # items of the initial hidden state (None) cost nothing and depend on nothing: each goes right in front of its
+    # reader, so that the one cut that would send a None across is the only one they forbid
+    moved = [nid for nid in order if of_hidden(nid)]
+    order = [nid for nid in order if nid not in moved]
+    for nid in moved:
+        readers = [order.index(v) for v in g.succ.get(nid, []) if v in order]
+        order.insert(min(readers) if readers else len(order), nid)
     pos = {nid: i for i, nid in enumerate(order)}
     L = len(order)
     crossing = [set() for _ in range(L)]               # crossing[k]: sources of the edges over the cut after position k
@@ -149,10 +162,15 @@ def chain_layers(g):
         for v in vs:
             for k in range(pos[u], pos[v]):
                 crossing[k].add(u)
+    def carries_tensor(u):
+        if g.nodes[u].desc.startswith("Size") or of_hidden(u):
+            return False
+        succs = g.succ.get(u, [])
+        return not (succs and all(g.nodes[v].desc.startswith("__getitem__") for v in succs)) or g.nodes[u].desc.startswith("hidden")
     groups, cur = [], []
     for k, nid in enumerate(order):
         cur.append(nid)
-        legal = k == L - 1 or not any(g.nodes[u].desc.startswith("Size") for u in crossing[k])
+        legal = k == L - 1 or all(carries_tensor(u) for u in crossing[k])
         if legal:
             groups.append(cur)
             cur = []

@@ -912,6 +912,16 @@ def make_stagegen(ref):
     golden["checked_on_reference_graphs"]["profiles/gnmt_large/graph.txt, cut into 4 stages"] = {
         "sha256": hashlib.sha256(gtext.encode()).hexdigest(), "stages": len(desc["stages"]),
         "modules": sum(len(st["modules"]) for st in desc["stages"]), "equal_to_generator_output": same}
+    # the same profile partitioned by this repository's planner for 4 GPUs (reference cost model): the generator and
+    # the front end must agree on whatever cut comes out
+    from pipedream_b200 import partition
+    _, plan4, planned = partition.plan_graph(stagegen.Graph.parse(gtext), 4, 16e9, straight=True, cost="reference")
+    desc, _ = generated_description(planned, "gnmt_large", "gnmt_large_planned")
+    same = _canonical(stagegen.describe(planned, "gnmt_large")) == _canonical(desc)
+    assert same, "gnmt_large planned"
+    golden["checked_on_reference_graphs"]["profiles/gnmt_large/graph.txt, partitioned by partition.plan_graph for 4 GPUs"] = {
+        "sha256": hashlib.sha256(gtext.encode()).hexdigest(), "stages": len(desc["stages"]),
+        "layers_per_stage": [e - b for b, e, _ in plan4], "equal_to_generator_output": same}
     # the reference's own partitioned test graphs: checked here, where the reference is at hand; only the outcome,
     # the stage count and the file's digest are recorded
     for fname, arch in (("vgg16_partitioned.txt", "vgg16"), ("resnet50_partitioned.txt", "resnet50")):

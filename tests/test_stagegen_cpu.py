@@ -78,7 +78,8 @@ def test_stages_built_from_the_description_match_the_generated_modules(name):
 
 def test_the_reference_graphs_were_checked_when_the_golden_file_was_written():
     rec = GOLD["checked_on_reference_graphs"]
-    assert set(rec) == {"vgg16_partitioned.txt", "resnet50_partitioned.txt", "profiles/gnmt_large/graph.txt, cut into 4 stages"}
+    assert set(rec) == {"vgg16_partitioned.txt", "resnet50_partitioned.txt", "profiles/gnmt_large/graph.txt, cut into 4 stages",
+                        "profiles/gnmt_large/graph.txt, partitioned by partition.plan_graph for 4 GPUs"}
     assert rec["profiles/gnmt_large/graph.txt, cut into 4 stages"]["stages"] == 4
     assert all(r["equal_to_generator_output"] for r in rec.values())
     assert rec["resnet50_partitioned.txt"]["stages"] == 4 and rec["vgg16_partitioned.txt"]["stages"] == 3
@@ -175,3 +176,31 @@ def test_translation_stages_from_a_graph():
         vals.update(dict(zip(outs, r if isinstance(r, tuple) else (r,))))
     out = vals[model[-2][2][0]]
     assert tuple(out.shape) == (T, B, V) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("gpus", [2, 3, 4])
+def test_partitioner_on_the_translation_graph(gpus):
+    """plan_graph on the translation graph: no cut sends a tuple, an integer or a None across, and the stages it
+    yields run end to end."""
+    import re
+    g = GOLD["graphs"]["translation"]
+    flat = stagegen.Graph.parse(re.sub(r"stage_id=\d+", "stage_id=0", g["text"]))
+    groups, times, params, acts, outs = stagegen.chain_layers(flat)
+    for grp in groups[:-1]:
+        last = flat.nodes[grp[-1]]
+        assert not last.desc.startswith(("LSTM", "RecurrentAttention", "Size")), last.desc
+    t, plan, text = partition.plan_graph(stagegen.Graph.parse(re.sub(r"stage_id=\d+", "stage_id=0", g["text"])), gpus, 1e9,
+                                         straight=True)
+    assert len(plan) == gpus
+    model = stages.SpecPackage(stagegen.describe(text, g["arch"])).model(torch.nn.CrossEntropyLoss())
+    T, B, V = 6, 2, 40
+    gen = torch.Generator().manual_seed(4)
+    vals = {"input0": torch.randint(4, V, (T, B), generator=gen), "input1": torch.tensor([T, T - 2]),
+            "input2": torch.randint(4, V, (T, B), generator=gen)}
+    for (m, ins, outs_) in model[:-1]:
+        m.eval()
+        for i in ins:
+            assert torch.is_tensor(vals[i]), i          # only tensors travel
+        r = m(*[vals[i] for i in ins])
+        vals.update(dict(zip(outs_, r if isinstance(r, tuple) else (r,))))
+    assert tuple(vals[model[-2][2][0]].shape) == (T, B, V)
