@@ -200,6 +200,40 @@ def with_stages(g, groups, stages):
     return "\n".join(lines)
 
 
+def chain_graph(modules, times=None, param_bytes=None, out_bytes=None):
+    """Profile-graph text of a plain chain of torch.nn layers (an `nn.Sequential`-like list): an `Input` node, one node
+    per layer described by its repr (the profiler's form, `Conv2d(3, 64, kernel_size=(3, 3), ...)`), edges from each
+    node to the next; a `torch.nn.Flatten` becomes the `Size(0)` / `View(-1)` pair the reference's traces hold.  times:
+    per-layer (forward, backward) milliseconds; sizes in bytes - what `partition.measure_layer_times` measures; zeros
+    when not given.  The result is what `partition.plan_graph` and, once partitioned, `describe` take."""
+    import torch.nn as nn
+    nodes, edges = [("node1", "Input", 0.0, 0.0, 0.0, 0.0)], []
+    prev, k = "node1", 2
+    for i, m in enumerate(modules):
+        f, b = times[i] if times is not None else (0.0, 0.0)
+        pb = float(param_bytes[i]) if param_bytes is not None else float(sum(p.numel() * p.element_size() for p in m.parameters()))
+        ob = float(out_bytes[i]) if out_bytes is not None else 0.0
+        if isinstance(m, nn.Flatten):
+            size, view = "node%d" % k, "node%d" % (k + 1)
+            nodes += [(size, "Size(0)", 0.0, 0.0, 4.0, 0.0), (view, "View(-1)", f, b, ob, 0.0)]
+            edges += [(prev, size), (prev, view), (size, view)]
+            prev, k = view, k + 2
+            continue
+        desc = repr(m).replace("\n", "")
+        if isinstance(m, nn.ReLU) and m.inplace:
+            desc = "ReLU(inplace)"
+        kind = desc.split("(")[0]
+        if kind not in _POSITIONAL:
+            raise ValueError("layer %d (%s) is not a kind a stage description can hold" % (i, kind))
+        nid = "node%d" % k
+        nodes.append((nid, desc, f, b, ob, pb))
+        edges.append((prev, nid))
+        prev, k = nid, k + 1
+    lines = ["%s -- %s -- forward_compute_time=%.3f, backward_compute_time=%.3f, activation_size=%.3f, parameter_size=%.3f"
+             % n for n in nodes]
+    return "\n".join(lines + ["\t%s -- %s" % e for e in edges])
+
+
 def parse_module(desc):
     """`Conv2d(3, 64, kernel_size=(3, 3), ...)` -> ("Conv2d", {keyword arguments}); a bare `inplace` means True
     (the profiler prints modules with their repr, convert_graph_to_model.py:120-121)."""

@@ -204,3 +204,43 @@ def test_partitioner_on_the_translation_graph(gpus):
         r = m(*[vals[i] for i in ins])
         vals.update(dict(zip(outs_, r if isinstance(r, tuple) else (r,))))
     assert tuple(vals[model[-2][2][0]].shape) == (T, B, V)
+
+
+def test_a_module_chain_becomes_a_profile_graph_and_back():
+    """chain_graph writes what the profiler would have written for a plain chain; planned, described and rebuilt, the
+    stages compute what the chain computes."""
+    torch.manual_seed(0)
+    nn = torch.nn
+    chain = [nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(inplace=True), nn.MaxPool2d(2, 2), nn.Conv2d(8, 8, 3, padding=1, bias=False),
+             nn.BatchNorm2d(8), nn.ReLU(), nn.AvgPool2d(4), nn.Flatten(), nn.Linear(8, 5), nn.Dropout(0.3), nn.Linear(5, 4)]
+    times = [(1.0 + i, 2.0 + i) for i in range(len(chain))]
+    outs = [100.0 * (i + 1) for i in range(len(chain))]
+    text = stagegen.chain_graph(chain, times, None, outs)
+    g = stagegen.Graph.parse(text)
+    assert len(g.nodes) == len(chain) + 2                      # + Input, + the Size node of the flatten
+    assert [n.stage for n in g.nodes.values()] == [None] * len(g.nodes)
+    t, plan, ptext = partition.plan_graph(stagegen.Graph.parse(text), 3, 1e9, straight=True)
+    assert len(plan) == 3 and t > 0
+    model = stages.SpecPackage(stagegen.describe(ptext, "chain")).model(nn.CrossEntropyLoss())
+    # weights: node k + 2 of the graph is layer k of the chain (the flatten took two node numbers)
+    node_layer, k = {}, 2
+    for i, m in enumerate(chain):
+        if isinstance(m, nn.Flatten):
+            k += 2
+            continue
+        node_layer["node%d" % k] = m
+        k += 1
+    for (m, _, _), st in zip(model[:-1], stagegen.describe(ptext, "chain")["stages"]):
+        for lname, node in st["nodes"].items():
+            getattr(m, lname).load_state_dict(node_layer[node].state_dict())
+    x = torch.randn(2, 3, 8, 8)
+    want = x
+    for m in chain:
+        m.eval()
+        want = m(want)
+    vals = {"input0": x}
+    for (m, ins, outs_) in model[:-1]:
+        m.eval()
+        r = m(*[vals[i] for i in ins])
+        vals.update(dict(zip(outs_, r if isinstance(r, tuple) else (r,))))
+    assert torch.allclose(vals[model[-2][2][0]], want, rtol=1e-5, atol=1e-6)
