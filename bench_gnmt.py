@@ -1,7 +1,6 @@
 """GNMT arm of bench.py (`python bench.py --model gnmt`): the 8+8-layer GNMT ("gnmt_large") in bf16,
 batch 128 sentence pairs, source/target lengths uniform in [20,50], Zipf(1.1) token ids, label-smoothed
 cross-entropy (0.1), Adam lr 2e-3 - all four stages in one process on one GPU."""
-import json
 import os
 import time
 

@@ -13,7 +13,6 @@ gradient arena with one NCCL all-reduce per step.  Every rank times its own K st
 steps with CUDA events between barriers; the job time is the maximum over ranks.
 """
 import os
-import time
 
 import torch
 import torch.distributed as dist

@@ -9,7 +9,6 @@ tests and benchmarks can drive a stage without the driver script.
 it produces the same numbers as one process per stage because each stage's own
 operation order is unchanged.
 """
-import torch
 
 from . import communication
 

@@ -20,7 +20,7 @@ import torch
 # whole-run comparisons: weight gradients without the run-to-run varying split (see conftest.py)
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("deterministic_weight_gradients")]
 
-from pipedream_b200 import stages, schedule, communication, layers  # noqa: E402
+from pipedream_b200 import stages, schedule, communication  # noqa: E402
 from pipedream_b200 import functional as pf                         # noqa: E402
 import pipeline_util as pu                                          # noqa: E402
 
